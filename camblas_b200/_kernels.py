@@ -1,0 +1,364 @@
+"""Tensor-level operations over the C ABI.
+
+The names and argument meaning follow ``camblas/_kernels.py:34-59`` and the
+functions of ``src/cuda/torch_bindings.cpp`` they resolve to in the reference:
+``matmul`` (:155-199), ``linear`` (:244-270), ``qkv_linear`` (:725-736),
+``add_rms_norm`` (:675-701), ``rms_norm`` (:602-673), ``silu_multiply``,
+``swiglu``, ``fp8_decode`` / ``fp8_linear`` (:389-452). Tensors are validated in
+Python, then passed to ``libcamblas_cuda.so`` as device pointers; every
+operation runs on the current CUDA stream of the tensor's device. Bad metadata
+raises ``ValueError`` before anything is launched; a native failure raises
+``RuntimeError`` with the library's message.
+"""
+
+import ctypes as ct
+
+import torch
+
+from . import _native
+from ._native import algorithm, kernel_family, set_algorithm, stats  # noqa: F401
+
+_INT_MAX = 2**31 - 1
+
+
+def _require(condition, message):
+    if not condition:
+        raise ValueError(message)
+
+
+def _pointer(tensor):
+    return ct.c_void_p(tensor.data_ptr()) if tensor is not None else ct.c_void_p()
+
+
+def _check_tensor(tensor, reference, what="operand"):
+    _require(tensor.is_cuda and tensor.dtype == torch.bfloat16, f"{what} must be a CUDA BF16 tensor")
+    _require(
+        tensor.device == reference.device and tensor.dtype == reference.dtype,
+        "All operands must have the same device and dtype",
+    )
+    _require(all(size <= _INT_MAX for size in tensor.shape), "LP64 dimension overflow")
+    _require(all(stride <= _INT_MAX for stride in tensor.stride()), "LP64 stride overflow")
+
+
+def _operand(tensor):
+    """Map a 2-D tensor to (tensor, transpose flag, leading dimension).
+
+    A row-major [r, c] tensor is the column-major c x r matrix, flag 'N'; a
+    tensor with unit row stride is flagged 'T'; anything else is copied
+    (``torch_bindings.cpp:146-153``).
+    """
+    rows, columns = tensor.shape
+    stride0, stride1 = tensor.stride()
+    if stride1 == 1 and stride0 >= max(1, columns):
+        return tensor, b"N", stride0
+    if stride0 == 1 and stride1 >= max(1, rows):
+        return tensor, b"T", stride1
+    return tensor.contiguous(), b"N", max(1, columns)
+
+
+def matmul(a, b, out=None, alpha=1.0, beta=0.0):
+    """Return ``alpha * a @ b + beta * out`` for 2-D BF16 CUDA tensors.
+
+    The row-major product is issued as the transposed column-major product
+    ``bgemm(op(b), op(a))`` with ``m = b.shape[1]``, ``n = a.shape[0]``, exactly
+    as the reference binding does (``torch_bindings.cpp:189-194``).
+    """
+    _check_tensor(a, a)
+    _check_tensor(b, a)
+    _require(a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[0],
+             "matmul requires compatible rank-two operands")
+    m, k, n = a.shape[0], a.shape[1], b.shape[1]
+    if out is not None:
+        _check_tensor(out, a, "output")
+        _require(out.dim() == 2 and tuple(out.shape) == (m, n) and out.is_contiguous(),
+                 "Output must have the product shape and contiguous row storage")
+        _require(out.untyped_storage().data_ptr() != a.untyped_storage().data_ptr()
+                 and out.untyped_storage().data_ptr() != b.untyped_storage().data_ptr(),
+                 "GEMM output cannot alias an input")
+        c = out
+    else:
+        _require(beta == 0, "beta requires an existing output tensor")
+        c = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    if m == 0 or n == 0:
+        return c
+    left, left_flag, left_ld = _operand(b)
+    right, right_flag, right_ld = _operand(a)
+    with torch.cuda.device(a.device):
+        native = _native.context(a.device.index)
+        native.call("bgemm", left_flag, right_flag, n, m, k, float(alpha), _pointer(left), left_ld,
+                    _pointer(right), right_ld, float(beta), _pointer(c), max(1, n))
+    return c
+
+
+def linear(x, weight, bias=None, residual=None):
+    """Return ``x @ weight.T (+ bias) (+ residual)`` with the epilogue fused.
+
+    ``x`` is ``[..., inner]``, ``weight`` ``[outputs, inner]``; leading
+    dimensions are flattened (``torch_bindings.cpp:244-270``). Unlike the
+    reference, which adds the bias with a second kernel, bias and residual are
+    applied in the GEMM epilogue before the single rounding to BF16.
+    """
+    _check_tensor(x, x)
+    _check_tensor(weight, x, "weight")
+    _require(x.dim() >= 1 and weight.dim() == 2 and x.shape[-1] == weight.shape[1],
+             "linear requires matching input and [outputs, inputs] weight dimensions")
+    inner, outputs = weight.shape[1], weight.shape[0]
+    rows = 1
+    for size in x.shape[:-1]:
+        rows *= size
+    _require(rows <= _INT_MAX, "LP64 flattened row overflow")
+    x2 = x.reshape(rows, inner)
+    if x2.stride(-1) != 1 or (rows > 1 and x2.stride(0) < inner):
+        x2 = x2.contiguous()
+    w2 = weight if weight.stride(1) == 1 and weight.stride(0) >= inner else weight.contiguous()
+    if bias is not None:
+        _check_tensor(bias, x, "bias")
+        _require(bias.dim() == 1 and bias.shape[0] == outputs and bias.is_contiguous(),
+                 "linear bias must have the output width")
+    r2 = None
+    if residual is not None:
+        _check_tensor(residual, x, "residual")
+        _require(tuple(residual.shape) == tuple(x.shape[:-1]) + (outputs,),
+                 "residual must have the output shape")
+        r2 = residual.reshape(rows, outputs)
+        if r2.stride(-1) != 1:
+            r2 = r2.contiguous()
+    out = torch.empty((rows, outputs), dtype=x.dtype, device=x.device)
+    if rows and outputs:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("linear_bf16", rows, inner, outputs, _pointer(x2),
+                        x2.stride(0) if rows > 1 else inner, _pointer(w2), w2.stride(0),
+                        _pointer(bias), _pointer(r2),
+                        (r2.stride(0) if rows > 1 else outputs) if r2 is not None else 0,
+                        _pointer(out), outputs)
+    return out.reshape(tuple(x.shape[:-1]) + (outputs,))
+
+
+def qkv_linear(x, weight, q_out, k_out, v_out):
+    """Project ``x`` with a packed ``[q_out+k_out+v_out, inner]`` weight.
+
+    Returns three separately allocated tensors, like the reference's
+    ``qkv_linear`` (``torch_bindings.cpp:725-736``, ``tests/test_qkv.py:37``),
+    but from one kernel launch over the packed weight.
+    """
+    _check_tensor(x, x)
+    _check_tensor(weight, x, "weight")
+    _require(x.dim() >= 1 and weight.dim() == 2 and x.shape[-1] == weight.shape[1]
+             and weight.shape[0] == q_out + k_out + v_out and min(q_out, k_out, v_out) > 0,
+             "qkv_linear requires a [q+k+v, inner] weight")
+    inner = weight.shape[1]
+    rows = 1
+    for size in x.shape[:-1]:
+        rows *= size
+    x2 = x.reshape(rows, inner).contiguous()
+    w2 = weight.contiguous()
+    outs = [torch.empty((rows, width), dtype=x.dtype, device=x.device)
+            for width in (q_out, k_out, v_out)]
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("qkv_linear_bf16", rows, inner, q_out, k_out, v_out, _pointer(x2), inner,
+                        _pointer(w2), inner, _pointer(outs[0]), q_out, _pointer(outs[1]), k_out,
+                        _pointer(outs[2]), v_out)
+    lead = tuple(x.shape[:-1])
+    return tuple(o.reshape(lead + (o.shape[1],)) for o in outs)
+
+
+def _dtype_code(tensor):
+    if tensor.dtype == torch.float32:
+        return 0
+    if tensor.dtype == torch.bfloat16:
+        return 2
+    raise ValueError("RMS operations take FP32 or BF16 tensors")
+
+
+def add_rms_norm(x, residual, weight, epsilon):
+    """Return ``(added, normalised)`` for ``added = x + residual``.
+
+    ``added`` is rounded to the storage type before the mean of squares;
+    ``normalised = rnd(rnd(added * rsqrt(mean(added^2)+eps)) * weight)``
+    (``inference_fusion.cuh:136-191``). Any number of rows of a contiguous
+    ``[..., width]`` tensor is handled by one launch with one CTA per row.
+    """
+    _require(x.is_cuda and residual.is_cuda and weight.is_cuda, "operands must be CUDA tensors")
+    _require(x.dtype == residual.dtype == weight.dtype and x.device == residual.device == weight.device,
+             "All operands must have the same device and dtype")
+    _require(x.shape == residual.shape and weight.dim() == 1 and weight.shape[0] == x.shape[-1],
+             "residual must match x and weight the last dimension")
+    code = _dtype_code(x)
+    width = x.shape[-1]
+    _require(4 <= width <= 65536 and width % 4 == 0, "width must be a multiple of four up to 65536")
+    x2, r2, w2 = x.contiguous(), residual.contiguous(), weight.contiguous()
+    added, out = torch.empty_like(x2), torch.empty_like(x2)
+    rows = x2.numel() // width
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("add_rms_norm_rows", code, rows, width, float(epsilon), _pointer(x2),
+                        _pointer(r2), _pointer(w2), _pointer(added), _pointer(out))
+    return added, out
+
+
+def rms_norm(x, weight, epsilon):
+    """Return ``rnd(rnd(x * rsqrt(mean(x^2)+eps)) * weight)`` over the last dimension."""
+    _require(x.is_cuda and weight.is_cuda and x.dtype == weight.dtype and x.device == weight.device,
+             "All operands must have the same device and dtype")
+    _require(weight.dim() == 1 and weight.shape[0] == x.shape[-1], "weight must match the last dimension")
+    code = _dtype_code(x)
+    width = x.shape[-1]
+    x2, w2 = x.contiguous(), weight.contiguous()
+    out = torch.empty_like(x2)
+    rows = x2.numel() // width if width else 0
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("rms_norm", code, rows, width, float(epsilon), _pointer(x2), _pointer(w2),
+                        _pointer(out))
+    return out
+
+
+def silu_multiply(gate, up):
+    """Return ``rnd(rnd(silu(gate)) * up)`` (``inference_fusion.cuh:19-29``)."""
+    _require(gate.is_cuda and gate.shape == up.shape and gate.dtype == up.dtype
+             and gate.device == up.device, "gate and up must match")
+    code = _dtype_code(gate)
+    g, u = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(g)
+    if g.numel():
+        with torch.cuda.device(gate.device):
+            native = _native.context(gate.device.index)
+            native.call("silu_multiply", code, g.numel(), _pointer(g), _pointer(u), _pointer(out))
+    return out
+
+
+def swiglu(gate, up, limit=0.0, routing=None):
+    """Return ``rnd(silu(gate) * up [* routing[row]])`` with optional clipping."""
+    _require(gate.is_cuda and gate.shape == up.shape and gate.dtype == up.dtype
+             and gate.device == up.device and gate.dim() >= 1, "gate and up must match")
+    code = _dtype_code(gate)
+    g, u = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(g)
+    width = g.shape[-1]
+    if routing is not None:
+        _require(routing.dtype == torch.float32 and routing.is_cuda and routing.is_contiguous()
+                 and routing.numel() == g.numel() // max(1, width), "routing is one FP32 per row")
+    if g.numel():
+        with torch.cuda.device(gate.device):
+            native = _native.context(gate.device.index)
+            native.call("swiglu", code, g.numel(), width, float(limit), _pointer(g), _pointer(u),
+                        _pointer(routing), _pointer(out))
+    return out
+
+
+def fp8_quantize(x):
+    """Quantise BF16 rows to E4M3 with one FP32 scale per 128 elements.
+
+    Returns ``(q, scale)`` with ``q`` ``float8_e4m3fn [rows, inner]`` and
+    ``scale`` ``float32 [rows, inner/128]``; ``scale = max(amax,1e-10)/448``
+    (``camblas/_hopper.py:82-98``).
+    """
+    _check_tensor(x, x)
+    _require(x.dim() == 2 and x.shape[1] % 128 == 0 and x.shape[1] > 0,
+             "fp8_quantize takes [rows, inner] with inner a multiple of 128")
+    x2 = x if x.stride(1) == 1 and x.stride(0) >= x.shape[1] else x.contiguous()
+    rows, inner = x2.shape
+    q = torch.empty((rows, inner), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty((rows, inner // 128), dtype=torch.float32, device=x.device)
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("fp8_quantize_rows", rows, inner, _pointer(x2),
+                        x2.stride(0) if rows > 1 else inner, _pointer(q), _pointer(scale))
+    return q, scale
+
+
+def fp8_block_gemm(q, q_scale, weight, weight_scale):
+    """Block-scaled w8a8 product, BF16 ``[rows, outputs]``.
+
+    ``q`` E4M3 ``[rows, inner]`` with ``q_scale`` FP32 ``[rows, inner/128]``;
+    ``weight`` E4M3 ``[outputs, inner]`` with ``weight_scale`` FP32
+    ``[ceil(outputs/128), inner/128]``. Each 128-deep block is accumulated on
+    its own and promoted as ``fma(dot, q_scale*w_scale, acc)`` in ascending
+    block order (``camblas/_hopper.py:118-126, 168-182``).
+    """
+    _require(q.is_cuda and weight.is_cuda and q.dtype == torch.float8_e4m3fn
+             and weight.dtype == torch.float8_e4m3fn, "operands must be CUDA float8_e4m3fn")
+    _require(q.dim() == 2 and weight.dim() == 2 and q.shape[1] == weight.shape[1]
+             and q.shape[1] % 128 == 0, "inner dimensions must match and divide by 128")
+    rows, inner = q.shape
+    outputs = weight.shape[0]
+    groups = inner // 128
+    _require(q_scale.dtype == torch.float32 and tuple(q_scale.shape) == (rows, groups)
+             and q_scale.is_contiguous(), "q_scale must be contiguous FP32 [rows, inner/128]")
+    _require(weight_scale.dtype == torch.float32
+             and tuple(weight_scale.shape) == ((outputs + 127) // 128, groups)
+             and weight_scale.is_contiguous(),
+             "weight_scale must be contiguous FP32 [ceil(outputs/128), inner/128]")
+    _require(q.is_contiguous() and weight.is_contiguous(), "operands must be contiguous")
+    out = torch.empty((rows, outputs), dtype=torch.bfloat16, device=q.device)
+    if rows and outputs:
+        with torch.cuda.device(q.device):
+            native = _native.context(q.device.index)
+            native.call("fp8_block_gemm", rows, outputs, inner, _pointer(q), _pointer(q_scale),
+                        _pointer(weight), _pointer(weight_scale), _pointer(out), outputs)
+    return out
+
+
+def fp8_decode_supported(device=None):
+    """Return whether the single-token block-32 FP8 product is available."""
+    if device is None:
+        device = torch.cuda.current_device()
+    native = _native.context(torch.device("cuda", device).index if not isinstance(device, int) else device)
+    return bool(_native.library().camblas_cuda_fp8_decode_supported(native.handle))
+
+
+def _fp8_scales(weight_scale):
+    _require(weight_scale.dtype == torch.float32 and weight_scale.dim() == 2
+             and all(stride > 0 for stride in weight_scale.stride()),
+             "weight scales must be FP32 [ceil(outputs/32), inner/32] with positive strides")
+    return weight_scale.stride(0), weight_scale.stride(1)
+
+
+def fp8_decode(x, x_scale, weight, weight_scale):
+    """Single-token block-32 E4M3 product with FP32 scales, BF16 ``[outputs]``."""
+    _require(x.is_cuda and x.dtype == torch.float8_e4m3fn and weight.dtype == torch.float8_e4m3fn,
+             "input and weight must be CUDA float8_e4m3fn")
+    outputs, inner = weight.shape
+    _require(x.numel() == inner and weight.is_contiguous() and x.is_contiguous(),
+             "input must hold one token of the weight's inner width")
+    _require(inner % 32 == 0 and 32 <= inner <= 8192 and outputs % 16 == 0 and outputs > 0,
+             "inner must be a multiple of 32 in [32, 8192] and outputs a positive multiple of 16")
+    _require(x_scale.dtype == torch.float32 and x_scale.numel() == inner // 32
+             and x_scale.dim() >= 1 and x_scale.stride(-1) > 0, "input scales must be FP32 [inner/32]")
+    _require(tuple(weight_scale.shape) == ((outputs + 31) // 32, inner // 32),
+             "weight scales must be [ceil(outputs/32), inner/32]")
+    row_stride, column_stride = _fp8_scales(weight_scale)
+    out = torch.empty((outputs,), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        native = _native.context(x.device.index)
+        native.call("fp8_decode", outputs, inner, _pointer(x), _pointer(x_scale), _pointer(weight),
+                    _pointer(weight_scale), x_scale.stride(-1), row_stride, column_stride,
+                    ct.c_void_p(), 0, _pointer(out))
+    return out
+
+
+def fp8_linear(x, weight, weight_scale):
+    """Single BF16 token quantised to block-32 power-of-two scales, then ``fp8_decode``."""
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float8_e4m3fn,
+             "input must be CUDA BF16 and weight float8_e4m3fn")
+    outputs, inner = weight.shape
+    _require(x.numel() == inner and weight.is_contiguous() and x.is_contiguous(),
+             "input must hold one token of the weight's inner width")
+    _require(inner % 32 == 0 and 32 <= inner <= 8192 and outputs % 16 == 0 and outputs > 0,
+             "inner must be a multiple of 32 in [32, 8192] and outputs a positive multiple of 16")
+    _require(tuple(weight_scale.shape) == ((outputs + 31) // 32, inner // 32),
+             "weight scales must be [ceil(outputs/32), inner/32]")
+    row_stride, column_stride = _fp8_scales(weight_scale)
+    out = torch.empty((outputs,), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        native = _native.context(x.device.index)
+        native.call("fp8_linear", outputs, inner, _pointer(x), _pointer(weight),
+                    _pointer(weight_scale), row_stride, column_stride, ct.c_void_p(), 0,
+                    _pointer(out))
+    return out

@@ -1,0 +1,544 @@
+/*
+ * extern "C" surface of libcamblas_cuda.so for B200. Argument checks and
+ * status/error behaviour mirror the reference's wrappers
+ * (src/cuda/backend.cu:954-1535, src/cuda/bfloat16.cuh:11-57); the device work
+ * is in the headers included below. There is no CPU or vendor-library route:
+ * a call either launches one of these kernels or fails with a message.
+ */
+#include "context.cuh"
+#include "dispatch_bf16.cuh"
+#include "fp8_block.cuh"
+#include "rms_norm.cuh"
+
+#include <algorithm>
+#include <cmath>
+
+using host::fail;
+using host::guarded;
+using host::launched;
+
+extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_context **out)
+{
+    if (!out)
+        return fail(nullptr, "missing context output", 1);
+    *out = nullptr;
+    host::DeviceScope scope(device);
+    if (scope.status != cudaSuccess)
+        return fail(nullptr, "activate device", scope.status);
+    auto *context = new (std::nothrow) camblas_cuda_context;
+    if (!context)
+        return fail(nullptr, "context allocation", 2);
+    context->device = device;
+    context->stream = static_cast<cudaStream_t>(stream);
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    int status = int(cudaStreamIsCapturing(context->stream, &capture));
+    const char *what = "stream capture status";
+    if (status == 0 && capture != cudaStreamCaptureStatusNone) {
+        what = "context creation during CUDA graph capture";
+        status = 1;
+    }
+    cudaDeviceProp properties{};
+    if (status == 0) {
+        what = "device properties";
+        status = int(cudaGetDeviceProperties(&properties, device));
+    }
+    if (status == 0 && properties.major != 10) {
+        what = "B200 build on a device that is not compute capability 10.x";
+        status = 1;
+    }
+    if (status == 0) {
+        context->sm_count = properties.multiProcessorCount;
+        what = "tensor map encoder lookup";
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        status = int(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault,
+                                             &query));
+        if (status == 0 && (query != cudaDriverEntryPointSuccess || entry == nullptr))
+            status = 1;
+        context->encode = reinterpret_cast<EncodeTiledFn>(entry);
+    }
+    if (status == 0) {
+        what = "status word allocation";
+        status = int(cudaMalloc(reinterpret_cast<void **>(&context->status), sizeof(unsigned)));
+    }
+    if (status == 0) {
+        what = "status word initialisation";
+        status = int(cudaMemsetAsync(context->status, 0, sizeof(unsigned), context->stream));
+    }
+    if (status == 0) {
+        what = "kernel attributes";
+        status = host::prepare_kernels() | fp8::prepare_kernels();
+    }
+    if (status != 0) {
+        cudaGetLastError();
+        int result = fail(nullptr, what, status);
+        char keep[256];
+        std::memcpy(keep, host::creation_error, sizeof(keep));
+        camblas_cuda_destroy(context);
+        std::memcpy(host::creation_error, keep, sizeof(keep));
+        return result;
+    }
+    *out = context;
+    return 0;
+}
+
+extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
+{
+    if (!context)
+        return 0;
+    host::DeviceScope scope(context->device);
+    if (scope.status != cudaSuccess)
+        return fail(context, "activate device for destruction", scope.status);
+    cudaError_t error = cudaStreamSynchronize(context->stream);
+    if (context->scratch)
+        cudaFree(context->scratch);
+    for (void *allocation : context->retired)
+        cudaFree(allocation);
+    if (context->status)
+        cudaFree(context->status);
+    delete context;
+    return error == cudaSuccess ? 0 : fail(nullptr, "stream completion during destruction", error);
+}
+
+extern "C" const char *camblas_cuda_error(const camblas_cuda_context *context)
+{
+    return context ? context->error : host::creation_error;
+}
+
+extern "C" int camblas_cuda_set_algorithm(camblas_cuda_context *context, int algorithm)
+{
+    if (!context || algorithm < CAMBLAS_CUDA_AUTO || algorithm > CAMBLAS_CUDA_STRASSEN_FOUR)
+        return fail(context, "invalid algorithm", 1);
+    context->algorithm = algorithm;
+    return 0;
+}
+
+extern "C" int camblas_cuda_force_kernel(camblas_cuda_context *context, int family)
+{
+    if (!context || family < 0 || family > 4)
+        return fail(context, "invalid kernel family", 1);
+    context->forced_family = family;
+    return 0;
+}
+
+extern "C" int camblas_cuda_stats(const camblas_cuda_context *context, uint64_t *counts, int length)
+{
+    if (!context || !counts || (length != 6 && length != 8))
+        return fail(nullptr, "invalid stats output", 1);
+    for (int i = 0; i < length; ++i)
+        counts[i] = context->counts[i].load(std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int camblas_cuda_reset_stats(camblas_cuda_context *context)
+{
+    if (!context)
+        return fail(nullptr, "missing context", 1);
+    for (auto &count : context->counts)
+        count.store(0, std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status)
+{
+    return guarded(context, [&] {
+        if (!status)
+            return fail(context, "missing status output", 1);
+        cudaError_t error = cudaMemcpyAsync(status, context->status, sizeof(unsigned),
+                                            cudaMemcpyDeviceToHost, context->stream);
+        if (error == cudaSuccess)
+            error = cudaMemsetAsync(context->status, 0, sizeof(unsigned), context->stream);
+        if (error == cudaSuccess)
+            error = cudaStreamSynchronize(context->stream);
+        return error == cudaSuccess ? 0 : fail(context, "device status read", error);
+    });
+}
+
+/* ---- BF16 GEMM ---- */
+
+extern "C" int camblas_cuda_bgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m,
+                                  int n, int k, float alpha, const void *a, int lda, const void *b,
+                                  int ldb, float beta, void *c, int ldc)
+{
+    return guarded(context, [&] {
+        bool na = trans_a == 'N' || trans_a == 'n', ta = trans_a == 'T' || trans_a == 't';
+        bool nb = trans_b == 'N' || trans_b == 'n', tb = trans_b == 'T' || trans_b == 't';
+        if ((!na && !ta) || (!nb && !tb) || m < 0 || n < 0 || k < 0 || lda < 1 || ldb < 1 ||
+            ldc < 1)
+            return fail(context, "invalid BF16 GEMM arguments", 1);
+        if (m == 0 || n == 0)
+            return 0;
+        if (!c || lda < std::max(1, na ? m : k) || ldb < std::max(1, nb ? k : n) || ldc < m)
+            return fail(context, "invalid BF16 pointer or leading dimension", 1);
+        auto *out = static_cast<__nv_bfloat16 *>(c);
+        if (alpha == 0 || k == 0) {
+            if (beta == 1)
+                return 0;
+            generic::scale_window<<<unsigned((size_t(m) * n + 255) / 256), 256, 0,
+                                    context->stream>>>(m, n, beta, out, ldc);
+            return launched(context, "scale BF16 output");
+        }
+        if (!a || !b || a == c || b == c)
+            return fail(context, "missing or aliased BF16 GEMM operand", 1);
+        host::Product x{};
+        x.ta = ta, x.tb = tb, x.m = m, x.n = n, x.k = k;
+        x.alpha = alpha, x.beta = beta;
+        x.a = static_cast<const __nv_bfloat16 *>(a), x.lda = lda;
+        x.b = static_cast<const __nv_bfloat16 *>(b), x.ldb = ldb;
+        x.c = out, x.ldc = ldc;
+        x.addend = out, x.ld_add = ldc;
+        x.cut0 = x.cut1 = m;
+        if (context->algorithm == CAMBLAS_CUDA_STRASSEN && strassen::eligible(context, x))
+            return strassen::run(context, x);
+        return host::run_product(context, x);
+    });
+}
+
+extern "C" int camblas_cuda_linear_bf16(camblas_cuda_context *context, int rows, int inner,
+                                        int outputs, const void *x, int ldx, const void *w, int ldw,
+                                        const void *bias, const void *residual, int ldr, void *out,
+                                        int ldo)
+{
+    return guarded(context, [&] {
+        if (rows < 0 || inner < 1 || outputs < 0 || ldx < inner || ldw < inner || ldo < outputs ||
+            (residual && ldr < outputs))
+            return fail(context, "invalid BF16 linear dimensions", 1);
+        if (rows == 0 || outputs == 0)
+            return 0;
+        if (!x || !w || !out || out == x || out == w)
+            return fail(context, "missing or aliased BF16 linear operand", 1);
+        host::Product p{};
+        p.ta = true, p.tb = false, p.m = outputs, p.n = rows, p.k = inner;
+        p.alpha = 1.f, p.beta = residual ? 1.f : 0.f;
+        p.a = static_cast<const __nv_bfloat16 *>(w), p.lda = ldw;
+        p.b = static_cast<const __nv_bfloat16 *>(x), p.ldb = ldx;
+        p.c = static_cast<__nv_bfloat16 *>(out), p.ldc = ldo;
+        p.addend = static_cast<const __nv_bfloat16 *>(residual), p.ld_add = ldr;
+        p.bias = static_cast<const __nv_bfloat16 *>(bias);
+        p.cut0 = p.cut1 = outputs;
+        return host::run_product(context, p);
+    });
+}
+
+extern "C" int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int inner,
+                                            int q_out, int k_out, int v_out, const void *x, int ldx,
+                                            const void *w, int ldw, void *q, int ldq, void *k,
+                                            int ldk, void *v, int ldv)
+{
+    return guarded(context, [&] {
+        if (rows < 0 || inner < 1 || q_out < 1 || k_out < 1 || v_out < 1 || ldx < inner ||
+            ldw < inner || ldq < q_out || ldk < k_out || ldv < v_out ||
+            long(q_out) + k_out + v_out > INT_MAX)
+            return fail(context, "invalid packed projection dimensions", 1);
+        if (rows == 0)
+            return 0;
+        if (!x || !w || !q || !k || !v || q == k || q == v || k == v)
+            return fail(context, "missing or aliased packed projection operand", 1);
+        host::Product p{};
+        p.ta = true, p.tb = false, p.m = q_out + k_out + v_out, p.n = rows, p.k = inner;
+        p.alpha = 1.f, p.beta = 0.f;
+        p.a = static_cast<const __nv_bfloat16 *>(w), p.lda = ldw;
+        p.b = static_cast<const __nv_bfloat16 *>(x), p.ldb = ldx;
+        p.c = static_cast<__nv_bfloat16 *>(q), p.ldc = ldq;
+        p.c1 = static_cast<__nv_bfloat16 *>(k), p.ldc1 = ldk;
+        p.c2 = static_cast<__nv_bfloat16 *>(v), p.ldc2 = ldv;
+        p.addend = nullptr, p.ld_add = 0;
+        p.cut0 = q_out, p.cut1 = q_out + k_out;
+        return host::run_product(context, p);
+    });
+}
+
+/* ---- RMS normalisation ---- */
+
+namespace
+{
+template <typename T, typename W, bool Add>
+int launch_rms_rows(camblas_cuda_context *context, int rows, int width, float epsilon,
+                    const void *input, const void *residual, const void *weight, void *added,
+                    void *output, bool round_before_weight, bool descending)
+{
+    constexpr uintptr_t mask = sizeof(T) * 4 - 1, weight_mask = sizeof(W) * 4 - 1;
+    bool vector = width % 4 == 0 && !(uintptr_t(input) & mask) && !(uintptr_t(output) & mask) &&
+                  !(uintptr_t(weight) & weight_mask) &&
+                  (!Add || (!(uintptr_t(residual) & mask) && !(uintptr_t(added) & mask)));
+    auto *in = static_cast<const T *>(input);
+    auto *res = static_cast<const T *>(residual);
+    auto *gamma = static_cast<const W *>(weight);
+    auto *sum = static_cast<T *>(added);
+    auto *out = static_cast<T *>(output);
+    if (vector)
+        rms::rms_row_kernel<T, W, Add, true><<<rows, rms::kRowThreads, 0, context->stream>>>(
+            width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+    else
+        rms::rms_row_kernel<T, W, Add, false><<<rows, rms::kRowThreads, 0, context->stream>>>(
+            width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+    return launched(context, Add ? "residual RMS normalisation" : "RMS normalisation");
+}
+
+bool decode_width(int width)
+{
+    return width >= 2048 && width <= 65536 && width % 4 == 0;
+}
+} // namespace
+
+extern "C" int camblas_cuda_rms_norm(camblas_cuda_context *context, int dtype, int rows, int width,
+                                     float epsilon, const void *input, const void *weight,
+                                     void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || rows < 0 || width < 0 || !std::isfinite(epsilon) ||
+            epsilon < 0)
+            return fail(context, "invalid RMS normalisation dimensions, dtype or epsilon", 1);
+        if (!rows || !width)
+            return 0;
+        if (!input || !weight || !output || output == weight)
+            return fail(context, "invalid RMS normalisation operands", 1);
+        if (rows == 1 && decode_width(width)) {
+            if (dtype == 0)
+                return launch_rms_rows<float, float, false>(context, 1, width, epsilon, input,
+                                                            nullptr, weight, nullptr, output, true,
+                                                            false);
+            return launch_rms_rows<__nv_bfloat16, __nv_bfloat16, false>(
+                context, 1, width, epsilon, input, nullptr, weight, nullptr, output, true, false);
+        }
+        int grid = std::min(rows, 65535);
+        if (dtype == 0)
+            rms::rms_rows_kernel<float><<<grid, 256, 0, context->stream>>>(
+                rows, width, epsilon, static_cast<const float *>(input),
+                static_cast<const float *>(weight), static_cast<float *>(output));
+        else
+            rms::rms_rows_kernel<__nv_bfloat16><<<grid, 256, 0, context->stream>>>(
+                rows, width, epsilon, static_cast<const __nv_bfloat16 *>(input),
+                static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(output));
+        return launched(context, "RMS normalisation");
+    });
+}
+
+extern "C" int camblas_cuda_rms_norm_decode(camblas_cuda_context *context, int dtype,
+                                            int weight_dtype, int width, float epsilon,
+                                            int round_before_weight, int descending,
+                                            const void *input, const void *weight, void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || (weight_dtype != 0 && weight_dtype != 2) ||
+            (dtype == 0 && weight_dtype != 0) || !decode_width(width) ||
+            (round_before_weight != 0 && round_before_weight != 1) ||
+            (descending != 0 && descending != 1) || !std::isfinite(epsilon) || epsilon < 0 ||
+            !input || !weight || !output || output == input || output == weight ||
+            (uintptr_t(input) % (dtype == 0 ? 4 : 2)) ||
+            (uintptr_t(weight) % (weight_dtype == 0 ? 4 : 2)) ||
+            (uintptr_t(output) % (dtype == 0 ? 4 : 2)))
+            return fail(context, "invalid decode RMS arguments", 1);
+        if (dtype == 0)
+            return launch_rms_rows<float, float, false>(context, 1, width, epsilon, input, nullptr,
+                                                        weight, nullptr, output,
+                                                        round_before_weight, descending);
+        if (weight_dtype == 0)
+            return launch_rms_rows<__nv_bfloat16, float, false>(context, 1, width, epsilon, input,
+                                                                nullptr, weight, nullptr, output,
+                                                                round_before_weight, descending);
+        return launch_rms_rows<__nv_bfloat16, __nv_bfloat16, false>(
+            context, 1, width, epsilon, input, nullptr, weight, nullptr, output,
+            round_before_weight, descending);
+    });
+}
+
+namespace
+{
+int add_rms(camblas_cuda_context *context, int dtype, int rows, int width, float epsilon,
+            const void *input, const void *residual, const void *weight, void *added, void *output)
+{
+    if (dtype == 0)
+        return launch_rms_rows<float, float, true>(context, rows, width, epsilon, input, residual,
+                                                   weight, added, output, true, false);
+    return launch_rms_rows<__nv_bfloat16, __nv_bfloat16, true>(
+        context, rows, width, epsilon, input, residual, weight, added, output, true, false);
+}
+
+bool add_rms_operands_bad(const void *input, const void *residual, const void *weight, void *added,
+                          void *output)
+{
+    return !input || !residual || !weight || !added || !output || added == output ||
+           added == input || added == residual || added == weight || output == input ||
+           output == residual || output == weight;
+}
+} // namespace
+
+extern "C" int camblas_cuda_add_rms_norm(camblas_cuda_context *context, int dtype, int width,
+                                         float epsilon, const void *input, const void *residual,
+                                         const void *weight, void *added, void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || !decode_width(width) || !std::isfinite(epsilon) ||
+            epsilon < 0 || add_rms_operands_bad(input, residual, weight, added, output))
+            return fail(context, "invalid residual RMS arguments", 1);
+        return add_rms(context, dtype, 1, width, epsilon, input, residual, weight, added, output);
+    });
+}
+
+extern "C" int camblas_cuda_add_rms_norm_rows(camblas_cuda_context *context, int dtype, int rows,
+                                              int width, float epsilon, const void *input,
+                                              const void *residual, const void *weight,
+                                              void *added, void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || rows < 0 || width < 4 || width > 65536 || width % 4 ||
+            !std::isfinite(epsilon) || epsilon < 0)
+            return fail(context, "invalid residual RMS rows arguments", 1);
+        if (rows == 0)
+            return 0;
+        if (add_rms_operands_bad(input, residual, weight, added, output))
+            return fail(context, "invalid residual RMS rows operands", 1);
+        return add_rms(context, dtype, rows, width, epsilon, input, residual, weight, added,
+                       output);
+    });
+}
+
+extern "C" int camblas_cuda_bfloat16_square(camblas_cuda_context *context, uint64_t count,
+                                            const void *input, float *output)
+{
+    return guarded(context, [&] {
+        if (!count)
+            return 0;
+        if (!input || !output || count > SIZE_MAX / sizeof(float))
+            return fail(context, "invalid BF16 square operands", 1);
+        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        rms::square_kernel<<<blocks, 256, 0, context->stream>>>(
+            count, static_cast<const __nv_bfloat16 *>(input), output);
+        return launched(context, "BF16 squares");
+    });
+}
+
+extern "C" int camblas_cuda_rms_scale(camblas_cuda_context *context, int dtype, uint64_t count,
+                                      int width, float epsilon, const void *input,
+                                      const void *weight, const float *means, void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || width < 0 || !std::isfinite(epsilon) || epsilon < 0)
+            return fail(context, "invalid RMS scale dimensions, dtype or epsilon", 1);
+        if (!count)
+            return 0;
+        if (!width || count % width || count > SIZE_MAX / sizeof(float) || !input || !weight ||
+            !means || !output || output == weight)
+            return fail(context, "invalid RMS scale operands", 1);
+        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        if (dtype == 0)
+            rms::scale_kernel<float><<<blocks, 256, 0, context->stream>>>(
+                count, width, epsilon, static_cast<const float *>(input),
+                static_cast<const float *>(weight), means, static_cast<float *>(output));
+        else
+            rms::scale_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
+                count, width, epsilon, static_cast<const __nv_bfloat16 *>(input),
+                static_cast<const __nv_bfloat16 *>(weight), means,
+                static_cast<__nv_bfloat16 *>(output));
+        return launched(context, "RMS scaling");
+    });
+}
+
+extern "C" int camblas_cuda_silu_multiply(camblas_cuda_context *context, int dtype, uint64_t count,
+                                          const void *gate, const void *up, void *output)
+{
+    return guarded(context, [&] {
+        if (dtype != 0 && dtype != 2)
+            return fail(context, "invalid SiLU multiply dtype", 1);
+        if (!count)
+            return 0;
+        if (!gate || !up || !output)
+            return fail(context, "missing SiLU multiply operand", 1);
+        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        if (dtype == 0)
+            rms::silu_multiply_kernel<float><<<blocks, 256, 0, context->stream>>>(
+                count, static_cast<const float *>(gate), static_cast<const float *>(up),
+                static_cast<float *>(output));
+        else
+            rms::silu_multiply_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
+                count, static_cast<const __nv_bfloat16 *>(gate),
+                static_cast<const __nv_bfloat16 *>(up), static_cast<__nv_bfloat16 *>(output));
+        return launched(context, "SiLU multiply");
+    });
+}
+
+extern "C" int camblas_cuda_swiglu(camblas_cuda_context *context, int dtype, uint64_t count,
+                                   int width, float limit, const void *gate, const void *up,
+                                   const float *routing, void *output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || width < 1 || !(limit >= 0) || !std::isfinite(limit) ||
+            count % uint64_t(width))
+            return fail(context, "invalid SwiGLU dimensions, dtype or limit", 1);
+        if (!count)
+            return 0;
+        if (!gate || !up || !output || static_cast<const void *>(routing) == output)
+            return fail(context, "invalid SwiGLU operands", 1);
+        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        if (dtype == 0)
+            rms::swiglu_kernel<float><<<blocks, 256, 0, context->stream>>>(
+                count, width, limit, static_cast<const float *>(gate),
+                static_cast<const float *>(up), routing, static_cast<float *>(output));
+        else
+            rms::swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
+                count, width, limit, static_cast<const __nv_bfloat16 *>(gate),
+                static_cast<const __nv_bfloat16 *>(up), routing,
+                static_cast<__nv_bfloat16 *>(output));
+        return launched(context, "SwiGLU");
+    });
+}
+
+/* ---- exported for link compatibility only ---- */
+
+extern "C" int camblas_cuda_sgemm(camblas_cuda_context *context, char, char, int, int, int, float,
+                                  const float *, int, const float *, int, float, float *, int)
+{
+    return host::unavailable(context, "camblas_cuda_sgemm");
+}
+extern "C" int camblas_cuda_dgemm(camblas_cuda_context *context, char, char, int, int, int, double,
+                                  const double *, int, const double *, int, double, double *, int)
+{
+    return host::unavailable(context, "camblas_cuda_dgemm");
+}
+extern "C" int camblas_cuda_affine(camblas_cuda_context *context, int, int, int, int, const void *,
+                                   const void *, const void *, int, void *)
+{
+    return host::unavailable(context, "camblas_cuda_affine");
+}
+extern "C" int camblas_cuda_mlp(camblas_cuda_context *context, int, int, int, int, int,
+                                const void *, const void *, const void *, const void *,
+                                const void *, void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_mlp");
+}
+extern "C" int camblas_cuda_attention(camblas_cuda_context *context, int, int, int, int, int,
+                                      double, const void *, const void *, const void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_attention");
+}
+extern "C" int camblas_cuda_mlp_backward(camblas_cuda_context *context, int, int, int, int, int,
+                                         const void *, const void *, const void *, const void *,
+                                         const void *, void *, void *, void *, void *, void *,
+                                         void *)
+{
+    return host::unavailable(context, "camblas_cuda_mlp_backward");
+}
+extern "C" int camblas_cuda_quantized_matmul(camblas_cuda_context *context, int, int, int, int, int,
+                                             const void *, const void *, const void *,
+                                             const void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_quantized_matmul");
+}
+extern "C" int camblas_cuda_grouped_quantized_matmul(camblas_cuda_context *context, int, int, int,
+                                                     int, int, int, int, const void *,
+                                                     const void *, const void *, const void *,
+                                                     const void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_grouped_quantized_matmul");
+}
+extern "C" int camblas_cuda_route_groups(camblas_cuda_context *context, int, int, int, int, int,
+                                         const void *, const void *, void *, void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_route_groups");
+}
+extern "C" int camblas_cuda_reduce_groups(camblas_cuda_context *context, int, int, int, int,
+                                          const void *, const void *, const void *, void *)
+{
+    return host::unavailable(context, "camblas_cuda_reduce_groups");
+}

@@ -1,0 +1,176 @@
+/*
+ * Context object behind the C ABI: device, stream, policy, scratch arena with
+ * the reference's capture rules, device status word, launch counters, error
+ * text. It holds no vendor-library handle.
+ */
+#pragma once
+
+#include "../../include/camblas_cuda.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <exception>
+#include <new>
+#include <vector>
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct camblas_cuda_context {
+    int device = 0;
+    int algorithm = CAMBLAS_CUDA_AUTO;
+    int forced_family = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    bool scratch_captured = false;
+    std::vector<void *> retired;
+    unsigned *status = nullptr; /* device word written by bounded waits that gave up */
+    EncodeTiledFn encode = nullptr;
+    std::atomic<uint64_t> counts[8] = {};
+    char error[256] = "";
+};
+
+namespace host
+{
+
+inline thread_local char creation_error[256] = "";
+
+/* Record "<what> failed (status <code>)" and turn the code into a negative
+ * status, as the reference does (backend.cu:81-86). */
+inline int fail(camblas_cuda_context *context, const char *what, int code)
+{
+    char *message = context ? context->error : creation_error;
+    std::snprintf(message, 256, "%s failed (status %d)", what, code);
+    return code > 0 ? -code : -1;
+}
+
+inline int unavailable(camblas_cuda_context *context, const char *name)
+{
+    char *message = context ? context->error : creation_error;
+    std::snprintf(message, 256, "%s is not provided by the B200 build", name);
+    return -1;
+}
+
+class DeviceScope
+{
+    int previous = -1;
+    bool changed = false;
+
+  public:
+    cudaError_t status;
+    explicit DeviceScope(int device) : status(cudaGetDevice(&previous))
+    {
+        if (status == cudaSuccess && previous != device) {
+            status = cudaSetDevice(device);
+            changed = status == cudaSuccess;
+        }
+    }
+    ~DeviceScope()
+    {
+        if (changed)
+            cudaSetDevice(previous);
+    }
+};
+
+/* Run one entry point on the context's device, restoring the caller's device
+ * and turning host exceptions into a status (reference: backend.cu:913-951). */
+template <typename Function> int guarded(camblas_cuda_context *context, Function function)
+{
+    if (!context)
+        return fail(nullptr, "missing context", 1);
+    DeviceScope scope(context->device);
+    if (scope.status != cudaSuccess)
+        return fail(context, "activate device", scope.status);
+    try {
+        return function();
+    } catch (const std::bad_alloc &) {
+        return fail(context, "host allocation", 2);
+    } catch (const std::exception &error) {
+        std::snprintf(context->error, sizeof(context->error), "host exception: %s", error.what());
+        return -1;
+    } catch (...) {
+        return fail(context, "unexpected host exception", 1);
+    }
+}
+
+inline int launched(camblas_cuda_context *context, const char *what)
+{
+    cudaError_t error = cudaGetLastError();
+    return error == cudaSuccess ? 0 : fail(context, what, error);
+}
+
+/* Make the arena at least `required` bytes. During stream capture growth is
+ * refused and the arena is marked as recorded; a recorded arena is retired, not
+ * freed, when it later grows, so replayed graphs keep valid addresses
+ * (reference: backend.cu:397-434). */
+inline int reserve_scratch(camblas_cuda_context *context, size_t required)
+{
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    cudaError_t error = cudaStreamIsCapturing(context->stream, &capture);
+    if (error != cudaSuccess)
+        return fail(context, "scratch capture status", error);
+    if (capture != cudaStreamCaptureStatusNone) {
+        if (required > context->scratch_bytes)
+            return fail(context, "warm up scratch storage before CUDA graph capture", 1);
+        context->scratch_captured = true;
+        return 0;
+    }
+    if (required <= context->scratch_bytes)
+        return 0;
+    error = cudaStreamSynchronize(context->stream);
+    if (error != cudaSuccess)
+        return fail(context, "scratch synchronisation", error);
+    size_t rounded = (required + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    void *replacement = nullptr;
+    error = cudaMalloc(&replacement, rounded);
+    if (error != cudaSuccess) {
+        cudaGetLastError();
+        return fail(context, "scratch allocation", error);
+    }
+    if (context->scratch_captured)
+        context->retired.push_back(context->scratch);
+    else if (context->scratch)
+        cudaFree(context->scratch);
+    context->scratch = replacement;
+    context->scratch_bytes = rounded;
+    context->scratch_captured = false;
+    return 0;
+}
+
+/* 2-D tensor map over a row-major [extent1][extent0] array of `element_bytes`
+ * elements with row pitch `pitch_bytes`, 128-byte swizzle. */
+inline bool encode_2d(camblas_cuda_context *context, CUtensorMap *map, CUtensorMapDataType type,
+                      int element_bytes, const void *base, uint64_t extent0, uint64_t extent1,
+                      uint64_t pitch_bytes, uint32_t box0, uint32_t box1)
+{
+    cuuint64_t dims[2] = {extent0, extent1};
+    /* A single row never uses the pitch; keep it legal (multiple of 16). */
+    if (extent1 == 1)
+        pitch_bytes = (extent0 * element_bytes + 15) & ~uint64_t(15);
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box0, box1};
+    cuuint32_t element_strides[2] = {1, 1};
+    (void)element_bytes;
+    CUresult result = context->encode(map, type, 2, const_cast<void *>(base), dims, strides, box,
+                                      element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return result == CUDA_SUCCESS;
+}
+
+inline bool aligned16(const void *pointer)
+{
+    return (reinterpret_cast<uintptr_t>(pointer) & 15) == 0;
+}
+
+} // namespace host

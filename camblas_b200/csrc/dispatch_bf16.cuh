@@ -1,0 +1,375 @@
+/*
+ * Host-side choice of the BF16 kernel family and launch geometry. The table is
+ * static: the same shape always gets the same kernel, tile and K split, so the
+ * first call is as fast as the hundredth and results are repeatable (the
+ * reference times up to twelve library candidates on first use,
+ * backend.cu:719-779).
+ *
+ * In BLAS terms C[m,n] (column-major) = op(A)[m,k] op(B)[k,n]. Written from
+ * the torch side, A is the weight [outputs,inner] ('T'), B the activations
+ * [tokens,inner] ('N'), and C the row-major [tokens,outputs] result. The
+ * kernels see a row-major D[n,m] with row pitch ldc:
+ *   family 3 (tcgen05)          P = op(B) rows (tokens), Q = op(A) rows (outputs)
+ *   family 4 (tcgen05, swapped) P = op(A) rows (outputs), Q = op(B) rows (tokens),
+ *                               D^T stored, optional split-K through scratch
+ *   family 2 (skinny)           up to four tokens, CUDA cores, split-K
+ *   family 1 (generic)          anything else
+ */
+#pragma once
+
+#include "context.cuh"
+#include "gemm_bf16_tcgen05.cuh"
+#include "gemm_generic.cuh"
+#include "gemv_skinny.cuh"
+
+namespace host
+{
+
+enum Family : int { kAuto = 0, kGeneric = 1, kSkinny = 2, kTensor = 3, kTensorSwapped = 4 };
+
+struct Product {
+    bool ta, tb;
+    int m, n, k;
+    float alpha, beta;
+    const __nv_bfloat16 *a, *b;
+    long long lda, ldb;
+    __nv_bfloat16 *c;
+    long long ldc;
+    const __nv_bfloat16 *addend; /* beta term, indexed like c */
+    long long ld_add;
+    const __nv_bfloat16 *bias; /* per BLAS row i (output feature), may be NULL */
+    /* packed projection: BLAS rows [0,cut0) -> c, [cut0,cut1) -> c1, [cut1,m) -> c2 */
+    int cut0, cut1;
+    __nv_bfloat16 *c1, *c2;
+    long long ldc1, ldc2;
+};
+
+template <int BN, int Stages, int Mode> int prepare_kernel()
+{
+    return int(cudaFuncSetAttribute(sm100::gemm_bf16_tcgen05<BN, Stages, Mode>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    sm100::GemmSmem<BN, Stages, Mode>::kTotal));
+}
+
+inline int prepare_kernels()
+{
+    int status = prepare_kernel<256, 4, sm100::kStoreRows>();
+    status |= prepare_kernel<128, 6, sm100::kStoreRows>();
+    status |= prepare_kernel<64, 8, sm100::kStoreRows>();
+    status |= prepare_kernel<16, 8, sm100::kStoreColumns>();
+    status |= prepare_kernel<32, 8, sm100::kStoreColumns>();
+    status |= prepare_kernel<64, 8, sm100::kStoreColumns>();
+    status |= prepare_kernel<16, 8, sm100::kStorePartial>();
+    status |= prepare_kernel<32, 8, sm100::kStorePartial>();
+    status |= prepare_kernel<64, 8, sm100::kStorePartial>();
+    return status;
+}
+
+template <int BN, int Stages, int Mode>
+void launch_tensor(camblas_cuda_context *context, const CUtensorMap &p, const CUtensorMap &q,
+                   const CUtensorMap &d0, const CUtensorMap &d1, const CUtensorMap &d2,
+                   const sm100::GemmTask &task)
+{
+    int units = task.r_blocks * task.c_blocks * task.split;
+    int grid = units < context->sm_count ? units : context->sm_count;
+    sm100::gemm_bf16_tcgen05<BN, Stages, Mode>
+        <<<grid, sm100::kThreads, sm100::GemmSmem<BN, Stages, Mode>::kTotal, context->stream>>>(
+            p, q, d0, d1, d2, task);
+}
+
+inline bool tensor_operands_ok(const Product &x)
+{
+    /* both operands K-major with 16-byte aligned rows */
+    return x.ta && !x.tb && aligned16(x.a) && aligned16(x.b) && x.lda % 8 == 0 &&
+           (x.ldb % 8 == 0 || x.n == 1);
+}
+
+inline bool rows_store_ok(const Product &x)
+{
+    if (!aligned16(x.c) || x.ldc % 8 != 0)
+        return false;
+    if (x.cut0 < x.m)
+        return aligned16(x.c1) && aligned16(x.c2) && x.ldc1 % 8 == 0 && x.ldc2 % 8 == 0;
+    return true;
+}
+
+/* Smallest K split whose work units fill the SMs evenly; the split costs
+ * 8 bytes of scratch traffic per partial element, so smaller is better. */
+inline int choose_split(int tiles, int k_blocks, int sms)
+{
+    int limit = k_blocks / 8 < 1 ? 1 : (k_blocks / 8 > 32 ? 32 : k_blocks / 8);
+    int best = 1;
+    double best_score = 0;
+    for (int split = 1; split <= limit; ++split) {
+        long long units = 1ll * tiles * split;
+        long long waves = (units + sms - 1) / sms;
+        double fill = double(units) / double(waves * sms);
+        double score = fill - 0.01 * split;
+        if (score > best_score + 1e-9) {
+            best_score = score;
+            best = split;
+        }
+    }
+    return best;
+}
+
+inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
+{
+    sm100::GemmTask task{};
+    task.rows = x.n, task.cols = x.m, task.depth = x.k;
+    task.r_blocks = (x.n + 127) / 128;
+    task.k_blocks = (x.k + 63) / 64;
+    task.split = 1, task.k_blocks_per_split = task.k_blocks;
+    task.alpha = x.alpha, task.beta = x.beta;
+    task.out = x.c, task.ld_out = x.ldc;
+    task.addend = x.addend, task.ld_add = x.ld_add;
+    task.bias = x.bias;
+    task.status = context->status;
+    task.cut0 = x.cut0, task.cut1 = x.cut1;
+    bool packed = x.cut0 < x.m;
+    /* Tile width: compare the padded cost (waves x tile width) of 256- and
+     * 128-column tiles over the SMs. */
+    int sms = context->sm_count;
+    auto cost = [&](int bn) {
+        long long tiles = 1ll * task.r_blocks * ((x.m + bn - 1) / bn);
+        return ((tiles + sms - 1) / sms) * bn;
+    };
+    int bn = 256;
+    if (x.m <= 64)
+        bn = 64;
+    else if (x.m <= 128 || cost(128) * 1.15 < cost(256))
+        bn = 128;
+    if (packed && (x.cut0 % bn != 0 || x.cut1 % bn != 0)) {
+        bn = 128;
+        if (x.cut0 % bn != 0 || x.cut1 % bn != 0)
+            return fail(context, "packed projection widths must be multiples of 128", 1);
+    }
+    task.c_blocks = (x.m + bn - 1) / bn;
+    task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+
+    CUtensorMap p, q, d0, d1, d2;
+    bool ok = encode_2d(context, &p, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.b, x.k, x.n, x.ldb * 2,
+                        64, 128) &&
+              encode_2d(context, &q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.a, x.k, x.m, x.lda * 2,
+                        64, bn);
+    if (packed) {
+        ok = ok &&
+             encode_2d(context, &d0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.c, x.cut0, x.n,
+                       x.ldc * 2, 64, 32) &&
+             encode_2d(context, &d1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.c1, x.cut1 - x.cut0,
+                       x.n, x.ldc1 * 2, 64, 32) &&
+             encode_2d(context, &d2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.c2, x.m - x.cut1, x.n,
+                       x.ldc2 * 2, 64, 32);
+    } else {
+        ok = ok && encode_2d(context, &d0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.c, x.m, x.n,
+                             x.ldc * 2, 64, 32);
+        d1 = d0, d2 = d0;
+    }
+    if (!ok)
+        return fail(context, "tensor map encoding", 1);
+    if (bn == 256)
+        launch_tensor<256, 4, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
+    else if (bn == 128)
+        launch_tensor<128, 6, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
+    else
+        launch_tensor<64, 8, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
+    return launched(context, "tcgen05 BF16 GEMM");
+}
+
+inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
+{
+    sm100::GemmTask task{};
+    task.rows = x.m, task.cols = x.n, task.depth = x.k;
+    task.r_blocks = (x.m + 127) / 128;
+    int bn = x.n <= 16 ? 16 : (x.n <= 32 ? 32 : 64);
+    task.c_blocks = (x.n + bn - 1) / bn;
+    task.k_blocks = (x.k + 63) / 64;
+    task.split = choose_split(task.r_blocks * task.c_blocks, task.k_blocks, context->sm_count);
+    task.k_blocks_per_split = (task.k_blocks + task.split - 1) / task.split;
+    task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
+    task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    task.alpha = x.alpha, task.beta = x.beta;
+    task.out = x.c, task.ld_out = x.ldc;
+    task.addend = x.addend, task.ld_add = x.ld_add;
+    task.bias = x.bias;
+    task.status = context->status;
+    task.cut0 = task.cut1 = x.m;
+    long long plane = 1ll * task.r_blocks * 128;
+    if (task.split > 1) {
+        size_t bytes = size_t(task.split) * x.n * plane * sizeof(float);
+        int status = reserve_scratch(context, bytes);
+        if (status != 0)
+            return status;
+        task.partial = static_cast<float *>(context->scratch);
+    }
+    CUtensorMap p, q;
+    bool ok = encode_2d(context, &p, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.a, x.k, x.m, x.lda * 2,
+                        64, 128) &&
+              encode_2d(context, &q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.b, x.k, x.n, x.ldb * 2,
+                        64, bn);
+    if (!ok)
+        return fail(context, "tensor map encoding", 1);
+    if (task.split > 1) {
+        if (bn == 16)
+            launch_tensor<16, 8, sm100::kStorePartial>(context, p, q, p, p, p, task);
+        else if (bn == 32)
+            launch_tensor<32, 8, sm100::kStorePartial>(context, p, q, p, p, p, task);
+        else
+            launch_tensor<64, 8, sm100::kStorePartial>(context, p, q, p, p, p, task);
+        int status = launched(context, "tcgen05 split-K BF16 GEMM");
+        if (status != 0)
+            return status;
+        dim3 grid((x.m + 255) / 256, x.n);
+        sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(
+            x.m, x.n, task.split, plane, x.alpha, x.beta, task.partial, x.addend, x.ld_add, x.bias,
+            x.c, x.ldc);
+        return launched(context, "split-K reduction");
+    }
+    if (bn == 16)
+        launch_tensor<16, 8, sm100::kStoreColumns>(context, p, q, p, p, p, task);
+    else if (bn == 32)
+        launch_tensor<32, 8, sm100::kStoreColumns>(context, p, q, p, p, p, task);
+    else
+        launch_tensor<64, 8, sm100::kStoreColumns>(context, p, q, p, p, p, task);
+    return launched(context, "tcgen05 swapped BF16 GEMM");
+}
+
+template <int Tokens> int launch_skinny(camblas_cuda_context *context, skinny::Task &task)
+{
+    /* rows per warp: more rows amortise the token reads, fewer rows give more
+     * CTAs; keep at least two CTAs per SM when the matrix allows it */
+    int sms = context->sm_count;
+    int rows_per_warp = 4;
+    while (rows_per_warp > 1 &&
+           (task.outputs + rows_per_warp * skinny::kWarps - 1) / (rows_per_warp * skinny::kWarps) <
+               2 * sms)
+        rows_per_warp >>= 1;
+    int row_blocks =
+        (task.outputs + rows_per_warp * skinny::kWarps - 1) / (rows_per_warp * skinny::kWarps);
+    /* K split: slices of at most 4096 elements (the staged tokens must fit in
+     * shared memory) and enough CTAs for four per SM */
+    int split = (task.depth + 4095) / 4096;
+    while (1ll * row_blocks * split < 4ll * sms && task.depth / (split * 2) >= 512)
+        split *= 2;
+    int per = ((task.depth + split - 1) / split + 7) & ~7;
+    split = (task.depth + per - 1) / per;
+    task.split = split, task.depth_per_split = per;
+    if (split > 1) {
+        size_t bytes = size_t(split) * task.tokens * task.outputs * sizeof(float);
+        int status = reserve_scratch(context, bytes);
+        if (status != 0)
+            return status;
+        task.partial = static_cast<float *>(context->scratch);
+    }
+    size_t shared = size_t(Tokens) * per * sizeof(__nv_bfloat16);
+    dim3 grid(row_blocks, split);
+    if (rows_per_warp == 4)
+        skinny::skinny_gemv<Tokens, 4><<<grid, skinny::kThreads, shared, context->stream>>>(task);
+    else if (rows_per_warp == 2)
+        skinny::skinny_gemv<Tokens, 2><<<grid, skinny::kThreads, shared, context->stream>>>(task);
+    else
+        skinny::skinny_gemv<Tokens, 1><<<grid, skinny::kThreads, shared, context->stream>>>(task);
+    int status = launched(context, "skinny BF16 GEMV");
+    if (status != 0 || split == 1)
+        return status;
+    dim3 reduce_grid((task.outputs + 255) / 256, task.tokens);
+    skinny::skinny_reduce<<<reduce_grid, 256, 0, context->stream>>>(task);
+    return launched(context, "skinny split-K reduction");
+}
+
+inline int run_skinny(camblas_cuda_context *context, const Product &x)
+{
+    skinny::Task task{};
+    task.outputs = x.m, task.tokens = x.n, task.depth = x.k;
+    task.ldw = x.lda, task.ldx = x.ldb;
+    task.alpha = x.alpha, task.beta = x.beta;
+    task.w = x.a, task.x = x.b;
+    task.out = x.c, task.ld_out = x.ldc;
+    task.addend = x.addend, task.ld_add = x.ld_add;
+    task.bias = x.bias;
+    switch (x.n) {
+    case 1:
+        return launch_skinny<1>(context, task);
+    case 2:
+        return launch_skinny<2>(context, task);
+    case 3:
+    case 4:
+        return launch_skinny<4>(context, task);
+    }
+    return fail(context, "skinny kernel token count", 1);
+}
+
+inline int run_generic(camblas_cuda_context *context, const Product &x)
+{
+    generic::Task task{};
+    task.m = x.m, task.n = x.n, task.k = x.k;
+    task.ta = x.ta, task.tb = x.tb;
+    task.lda = x.lda, task.ldb = x.ldb, task.ldc = x.ldc;
+    task.alpha = x.alpha, task.beta = x.beta;
+    task.a = x.a, task.b = x.b, task.c = x.c;
+    task.bias = x.bias, task.addend = x.addend, task.ld_add = x.ld_add;
+    dim3 grid((x.m + 63) / 64, (x.n + 63) / 64);
+    if (grid.y > 65535)
+        return fail(context, "generic GEMM column count", 1);
+    generic::gemm_bf16_generic<<<grid, 256, 0, context->stream>>>(task);
+    return launched(context, "generic BF16 GEMM");
+}
+
+/* Route one product. Packed projections (cut0 < m) are split into three
+ * products unless the tensor-core row store takes them in one launch. */
+inline int run_product(camblas_cuda_context *context, const Product &x)
+{
+    bool packed = x.cut0 < x.m;
+    bool tensor = tensor_operands_ok(x);
+    bool skinny_ok = x.ta && !x.tb && aligned16(x.a) && x.lda % 8 == 0 && x.n <= 4;
+    int family = context->forced_family;
+    if (family == kAuto) {
+        if (skinny_ok)
+            family = kSkinny;
+        else if (tensor && x.n <= 64)
+            family = kTensorSwapped;
+        else if (tensor && rows_store_ok(x))
+            family = kTensor;
+        else
+            family = kGeneric;
+    } else {
+        bool possible = family == kGeneric || (family == kSkinny && skinny_ok) ||
+                        (family == kTensorSwapped && tensor) ||
+                        (family == kTensor && tensor && rows_store_ok(x));
+        if (!possible)
+            return fail(context, "forced kernel family cannot take these operands", 1);
+    }
+    if (packed && family != kTensor) {
+        Product part = x;
+        part.cut0 = part.cut1 = 0;
+        const int starts[4] = {0, x.cut0, x.cut1, x.m};
+        __nv_bfloat16 *outs[3] = {x.c, x.c1, x.c2};
+        const long long lds[3] = {x.ldc, x.ldc1, x.ldc2};
+        for (int i = 0; i < 3; ++i) {
+            part.m = starts[i + 1] - starts[i];
+            if (part.m == 0)
+                continue;
+            part.a = x.a + starts[i] * x.lda; /* 'T' operand: row block of the weight */
+            part.c = outs[i], part.ldc = lds[i];
+            part.cut0 = part.cut1 = part.m;
+            part.addend = part.c, part.ld_add = part.ldc;
+            int status = run_product(context, part);
+            if (status != 0)
+                return status;
+        }
+        return 0;
+    }
+    context->counts[context->algorithm == CAMBLAS_CUDA_LT ? 4 : 0]++;
+    switch (family) {
+    case kSkinny:
+        return run_skinny(context, x);
+    case kTensorSwapped:
+        return run_tensor_swapped(context, x);
+    case kTensor:
+        return run_tensor_rows(context, x);
+    default:
+        return run_generic(context, x);
+    }
+}
+
+} // namespace host

@@ -1,0 +1,408 @@
+/*
+ * BF16 GEMM on the fifth-generation tensor cores: D[R,C] = P[R,K] . Q[C,K]^T
+ * with FP32 accumulation in tensor memory.
+ *
+ * One persistent CTA per SM, six warps with fixed roles:
+ *   warp 0      TMA producer: streams 128 x 64 tiles of P and BN x 64 tiles of Q
+ *               into a ring of 128-byte-swizzled shared-memory stages.
+ *   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16)
+ *               four times per stage and commits the stage back to the producer;
+ *               accumulators alternate between two TMEM buffers so the epilogue
+ *               of one tile overlaps the main loop of the next.
+ *   warps 2-5   epilogue: tcgen05.ld of the accumulator quarter the warp owns,
+ *               alpha/beta/bias/addend in FP32, one rounding to BF16, then
+ *                 kStoreRows     swizzled staging + TMA store (row-major D),
+ *                 kStoreColumns  lane-contiguous stores of D^T (operands swapped:
+ *                                P = weights, Q = tokens, for few tokens),
+ *                 kStorePartial  FP32 partial sums of one K split into scratch.
+ * Every barrier wait is bounded; a wait that gives up records its role in the
+ * status word, raises a CTA-wide abort flag and all roles drain and return.
+ */
+#pragma once
+
+#include "sm100_primitives.cuh"
+
+namespace sm100
+{
+
+enum StoreMode : int { kStoreRows = 0, kStoreColumns = 1, kStorePartial = 2 };
+
+struct GemmTask {
+    int rows, cols, depth;         /* R, C, K */
+    int r_blocks, c_blocks;        /* tiles along R (128) and C (BN) */
+    int k_blocks;                  /* ceil(K / 64) */
+    int split, k_blocks_per_split; /* K partition (1 = whole K per tile) */
+    int panel;                     /* row blocks per rasterisation panel */
+    float alpha, beta;
+    __nv_bfloat16 *out;
+    long long ld_out;
+    const __nv_bfloat16 *addend; /* indexed like out; read only when beta != 0 */
+    long long ld_add;
+    const __nv_bfloat16 *bias; /* per column (kStoreRows) or per row (kStoreColumns) */
+    float *partial;            /* kStorePartial: [split][cols][r_blocks*128] */
+    unsigned *status;
+    /* Optional second and third outputs for a packed projection: columns
+     * [0,cut0) go to out, [cut0,cut1) to out1, [cut1,cols) to out2. cut0 and
+     * cut1 are multiples of BN; cut0 == cols disables the feature. */
+    int cut0, cut1;
+};
+
+constexpr int kBlockR = 128;
+constexpr int kBlockK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kStagingBytes = 4 * 2 * 4096; /* 4 warps x 2 buffers x (32 rows x 128 B) */
+
+template <int BN, int Stages, int Mode> struct GemmSmem {
+    static constexpr int kPBytes = kBlockR * kBlockK * 2;
+    static constexpr int kQBytes = BN * kBlockK * 2;
+    static constexpr int kStageBytes = kPBytes + kQBytes;
+    static constexpr int kStaging = Mode == kStoreRows ? kStagingBytes : 0;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = Stages * kStageBytes + kStaging + kBarrierBytes + 1024;
+};
+
+__device__ __forceinline__ void report(unsigned *status, volatile uint32_t *abort, unsigned role)
+{
+    if (!*abort) {
+        *abort = 1;
+        atomicCAS(status, 0u, role | (blockIdx.x << 4));
+    }
+}
+
+__device__ __forceinline__ void decode_unit(const GemmTask &task, int unit, int &rb, int &cb,
+                                            int &part)
+{
+    part = unit % task.split;
+    int tile = unit / task.split;
+    int per_panel = task.panel * task.c_blocks;
+    int panel = tile / per_panel;
+    int local = tile - panel * per_panel;
+    int height = min(task.panel, task.r_blocks - panel * task.panel);
+    cb = local / height;
+    rb = panel * task.panel + local - cb * height;
+}
+
+template <int BN, int Stages, int Mode>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_p,
+                      const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_d0,
+                      const __grid_constant__ CUtensorMap map_d1,
+                      const __grid_constant__ CUtensorMap map_d2, const GemmTask task)
+{
+    using Layout = GemmSmem<BN, Stages, Mode>;
+    constexpr uint32_t kTmemColumns = BN * 2 < 32 ? 32 : BN * 2;
+    static_assert((kTmemColumns & (kTmemColumns - 1)) == 0 && kTmemColumns <= 512, "TMEM size");
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
+    static_assert(Mode != kStoreRows || BN % 64 == 0, "row store works on 64-column slabs");
+
+    extern __shared__ uint8_t raw_smem[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *staging = smem + Stages * Layout::kStageBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(staging + Layout::kStaging);
+    uint64_t *empty = full + Stages;
+    uint64_t *tmem_full = empty + Stages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int units = task.r_blocks * task.c_blocks * task.split;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 4);
+        }
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+        if (Mode == kStoreRows)
+            prefetch_tensormap(&map_d0);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            /* ---- producer ---- */
+            const uint64_t keep = policy_evict_last();
+            const uint64_t stream = policy_evict_first();
+            /* The operand that is re-read by many tiles stays in L2; the one
+             * that is read once per panel is streamed. With few row blocks the
+             * column operand (weights) is the streamed one. */
+            const uint64_t policy_p = task.r_blocks <= task.panel ? keep : stream;
+            const uint64_t policy_q = task.r_blocks <= task.panel ? stream : keep;
+            uint32_t stage = 0, phase = 0;
+            uint32_t armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+                int rb, cb, part;
+                decode_unit(task, unit, rb, cb, part);
+                int kb0 = part * task.k_blocks_per_split;
+                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                        report(task.status, abort, kRoleProducer);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *p_tile = smem + stage * Layout::kStageBytes;
+                    uint8_t *q_tile = p_tile + Layout::kPBytes;
+                    mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
+                    tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockK, rb * kBlockR,
+                                     policy_p);
+                    tma_load_2d_hint(q_tile, &map_q, &full[stage], kb * kBlockK, cb * BN,
+                                     policy_q);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                /* Let copies already in flight land before the CTA retires. */
+                for (uint32_t s = 0; s < Stages; ++s)
+                    if (armed & (1u << s))
+                        for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                            if (mbar_try_wait(&full[s], (armed_parity >> s) & 1))
+                                break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            /* ---- MMA issuer ---- */
+            constexpr uint32_t idesc = make_idesc(1, kBlockR, BN, 0, 0);
+            uint32_t stage = 0, phase = 0;
+            uint32_t local = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x, ++local) {
+                int part = unit % task.split;
+                int kb0 = part * task.k_blocks_per_split;
+                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+                uint32_t buffer = local & 1, use = local >> 1;
+                if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                    report(task.status, abort, kRoleMmaTmemEmpty);
+                    break;
+                }
+                tcgen05_fence_after();
+                uint32_t tmem_d = tmem_base + buffer * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort)) {
+                        report(task.status, abort, kRoleMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    uint64_t desc_p = desc_kmajor_sw128(p_address);
+                    uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
+                        umma_f16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc,
+                                 (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok)
+                    umma_commit(&tmem_full[buffer]);
+            }
+        }
+    } else {
+        /* ---- epilogue ---- */
+        const int quarter = warp & 3;
+        uint8_t *slab = staging + (warp - 2) * 8192;
+        uint32_t local = 0;
+        uint32_t slab_use = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
+            int rb, cb, part;
+            decode_unit(task, unit, rb, cb, part);
+            uint32_t buffer = local & 1, use = local >> 1;
+            if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
+                report(task.status, abort, kRoleEpilogueFull);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + buffer * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int row = rb * kBlockR + quarter * 32 + lane;
+            const int col0 = cb * BN;
+
+            if constexpr (Mode == kStoreRows) {
+                const CUtensorMap *map_d = &map_d0;
+                __nv_bfloat16 *out = task.out;
+                const __nv_bfloat16 *addend = task.addend;
+                int col_shift = 0;
+                if (col0 >= task.cut0) {
+                    bool third = col0 >= task.cut1;
+                    map_d = third ? &map_d2 : &map_d1;
+                    col_shift = third ? task.cut1 : task.cut0;
+                }
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN / 64; ++chunk) {
+                    uint32_t acc[2][32];
+                    tmem_ld_32x32(taddr + chunk * 64, acc[0]);
+                    tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+                    tmem_ld_wait();
+                    if (chunk == BN / 64 - 1) {
+                        /* accumulator fully read: hand the TMEM buffer back */
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&tmem_empty[buffer]);
+                    }
+                    uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
+                    /* the TMA store that last read this buffer must be done */
+                    if (lane == 0)
+                        tma_store_wait_read<1>();
+                    __syncwarp();
+                    const int cbase = col0 + chunk * 64;
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            v[i] = task.alpha *
+                                   __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
+                        const int c = cbase + piece * 8;
+                        if (task.bias != nullptr) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (c + i < task.cols)
+                                    v[i] += __bfloat162float(task.bias[c + i]);
+                        }
+                        if (task.beta != 0.f && row < task.rows) {
+                            const __nv_bfloat16 *source =
+                                addend + static_cast<long long>(row) * task.ld_add + c;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (c + i < task.cols)
+                                    v[i] = fmaf(task.beta, __bfloat162float(source[i]), v[i]);
+                        }
+                        uint4 packed;
+                        packed.x = pack_bf16(v[0], v[1]);
+                        packed.y = pack_bf16(v[2], v[3]);
+                        packed.z = pack_bf16(v[4], v[5]);
+                        packed.w = pack_bf16(v[6], v[7]);
+                        *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 +
+                                                   ((piece ^ (lane & 7)) << 4)) = packed;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(map_d, buffer_smem, cbase - col_shift,
+                                     rb * kBlockR + quarter * 32);
+                        tma_store_commit();
+                    }
+                    ++slab_use;
+                }
+                (void)out;
+            } else {
+                /* Operands are swapped: this thread owns output feature `row`,
+                 * the registers run over tokens col0 + i. */
+                constexpr int kPiece = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN / kPiece; ++chunk) {
+                    uint32_t acc[kPiece];
+                    if constexpr (kPiece == 32)
+                        tmem_ld_32x32(taddr + chunk * kPiece, acc);
+                    else
+                        tmem_ld_32x16(taddr + chunk * kPiece, acc);
+                    tmem_ld_wait();
+                    if (chunk == BN / kPiece - 1) {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&tmem_empty[buffer]);
+                    }
+                    const int cbase = col0 + chunk * kPiece;
+                    if constexpr (Mode == kStorePartial) {
+                        const long long plane =
+                            static_cast<long long>(task.r_blocks) * kBlockR;
+                        float *target = task.partial +
+                                        (static_cast<long long>(part) * task.cols + cbase) * plane +
+                                        row;
+#pragma unroll
+                        for (int i = 0; i < kPiece; ++i)
+                            if (cbase + i < task.cols)
+                                target[i * plane] = __uint_as_float(acc[i]);
+                    } else {
+                        if (row < task.rows) {
+                            float bias =
+                                task.bias != nullptr ? __bfloat162float(task.bias[row]) : 0.f;
+#pragma unroll
+                            for (int i = 0; i < kPiece; ++i) {
+                                if (cbase + i < task.cols) {
+                                    float v = task.alpha * __uint_as_float(acc[i]) + bias;
+                                    long long at = static_cast<long long>(cbase + i);
+                                    if (task.beta != 0.f)
+                                        v = fmaf(task.beta,
+                                                 __bfloat162float(
+                                                     task.addend[at * task.ld_add + row]),
+                                                 v);
+                                    task.out[at * task.ld_out + row] = __float2bfloat16_rn(v);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if constexpr (Mode == kStoreRows) {
+            if (lane == 0)
+                tma_store_wait_all<0>();
+            __syncwarp();
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+/* Ordered reduction of the K splits written by kStorePartial:
+ * out[c*ld_out + r] = rnd(alpha * sum_s partial[s][c][r] + beta*addend + bias[r]). */
+__global__ void gemm_split_reduce(int rows, int cols, int split, long long plane, float alpha,
+                                  float beta, const float *partial, const __nv_bfloat16 *addend,
+                                  long long ld_add, const __nv_bfloat16 *bias, __nv_bfloat16 *out,
+                                  long long ld_out)
+{
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    int c = blockIdx.y;
+    if (r >= rows)
+        return;
+    float sum = 0.f;
+    for (int s = 0; s < split; ++s)
+        sum += partial[(static_cast<long long>(s) * cols + c) * plane + r];
+    float v = alpha * sum;
+    if (bias != nullptr)
+        v += __bfloat162float(bias[r]);
+    if (beta != 0.f)
+        v = fmaf(beta, __bfloat162float(addend[c * ld_add + r]), v);
+    out[c * ld_out + r] = __float2bfloat16_rn(v);
+}
+
+} // namespace sm100

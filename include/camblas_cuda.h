@@ -1,0 +1,255 @@
+/*
+ * C ABI of libcamblas_cuda.so, B200 (sm_100a) build.
+ *
+ * Every function of the reference header include/camblas_cuda.h is declared
+ * here with the same name, argument list and status convention, so a caller
+ * compiled against the reference links against this library unchanged. Each
+ * declaration cites the reference declaration and implementation it stands in
+ * for. Entry points that are outside the BF16/FP8 GEMM path are exported but
+ * return -1 with a message naming the operation; nothing here falls back to a
+ * CPU or to a vendor GEMM library.
+ *
+ * Conventions shared by all entry points
+ *   status      0 on success, negative on failure; the text of the last
+ *               failure is camblas_cuda_error(context) (creation failures are
+ *               kept per host thread and read with a NULL context).
+ *   memory      all operand, output and workspace pointers are device memory
+ *               of the context's device, owned by the caller, and must stay
+ *               alive until the context stream has drained. Outputs never
+ *               alias inputs unless a function says otherwise.
+ *   execution   work is enqueued on the context stream and returns without
+ *               waiting. The calling thread's current device is restored.
+ *   threading   a context serves one host thread and one stream; it is not
+ *               usable after fork().
+ *   capture     scratch-using operations must be run once on the stream before
+ *               that stream is captured into a CUDA graph; growth of scratch is
+ *               refused during capture, and scratch addresses recorded by a
+ *               capture stay valid until camblas_cuda_destroy().
+ */
+#ifndef CAMBLAS_CUDA_H
+#define CAMBLAS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct camblas_cuda_context camblas_cuda_context;
+
+/* Multiplication policies; values match reference include/camblas_cuda.h:14-23.
+ * AUTO, CLASSICAL and LT all select the tcgen05 GEMM (LT has no separate
+ * library route here). STRASSEN applies one Strassen level to eligible BF16
+ * squares; the multi-level and SYMMETRIC values are accepted and treated as
+ * CLASSICAL for BF16, as the reference does (camblas_cuda.h:64-66). */
+enum camblas_cuda_algorithm {
+    CAMBLAS_CUDA_AUTO = 0,
+    CAMBLAS_CUDA_CLASSICAL = 1,
+    CAMBLAS_CUDA_STRASSEN = 2,
+    CAMBLAS_CUDA_LT = 3,
+    CAMBLAS_CUDA_SYMMETRIC = 4,
+    CAMBLAS_CUDA_STRASSEN_TWO = 5,
+    CAMBLAS_CUDA_STRASSEN_THREE = 6,
+    CAMBLAS_CUDA_STRASSEN_FOUR = 7
+};
+
+/* ---- context lifetime -------------------------------------------------- */
+
+/* Replaces camblas_cuda_create (camblas_cuda.h:39; backend.cu:954-1015).
+ * stream is a cudaStream_t passed as void* (NULL = legacy default stream).
+ * The context owns a scratch arena, a device status word and eight launch
+ * counters; it holds no vendor-library handle. Must not be called while the
+ * stream is being captured. */
+int camblas_cuda_create(int device, void *stream, camblas_cuda_context **out);
+/* Replaces camblas_cuda_destroy (camblas_cuda.h:40; backend.cu:1017-1042).
+ * Waits for the stream, then frees every allocation the context ever made.
+ * NULL is accepted. */
+int camblas_cuda_destroy(camblas_cuda_context *context);
+/* Replaces camblas_cuda_error (camblas_cuda.h:41; backend.cu:1044-1047). */
+const char *camblas_cuda_error(const camblas_cuda_context *context);
+/* Replaces camblas_cuda_set_algorithm (camblas_cuda.h:42; backend.cu:1049-1055). */
+int camblas_cuda_set_algorithm(camblas_cuda_context *context, int algorithm);
+/* Replace camblas_cuda_stats / reset_stats (camblas_cuda.h:211-215;
+ * backend.cu:1477-1493). Slots: 0 classical GEMM launches (tcgen05, skinny and
+ * generic kernels), 1 Strassen, 2 Gram (always 0), 3 affine (always 0), 4 LT
+ * policy launches, 5 guarded classical fall-backs, 6 attention (0), 7 MLP
+ * backward (0). length is 6 or 8. */
+int camblas_cuda_stats(const camblas_cuda_context *context, uint64_t *counts, int length);
+int camblas_cuda_reset_stats(camblas_cuda_context *context);
+
+/* ---- BF16 GEMM --------------------------------------------------------- */
+
+/* Replaces camblas_cuda_bgemm (camblas_cuda.h:67-72; backend.cu:1075-1084;
+ * bfloat16.cuh:11-57). C = alpha op(A) op(B) + beta C over column-major BF16
+ * storage with FP32 accumulation and FP32 scalars, one rounding to BF16.
+ * trans_* is 'N'/'n' or 'T'/'t'. m==0 or n==0 succeeds without touching memory.
+ * alpha==0 or k==0 scales C by beta without reading A or B (which may then be
+ * NULL); beta==0 overwrites C without reading it, so NaNs in C do not survive.
+ * lda/ldb/ldc must cover the stored rows; A==C or B==C is rejected. Elements
+ * of C beyond row m of each column are left untouched. */
+int camblas_cuda_bgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
+                       int k, float alpha, const void *a, int lda, const void *b, int ldb,
+                       float beta, void *c, int ldc);
+
+/* No counterpart in the reference ABI (its torch binding issues bgemm and a
+ * separate add, torch_bindings.cpp:244-270, and materialises addmm's bias,
+ * torch_backend.cuh:59-71). Row-major linear layer with the epilogue fused:
+ *   out[rows,outputs] = x[rows,inner] . w[outputs,inner]^T (+ bias[outputs])
+ *                       (+ residual[rows,outputs])
+ * ldx/ldw/ldo/ldr are row strides in elements; bias and residual may be NULL.
+ * out may equal residual; it must not overlap x or w. */
+int camblas_cuda_linear_bf16(camblas_cuda_context *context, int rows, int inner, int outputs,
+                             const void *x, int ldx, const void *w, int ldw, const void *bias,
+                             const void *residual, int ldr, void *out, int ldo);
+
+/* No counterpart in the reference ABI (qkv_linear_public runs three GEMMs,
+ * torch_bindings.cpp:725-736). One launch over a weight that stores the q, k
+ * and v projections as consecutive row blocks [q_out+k_out+v_out, inner]; the
+ * three results go to three distinct row-major outputs with their own row
+ * strides. */
+int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int inner, int q_out,
+                                 int k_out, int v_out, const void *x, int ldx, const void *w,
+                                 int ldw, void *q, int ldq, void *k, int ldk, void *v, int ldv);
+
+/* ---- residual add + RMS normalisation ---------------------------------- */
+
+/* Replaces camblas_cuda_rms_norm (camblas_cuda.h:171-175; backend.cu:1423-1440).
+ * dtype 0 FP32, 2 BF16. out = rnd(rnd(x * rsqrt(mean(x^2)+eps)) * weight). */
+int camblas_cuda_rms_norm(camblas_cuda_context *context, int dtype, int rows, int width,
+                          float epsilon, const void *input, const void *weight, void *output);
+/* Replaces camblas_cuda_rms_norm_decode (camblas_cuda.h:176-183;
+ * backend.cu:1363-1396): one row, width 2048..65536 divisible by four, with the
+ * 512-thread four-accumulator reduction order of inference_fusion.cuh:136-191. */
+int camblas_cuda_rms_norm_decode(camblas_cuda_context *context, int dtype, int weight_dtype,
+                                 int width, float epsilon, int round_before_weight, int descending,
+                                 const void *input, const void *weight, void *output);
+/* Replaces camblas_cuda_add_rms_norm (camblas_cuda.h:184-189; backend.cu:1398-1421):
+ * one row; added = rnd(input+residual); output = rnd(rnd(added*s)*weight). */
+int camblas_cuda_add_rms_norm(camblas_cuda_context *context, int dtype, int width, float epsilon,
+                              const void *input, const void *residual, const void *weight,
+                              void *added, void *output);
+/* No counterpart in the reference ABI (it handles one row per call and its
+ * torch binding falls back to separate add and RMS kernels for more rows,
+ * torch_bindings.cpp:686-690). Same arithmetic as camblas_cuda_add_rms_norm for
+ * rows >= 1 contiguous rows; width is a positive multiple of 8 up to 65536. */
+int camblas_cuda_add_rms_norm_rows(camblas_cuda_context *context, int dtype, int rows, int width,
+                                   float epsilon, const void *input, const void *residual,
+                                   const void *weight, void *added, void *output);
+/* Replace camblas_cuda_bfloat16_square / rms_scale (camblas_cuda.h:190-198;
+ * backend.cu:1442-1475). */
+int camblas_cuda_bfloat16_square(camblas_cuda_context *context, uint64_t count, const void *input,
+                                 float *output);
+int camblas_cuda_rms_scale(camblas_cuda_context *context, int dtype, uint64_t count, int width,
+                           float epsilon, const void *input, const void *weight, const float *means,
+                           void *output);
+
+/* ---- FP8 E4M3 w8a8 ------------------------------------------------------ */
+
+/* No counterpart in the reference ABI; the arithmetic is the quantiser of the
+ * reference's block-128 decode kernel (camblas/_hopper.py:82-98). For every
+ * 128-element group of each row: scale = max(amax,1e-10)/448 (FP32),
+ * q = e4m3_satfinite(clamp(x * (448/max(amax,1e-10)), -448, 448)).
+ * x is BF16 [rows,inner] with row stride ldx; q is E4M3 [rows,inner]
+ * contiguous; scale is FP32 [rows, inner/128] contiguous. inner % 128 == 0. */
+int camblas_cuda_fp8_quantize_rows(camblas_cuda_context *context, int rows, int inner,
+                                   const void *x, int ldx, void *q, float *scale);
+/* No counterpart in the reference ABI for rows > 1 (the reference's block-128
+ * product is single-token, camblas/_hopper.py:13-182). Row-major
+ *   out[rows,outputs] = sum over 128-deep K blocks g, in ascending g, of
+ *        fma(dot_g(q[r,:], w[o,:]), q_scale[r,g] * w_scale[o/128,g], acc)
+ * with E4M3 q [rows,inner], E4M3 w [outputs,inner], FP32 q_scale
+ * [rows,inner/128], FP32 w_scale [ceil(outputs/128), inner/128], BF16 out with
+ * row stride ldo, one rounding at the end. inner % 128 == 0; outputs % 8 == 0. */
+int camblas_cuda_fp8_block_gemm(camblas_cuda_context *context, int rows, int outputs, int inner,
+                                const void *q, const float *q_scale, const void *w,
+                                const float *w_scale, void *out, int ldo);
+
+/* Replace camblas_cuda_fp8_decode_supported / fp8_decode / fp8_workspace_size /
+ * fp8_linear (camblas_cuda.h:137-163; backend.cu:1193-1256; fp8_decode.cuh):
+ * single-token block-32 E4M3 product with FP32 scales and ordered FP32
+ * accumulation; fp8_linear quantises a BF16 token with power-of-two block-32
+ * scales first. inner is a multiple of 32 in [32,8192], outputs a positive
+ * multiple of 16. The workspace query always returns 0 in this build. */
+int camblas_cuda_fp8_decode_supported(const camblas_cuda_context *context);
+int camblas_cuda_fp8_decode(camblas_cuda_context *context, int outputs, int inner,
+                            const void *input, const float *input_scale, const void *weight,
+                            const float *weight_scale, int input_scale_stride,
+                            int weight_scale_row_stride, int weight_scale_column_stride,
+                            void *workspace, size_t workspace_bytes, void *output);
+size_t camblas_cuda_fp8_workspace_size(int quantise, int outputs, int inner);
+int camblas_cuda_fp8_linear(camblas_cuda_context *context, int outputs, int inner,
+                            const void *input, const void *weight, const float *weight_scale,
+                            int weight_scale_row_stride, int weight_scale_column_stride,
+                            void *workspace, size_t workspace_bytes, void *output);
+
+/* ---- elementwise --------------------------------------------------------- */
+
+/* Replace camblas_cuda_silu_multiply / swiglu (camblas_cuda.h:107-121;
+ * inference_fusion.cuh:19-51). dtype 0 FP32, 2 BF16. */
+int camblas_cuda_silu_multiply(camblas_cuda_context *context, int dtype, uint64_t count,
+                               const void *gate, const void *up, void *output);
+int camblas_cuda_swiglu(camblas_cuda_context *context, int dtype, uint64_t count, int width,
+                        float limit, const void *gate, const void *up, const float *routing,
+                        void *output);
+
+/* ---- diagnostics ---------------------------------------------------------- */
+
+/* No counterpart in the reference ABI. Copies the device status word of the
+ * context to *status after waiting for the stream: 0 when every bounded wait
+ * inside the pipelined kernels completed; otherwise a code naming the wait that
+ * gave up (role in bits 0-3, CTA index above). Clears the word. */
+int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status);
+/* No counterpart in the reference ABI. Chooses the BF16 kernel family for the
+ * next calls on this context: 0 automatic, 1 generic CUDA-core kernel,
+ * 2 skinny weight-streaming kernel, 3 tcgen05 kernel, 4 tcgen05 with swapped
+ * operands and split-K. A forced family that cannot take the operands fails
+ * with status -1 instead of silently using another one. For tests. */
+int camblas_cuda_force_kernel(camblas_cuda_context *context, int family);
+
+/* ---- exported for link compatibility; not on the BF16/FP8 GEMM path ------- */
+/* Each returns -1 and sets "<name> is not provided by the B200 build".
+ * Reference declarations: camblas_cuda.h:57-62 (sgemm/dgemm), :77-82 (affine,
+ * mlp), :87-89 (attention), :94-99 (mlp_backward), :131-135 (quantized_matmul),
+ * :171-176 (grouped_quantized_matmul), :183-185 (route_groups), :190-192
+ * (reduce_groups). */
+int camblas_cuda_sgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
+                       int k, float alpha, const float *a, int lda, const float *b, int ldb,
+                       float beta, float *c, int ldc);
+int camblas_cuda_dgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
+                       int k, double alpha, const double *a, int lda, const double *b, int ldb,
+                       double beta, double *c, int ldc);
+int camblas_cuda_affine(camblas_cuda_context *context, int dtype, int rows, int inner, int columns,
+                        const void *x, const void *weight, const void *bias, int relu,
+                        void *output);
+int camblas_cuda_mlp(camblas_cuda_context *context, int dtype, int rows, int inputs, int hidden,
+                     int outputs, const void *x, const void *w1, const void *b1, const void *w2,
+                     const void *b2, void *hidden_output, void *output);
+int camblas_cuda_attention(camblas_cuda_context *context, int dtype, int queries, int keys,
+                           int depth, int values, double scale, const void *q, const void *k,
+                           const void *v, void *output);
+int camblas_cuda_mlp_backward(camblas_cuda_context *context, int dtype, int rows, int inputs,
+                              int hidden, int outputs, const void *x, const void *w1,
+                              const void *w2, const void *hidden_output, const void *grad_output,
+                              void *grad_hidden, void *dx, void *dw1, void *db1, void *dw2,
+                              void *db2);
+int camblas_cuda_quantized_matmul(camblas_cuda_context *context, int packed, int rows, int outputs,
+                                  int inner, int activation_block, const void *input,
+                                  const void *input_scale, const void *weight,
+                                  const void *weight_scale, void *output);
+int camblas_cuda_grouped_quantized_matmul(camblas_cuda_context *context, int packed, int groups,
+                                          int weight_groups, int rows, int outputs, int inner,
+                                          int activation_block, const void *input,
+                                          const void *input_scale, const void *metadata,
+                                          const void *active, const void *counts, void *output);
+int camblas_cuda_route_groups(camblas_cuda_context *context, int tokens, int choices,
+                              int first_expert, int groups, int rows, const void *experts,
+                              const void *active, void *counts, void *slots, void *reverse);
+int camblas_cuda_reduce_groups(camblas_cuda_context *context, int tokens, int choices, int width,
+                               int grouped_rows, const void *experts, const void *reverse,
+                               const void *input, void *output);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
