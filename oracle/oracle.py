@@ -154,6 +154,62 @@ def reference_linear_f32(x, w):
     return y
 
 
+class _ReferenceContext(ct.Structure):
+    """``camblas_ctx_t`` of the reference (``include/camblas.h:63-69``)."""
+
+    _fields_ = [("num_threads", _I), ("reproducibility", _I), ("planner_mode", ct.c_char_p),
+                ("topo", _P), ("executor", _P)]
+
+
+class ReferencePool:
+    """The reference's pinned pthread pool driving its own ``camblas_sgemm``.
+
+    ``cblas_sgemm`` uses the default single-thread context; the native entry
+    point takes a context whose executor may be the reference's pool
+    (``include/camblas_pthread.h``, ``src/pthread_pool.c``), which the portable
+    kernel feeds with up to 256 row tiles of C (``src/scalar.c:456-461``).
+    """
+
+    def __init__(self, cpus=None):
+        import os
+
+        self.library = reference_lib()
+        if self.library is None:
+            raise RuntimeError("reference library not built")
+        cpus = sorted(os.sched_getaffinity(0)) if cpus is None else list(cpus)
+        self.cpus = cpus
+        self.library.camblas_pthread_pool_create.restype = _P
+        self.library.camblas_pthread_pool_create.argtypes = [_I, ct.POINTER(_I)]
+        self.library.camblas_pthread_pool_executor.restype = _P
+        self.library.camblas_pthread_pool_executor.argtypes = [_P]
+        self.library.camblas_pthread_pool_destroy.argtypes = [_P]
+        self.library.camblas_sgemm.argtypes = [ct.POINTER(_ReferenceContext), ct.c_char, ct.c_char,
+                                               _I, _I, _I, _F, _P, _I, _P, _I, _F, _P, _I]
+        self.pool = self.library.camblas_pthread_pool_create(len(cpus), (_I * len(cpus))(*cpus))
+        if not self.pool:
+            raise RuntimeError("reference pthread pool could not be created")
+        self.context = _ReferenceContext(len(cpus), 0, b"none", None,
+                                         self.library.camblas_pthread_pool_executor(self.pool))
+
+    def linear_f32(self, x, w):
+        """``x @ w.T`` in FP32: column-major C[outputs, rows] = w^T-view x, 'T','N'."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        rows, inner = x.shape
+        outputs = w.shape[0]
+        y = np.zeros((rows, outputs), dtype=np.float32)
+        status = self.library.camblas_sgemm(ct.byref(self.context), b"T", b"N", outputs, rows, inner,
+                                            1.0, _ptr(w), inner, _ptr(x), inner, 0.0, _ptr(y), outputs)
+        if status != 0:
+            raise RuntimeError("reference camblas_sgemm failed")
+        return y
+
+    def close(self):
+        if self.pool:
+            self.library.camblas_pthread_pool_destroy(self.pool)
+            self.pool = None
+
+
 # ---- RMS ------------------------------------------------------------------------
 
 def add_rms_norm_rows(x, residual, weight, epsilon):

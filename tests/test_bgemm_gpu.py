@@ -1,0 +1,284 @@
+"""BF16 GEMM parity: the CUDA kernels, called through the C ABI, against the CPU oracle.
+
+Tolerance: relative L2 error <= 1e-2 on BF16 outputs (BF16_TOLERANCE), the
+bound the benchmark definition states; known-answer and exact-integer cases are
+compared bit for bit. Shapes, padded leading dimensions with NaN canaries and
+the alpha/beta cases follow the reference's tests/test_bfloat16.py:54-205.
+"""
+
+import ctypes as ct
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from camblas_b200 import _kernels, _native
+from oracle import oracle
+from tests.helpers import (BF16_TOLERANCE, bits_to_tensor, error_text, normal_bits, pointer, raw,
+                           tensor_to_bits)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+NAN = 0x7FC0
+
+
+def padded(rng, rows, columns, ld):
+    """Column-major rows x columns matrix inside an ld x columns buffer, NaN padding."""
+    buffer = np.full((columns, ld), NAN, dtype=np.uint16)
+    buffer[:, :rows] = normal_bits(rng, (columns, rows))
+    return buffer  # buffer[j, i] is element (i, j)
+
+
+def run_bgemm(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, family="auto"):
+    da, db, dc = bits_to_tensor(a), bits_to_tensor(b), bits_to_tensor(c)
+    with _native.kernel_family(family):
+        status, context = raw("bgemm", ta.encode(), tb.encode(), m, n, k, alpha, pointer(da), lda,
+                              pointer(db), ldb, beta, pointer(dc), ldc)
+    assert status == 0, error_text(context)
+    assert context.device_status() == 0
+    return tensor_to_bits(dc)
+
+
+@pytest.mark.parametrize("ta,tb", [("N", "N"), ("N", "T"), ("T", "N"), ("T", "T")])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 3, 7), (64, 64, 64), (65, 129, 33), (130, 70, 257),
+                                   (257, 5, 130)])
+def test_transposes_padding_alpha_beta(rng, ta, tb, m, n, k):
+    lda = (m if ta == "N" else k) + 3
+    ldb = (k if tb == "N" else n) + 5
+    ldc = m + 2
+    a = padded(rng, m if ta == "N" else k, k if ta == "N" else m, lda)
+    b = padded(rng, k if tb == "N" else n, n if tb == "N" else k, ldb)
+    c = padded(rng, m, n, ldc)
+    for alpha, beta in ((1.0, 0.0), (0.5, -1.25)):
+        expected = c.copy()
+        expected[:, m:] = 0  # keep the oracle away from NaN padding it never touches anyway
+        oracle.bgemm(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, expected, ldc)
+        actual = run_bgemm(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc)
+        assert np.all(actual[:, m:] == NAN), "padding rows of C were written"
+        error = oracle.rel_l2(oracle.bf16_values(actual[:, :m]), oracle.bf16_values(expected[:, :m]))
+        assert error <= BF16_TOLERANCE, error
+
+
+FAMILY_SHAPES = {
+    "generic": [(40, 3, 72), (200, 130, 64)],
+    "skinny": [(256, 1, 2048), (100, 2, 1000), (512, 3, 4104), (96, 4, 8200)],
+    "tensor": [(256, 128, 64), (264, 130, 136), (520, 200, 264), (1024, 512, 1024), (72, 300, 128)],
+    "tensor_swapped": [(128, 16, 64), (136, 5, 72), (1000, 40, 1032), (4096, 8, 2048),
+                       (256, 64, 8192), (300, 70, 520)],
+}
+
+
+@pytest.mark.parametrize("family", list(FAMILY_SHAPES))
+def test_each_kernel_family(rng, family):
+    for m, n, k in FAMILY_SHAPES[family]:
+        w = normal_bits(rng, (m, k))  # 'T' operand: outputs x inner, row-major
+        x = normal_bits(rng, (n, k))  # 'N' operand: tokens x inner, row-major
+        c = normal_bits(rng, (n, m))
+        for alpha, beta in ((1.0, 0.0), (-0.5, 0.75)):
+            expected = c.copy()
+            oracle.bgemm("T", "N", m, n, k, alpha, w, k, x, k, beta, expected, m)
+            actual = run_bgemm("T", "N", m, n, k, alpha, w, k, x, k, beta, c, m, family)
+            error = oracle.rel_l2(oracle.bf16_values(actual), oracle.bf16_values(expected))
+            assert error <= BF16_TOLERANCE, (family, m, n, k, error)
+
+
+def test_forced_family_that_cannot_run_fails_loudly(rng):
+    w = normal_bits(rng, (64, 63))  # inner width 63: rows are not 16-byte aligned
+    x = normal_bits(rng, (16, 63))
+    c = np.zeros((16, 64), dtype=np.uint16)
+    dw, dx, dc = bits_to_tensor(w), bits_to_tensor(x), bits_to_tensor(c)
+    for family in ("tensor", "tensor_swapped", "skinny"):
+        with _native.kernel_family(family):
+            status, context = raw("bgemm", b"T", b"N", 64, 16, 63, 1.0, pointer(dw), 63, pointer(dx),
+                                  63, 0.0, pointer(dc), 64)
+        assert status < 0 and "forced kernel family" in error_text(context)
+    actual = run_bgemm("T", "N", 64, 16, 63, 1.0, w, 63, x, 63, 0.0, c, 64)  # automatic -> generic
+    expected = oracle.linear_bf16(x, w)
+    assert oracle.rel_l2(oracle.bf16_values(actual), oracle.bf16_values(expected)) <= BF16_TOLERANCE
+
+
+@pytest.mark.parametrize("family,n", [("skinny", 1), ("skinny", 4), ("tensor_swapped", 8),
+                                      ("tensor_swapped", 33), ("tensor", 128), ("tensor", 300),
+                                      ("generic", 9)])
+def test_exact_integer_products(family, n):
+    """Rank-2 integer operands make every output an exact small integer: any tile
+    boundary or K-tail mistake shows as a wrong integer, not as rounding noise
+    (the trick of the reference's tests/test_mlp_packing.py:120-224)."""
+    m, k = 392, 1096
+    i = np.arange(m)[:, None]
+    j = np.arange(n)[:, None]
+    l = np.arange(k)[None, :]
+    w = ((i % 3) * (l % 2) + ((i + 1) % 2) * ((l + 1) % 2) * ((l % 5) == 0)).astype(np.float32)
+    x = ((j % 2 + 1) * (l % 2) - ((j % 3) == 0) * ((l + 1) % 2) * ((l % 5) == 0)).astype(np.float32)
+    expected = x.astype(np.int64) @ w.astype(np.int64).T
+    assert np.abs(expected).max() < 2048 and np.abs(expected).max() > 100
+    keep = np.abs(expected) <= 256  # integers up to 256 are exact in BF16
+    actual = run_bgemm("T", "N", m, n, k, 1.0, oracle.bf16_bits(w), k, oracle.bf16_bits(x), k, 0.0,
+                       np.zeros((n, m), dtype=np.uint16), m, family)
+    values = oracle.bf16_values(actual)
+    assert np.array_equal(values[keep], expected[keep].astype(np.float32))
+    assert np.array_equal(actual, oracle.bf16_bits(expected.astype(np.float32)))
+
+
+def test_identity_and_fp32_accumulation_probe():
+    n = 192
+    identity = np.zeros((n, n), dtype=np.uint16)
+    identity[np.arange(n), np.arange(n)] = oracle.bf16_bits(np.float32(1.0))
+    rng = np.random.default_rng(5)
+    b = normal_bits(rng, (n, n))
+    for ta in "NT":
+        for family in ("auto", "generic"):
+            actual = run_bgemm(ta, "N", n, n, n, 1.0, identity, n, b, n, 0.0,
+                               np.zeros((n, n), dtype=np.uint16), n, family)
+            assert np.array_equal(actual, b)
+    k = 1024
+    a = np.zeros((8, k), dtype=np.float32)
+    a[:, [0, 500, 1023]] = [256.0, 1.0, -256.0]
+    ones = np.ones((16, k), dtype=np.float32)
+    for family, tokens in (("skinny", 1), ("tensor_swapped", 16), ("generic", 16)):
+        actual = run_bgemm("T", "N", 8, tokens, k, 1.0, oracle.bf16_bits(a), k,
+                           oracle.bf16_bits(ones[:tokens]), k, 0.0,
+                           np.zeros((tokens, 8), dtype=np.uint16), 8, family)
+        assert np.all(oracle.bf16_values(actual) == 1.0), family
+
+
+def test_alpha_zero_ignores_operands_and_beta_zero_overwrites_nan():
+    nan = bits_to_tensor(np.full((32, 32), NAN, dtype=np.uint16))
+    c = bits_to_tensor(np.full((32, 32), NAN, dtype=np.uint16))
+    status, context = raw("bgemm", b"N", b"N", 32, 32, 32, 0.0, pointer(nan), 32, pointer(nan), 32,
+                          0.0, pointer(c), 32)
+    assert status == 0, error_text(context)
+    assert np.all(tensor_to_bits(c) == 0)
+    c = bits_to_tensor(oracle.bf16_bits(np.full((32, 32), 2.0, dtype=np.float32)))
+    status, context = raw("bgemm", b"N", b"N", 32, 32, 32, 0.0, None, 32, None, 32, -0.75,
+                          pointer(c), 32)
+    assert status == 0, error_text(context)
+    assert np.all(oracle.bf16_values(tensor_to_bits(c)) == -1.5)
+    # k == 0 behaves the same; beta == 1 is a no-op
+    status, _ = raw("bgemm", b"T", b"N", 32, 32, 0, 1.0, None, 1, None, 1, 1.0, pointer(c), 32)
+    assert status == 0 and np.all(oracle.bf16_values(tensor_to_bits(c)) == -1.5)
+    # beta == 0 with a real product must not let NaNs in C through
+    rng = np.random.default_rng(9)
+    w, x = normal_bits(rng, (256, 128)), normal_bits(rng, (130, 128))
+    actual = run_bgemm("T", "N", 256, 130, 128, 1.0, w, 128, x, 128, 0.0,
+                       np.full((130, 256), NAN, dtype=np.uint16), 256)
+    assert not np.isnan(oracle.bf16_values(actual)).any()
+
+
+def test_argument_validation_and_error_text():
+    buffer = bits_to_tensor(np.zeros((64, 64), dtype=np.uint16))
+    other = bits_to_tensor(np.zeros((64, 64), dtype=np.uint16))
+    out = bits_to_tensor(np.zeros((64, 64), dtype=np.uint16))
+    p, q, c = pointer(buffer), pointer(other), pointer(out)
+    cases = [
+        ((b"X", b"N", 8, 8, 8, 1.0, p, 8, q, 8, 0.0, c, 8), "invalid BF16 GEMM arguments"),
+        ((b"N", b"N", -1, 8, 8, 1.0, p, 8, q, 8, 0.0, c, 8), "invalid BF16 GEMM arguments"),
+        ((b"N", b"N", 8, 8, 8, 1.0, p, 0, q, 8, 0.0, c, 8), "invalid BF16 GEMM arguments"),
+        ((b"N", b"N", 8, 8, 8, 1.0, p, 7, q, 8, 0.0, c, 8), "invalid BF16 pointer or leading dimension"),
+        ((b"T", b"T", 8, 8, 16, 1.0, p, 16, q, 7, 0.0, c, 8), "invalid BF16 pointer or leading dimension"),
+        ((b"N", b"N", 8, 8, 8, 1.0, p, 8, q, 8, 0.0, c, 7), "invalid BF16 pointer or leading dimension"),
+        ((b"N", b"N", 8, 8, 8, 1.0, p, 8, q, 8, 0.0, None, 8), "invalid BF16 pointer or leading dimension"),
+        ((b"N", b"N", 8, 8, 8, 1.0, None, 8, q, 8, 0.0, c, 8), "missing or aliased BF16 GEMM operand"),
+        ((b"N", b"N", 8, 8, 8, 1.0, c, 8, q, 8, 0.0, c, 8), "missing or aliased BF16 GEMM operand"),
+        ((b"N", b"N", 8, 8, 8, 1.0, p, 8, c, 8, 0.0, c, 8), "missing or aliased BF16 GEMM operand"),
+    ]
+    for arguments, message in cases:
+        status, context = raw("bgemm", *arguments)
+        assert status == -1 and message in error_text(context), (arguments, error_text(context))
+    # empty products succeed without looking at pointers; lower-case flags are accepted
+    assert raw("bgemm", b"n", b"t", 0, 8, 8, 1.0, None, 1, None, 8, 0.0, None, 1)[0] == 0
+    assert raw("bgemm", b"t", b"n", 8, 0, 8, 1.0, None, 8, None, 8, 0.0, None, 8)[0] == 0
+    library = _native.library()
+    context = _native.context(0)
+    assert library.camblas_cuda_set_algorithm(context.handle, 8) == -1
+    assert library.camblas_cuda_set_algorithm(context.handle, 3) == 0
+    assert library.camblas_cuda_set_algorithm(context.handle, 0) == 0
+
+
+def test_cold_entry_points_say_so():
+    context = _native.context(0)
+    library = _native.library()
+    status = library.camblas_cuda_sgemm(context.handle, b"N", b"N", 1, 1, 1, 1.0, None, 1, None, 1,
+                                        0.0, None, 1)
+    assert status == -1
+    assert error_text(context) == "camblas_cuda_sgemm is not provided by the B200 build"
+
+
+def test_counters_count_launches(rng):
+    context = _native.context(0)
+    before = _native.stats(0, reset=True)
+    assert set(before) == {"classical", "strassen", "gram", "affine", "lt", "guard_fallback",
+                           "attention", "backward"}
+    w, x = bits_to_tensor(normal_bits(rng, (64, 64))), bits_to_tensor(normal_bits(rng, (8, 64)))
+    _kernels.linear(x, w)
+    assert _native.stats(0)["classical"] == 1
+    with _native.algorithm("lt"):
+        _kernels.matmul(x, w.t())
+        assert _native.stats(0)["lt"] == 1
+    counts = (ct.c_uint64 * 6)()
+    assert _native.library().camblas_cuda_stats(context.handle, counts, 6) == 0
+    assert _native.library().camblas_cuda_stats(context.handle, counts, 7) == -1
+    assert _native.stats(0, reset=True)["classical"] == 1
+    assert _native.stats(0)["classical"] == 0
+
+
+def test_golden_vectors_through_the_abi():
+    data = np.load(GOLDEN / "gemm_small.npz")
+    for index in range(3):
+        x, w, y = data[f"x{index}"], data[f"w{index}"], data[f"y{index}"]
+        out = _kernels.linear(bits_to_tensor(x), bits_to_tensor(w))
+        assert oracle.rel_l2(out.float().cpu().numpy(), y) <= BF16_TOLERANCE
+    from tests.golden.make_golden import config1_inputs
+
+    data = np.load(GOLDEN / "c1_decode.npz")
+    x, w = config1_inputs(int(data["seed"]))
+    for family in ("auto", "skinny", "tensor_swapped", "generic"):
+        with _native.kernel_family(family):
+            out = _kernels.linear(bits_to_tensor(x), bits_to_tensor(w))
+        assert oracle.rel_l2(out.float().cpu().numpy(), data["y"]) <= BF16_TOLERANCE, family
+
+
+def test_fused_epilogue_and_packed_projection(rng):
+    for rows in (1, 3, 20, 150):
+        inner, outputs = 264, 392
+        x, w = normal_bits(rng, (rows, inner)), normal_bits(rng, (outputs, inner))
+        bias, residual = normal_bits(rng, (outputs,)), normal_bits(rng, (rows, outputs))
+        expected = oracle.linear_bf16(x, w, bias, residual)
+        out = _kernels.linear(bits_to_tensor(x), bits_to_tensor(w), bits_to_tensor(bias),
+                              bits_to_tensor(residual))
+        error = oracle.rel_l2(out.float().cpu().numpy(), oracle.bf16_values(expected))
+        assert error <= BF16_TOLERANCE, (rows, error)
+    for rows in (2, 24, 200):
+        inner, widths = 256, (512, 128, 128)
+        x, w = normal_bits(rng, (rows, inner)), normal_bits(rng, (sum(widths), inner))
+        expected = oracle.bf16_values(oracle.linear_bf16(x, w))
+        q, k, v = _kernels.qkv_linear(bits_to_tensor(x), bits_to_tensor(w), *widths)
+        assert len({q.data_ptr(), k.data_ptr(), v.data_ptr()}) == 3
+        packed = torch.cat([q, k, v], dim=1).float().cpu().numpy()
+        assert oracle.rel_l2(packed, expected) <= BF16_TOLERANCE, rows
+
+
+@pytest.mark.parametrize("tokens,outputs,inner", [(512, 10240, 8192), (512, 8192, 28672),
+                                                  (64, 8192, 28672), (1, 57344, 8192)])
+def test_full_size_properties(tokens, outputs, inner):
+    """Benchmark-sized shapes: too large for the CPU oracle in full, so check
+    (1) a sampled set of output features against the oracle, (2) exact scaling:
+    doubling the activations doubles every output bit for bit, (3) splitting the
+    weight by output rows gives the same bits as the whole product (tensor-core
+    row kernel only: the K split of the few-token kernels depends on the shape)."""
+    generator = torch.Generator(device="cuda").manual_seed(705539)
+    x = torch.randn(tokens, inner, device="cuda", generator=generator).bfloat16()
+    w = (torch.randn(outputs, inner, device="cuda", generator=generator) * 0.02).bfloat16()
+    y = _kernels.linear(x, w)
+    assert _native.context(0).device_status() == 0
+    sample = torch.randperm(outputs, device="cuda", generator=generator)[:8].sort().values
+    rows = min(tokens, 16)
+    expected = oracle.linear_bf16(tensor_to_bits(x[:rows]), tensor_to_bits(w[sample]))
+    actual = y[:rows][:, sample].float().cpu().numpy()
+    assert oracle.rel_l2(actual, oracle.bf16_values(expected)) <= BF16_TOLERANCE
+    assert torch.equal(_kernels.linear(x * 2, w), y * 2)
+    if tokens > 64:  # below that the K split depends on the output count
+        half = outputs // 2
+        assert torch.equal(_kernels.linear(x, w[:half]), y[:, :half])
+        assert torch.equal(_kernels.linear(x, w[half:]), y[:, half:])
