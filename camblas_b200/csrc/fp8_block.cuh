@@ -1,13 +1,682 @@
+/*
+ * FP8 E4M3 w8a8 kernels.
+ *
+ * 1. quantize_rows_kernel: BF16 rows -> E4M3 with one FP32 scale per 128
+ *    elements (amax/448), the activation-quantise prologue.
+ * 2. fp8_block_gemm: block-scaled GEMM on the tensor cores (tcgen05.mma
+ *    kind::f8f6f4, FP32 accumulation in TMEM). The scales are FP32 amax/448
+ *    values, one per 1x128 activation block and per 128x128 weight block, so
+ *    they cannot ride on the hardware's E8M0 block-scaled MMA. Instead every
+ *    128-deep K block is a fresh accumulation into one of two TMEM buffers and
+ *    the epilogue warps promote it into FP32 registers while the next block is
+ *    being multiplied: acc = fma(block, a_scale*w_scale, acc), blocks in
+ *    ascending K order - the recurrence of the reference's block-128 decode
+ *    kernel (camblas/_hopper.py:118-126, 168-182), applied to every row.
+ *    Store modes as in the BF16 kernel: token rows on TMEM lanes with a TMA
+ *    store, or operands swapped for up to 64 tokens, optionally with a K split
+ *    through FP32 scratch and an ordered reduction.
+ * 3. fp8_token_kernel: the reference ABI's single-token block-32 product
+ *    (src/cuda/fp8_decode.cuh:74-165) on CUDA cores: 16-byte weight loads,
+ *    per-block FP32 dot products, then sum = fma(rnd(dot*sw), sx, sum) in
+ *    ascending block order; optional power-of-two BF16->E4M3 quantiser first
+ *    (fp8_decode.cuh:60-72).
+ */
 #pragma once
+
 #include "context.cuh"
-namespace fp8 { inline int prepare_kernels() { return 0; } }
-namespace strassen {
-inline bool eligible(camblas_cuda_context *, const host::Product &) { return false; }
-inline int run(camblas_cuda_context *context, const host::Product &) { return host::fail(context, "strassen", 1); }
+#include "dispatch_bf16.cuh"
+#include "gemm_bf16_tcgen05.cuh"
+
+#include <algorithm>
+#include <cuda_fp8.h>
+
+namespace fp8
+{
+
+using sm100::GemmSmem;
+using sm100::kStoreColumns;
+using sm100::kStorePartial;
+using sm100::kStoreRows;
+
+/* ---- 1. activation quantiser ------------------------------------------------ */
+
+/* One warp per 128-element group; lane l owns elements 4l..4l+3. */
+__global__ void __launch_bounds__(256) quantize_rows_kernel(int rows, int inner, long long ldx,
+                                                            const __nv_bfloat16 *x, uint8_t *q,
+                                                            float *scale)
+{
+    const int groups = inner >> 7;
+    const long long total = static_cast<long long>(rows) * groups;
+    const int lane = threadIdx.x & 31;
+    for (long long group = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+         group < total; group += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+        const long long row = group / groups;
+        const int g = static_cast<int>(group - row * groups);
+        const __nv_bfloat16 *source = x + row * ldx + g * 128 + lane * 4;
+        uint2 packed = *reinterpret_cast<const uint2 *>(source);
+        float v[4] = {sm100::bf16_low(packed.x), sm100::bf16_high(packed.x),
+                      sm100::bf16_low(packed.y), sm100::bf16_high(packed.y)};
+        float local = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        /* non-negative floats order like their bit patterns */
+        float maximum = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(local)));
+        maximum = fmaxf(maximum, 1e-10f);
+        if (lane == 0)
+            scale[group] = __fmul_rn(maximum, 1.0f / 448.0f);
+        const float inverse = __fdiv_rn(448.0f, maximum);
+        uint32_t bytes = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float value = fminf(fmaxf(__fmul_rn(v[i], inverse), -448.f), 448.f);
+            bytes |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(value, __NV_SATFINITE, __NV_E4M3))
+                     << (8 * i);
+        }
+        *reinterpret_cast<uint32_t *>(q + row * inner + g * 128 + lane * 4) = bytes;
+    }
 }
-extern "C" int camblas_cuda_fp8_quantize_rows(camblas_cuda_context *context, int, int, const void *, int, void *, float *) { return host::unavailable(context, "camblas_cuda_fp8_quantize_rows"); }
-extern "C" int camblas_cuda_fp8_block_gemm(camblas_cuda_context *context, int, int, int, const void *, const float *, const void *, const float *, void *, int) { return host::unavailable(context, "camblas_cuda_fp8_block_gemm"); }
-extern "C" int camblas_cuda_fp8_decode_supported(const camblas_cuda_context *) { return 0; }
-extern "C" int camblas_cuda_fp8_decode(camblas_cuda_context *context, int, int, const void *, const float *, const void *, const float *, int, int, int, void *, size_t, void *) { return host::unavailable(context, "camblas_cuda_fp8_decode"); }
-extern "C" size_t camblas_cuda_fp8_workspace_size(int, int, int) { return 0; }
-extern "C" int camblas_cuda_fp8_linear(camblas_cuda_context *context, int, int, const void *, const void *, const float *, int, int, void *, size_t, void *) { return host::unavailable(context, "camblas_cuda_fp8_linear"); }
+
+/* ---- 2. block-scaled tensor-core GEMM ---------------------------------------- */
+
+struct BlockTask {
+    int rows, cols, depth;  /* P rows, Q rows, K (multiple of 128) */
+    int r_blocks, c_blocks; /* 128-row and BN-row tiles */
+    int k_blocks;           /* K / 128 */
+    int split, k_blocks_per_split;
+    int panel;
+    const float *p_scale, *q_scale; /* kStoreRows: P per row [rows][G], Q per band [ceil/128][G];
+                                       swapped modes: P per band, Q per row */
+    __nv_bfloat16 *out;
+    long long ld_out;
+    float *partial; /* kStorePartial: [split][cols][r_blocks*128] */
+    unsigned *status;
+};
+
+constexpr int kBlockDepth = 128; /* bytes = E4M3 elements per stage row */
+
+template <int BN, int Stages, int Mode>
+__global__ void __launch_bounds__(sm100::kThreads, 1)
+    fp8_block_gemm(const __grid_constant__ CUtensorMap map_p,
+                   const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_d, const BlockTask task)
+{
+    using namespace sm100;
+    using Layout = GemmSmem<BN, Stages, Mode>; /* 128 B rows: same byte layout as BF16 x 64 */
+    constexpr uint32_t kTmemColumns = BN * 2 < 32 ? 32 : BN * 2;
+    static_assert(Mode != kStoreRows || BN == 128, "row store: one 128-column weight band per tile");
+
+    extern __shared__ uint8_t raw_smem[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *staging = smem + Stages * Layout::kStageBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(staging + Layout::kStaging);
+    uint64_t *empty = full + Stages;
+    uint64_t *tmem_full = empty + Stages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int units = task.r_blocks * task.c_blocks * task.split;
+    const int groups = task.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 4);
+        }
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto decode = [&](int unit, int &rb, int &cb, int &part) {
+        part = unit % task.split;
+        int tile = unit / task.split;
+        int per_panel = task.panel * task.c_blocks;
+        int panel = tile / per_panel;
+        int local = tile - panel * per_panel;
+        int height = min(task.panel, task.r_blocks - panel * task.panel);
+        cb = local / height;
+        rb = panel * task.panel + local - cb * height;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint64_t keep = policy_evict_last(), stream = policy_evict_first();
+            const bool weights_are_q = Mode == kStoreRows;
+            const uint64_t policy_p = weights_are_q ? keep : stream;
+            const uint64_t policy_q = weights_are_q ? stream : keep;
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+                int rb, cb, part;
+                decode(unit, rb, cb, part);
+                int kb0 = part * task.k_blocks_per_split;
+                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                        report(task.status, abort, kRoleProducer);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *p_tile = smem + stage * Layout::kStageBytes;
+                    mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
+                    tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockDepth, rb * kBlockR,
+                                     policy_p);
+                    tma_load_2d_hint(p_tile + Layout::kPBytes, &map_q, &full[stage],
+                                     kb * kBlockDepth, cb * BN, policy_q);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok)
+                for (uint32_t s = 0; s < Stages; ++s)
+                    if (armed & (1u << s))
+                        for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                            if (mbar_try_wait(&full[s], (armed_parity >> s) & 1))
+                                break;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(0, kBlockR, BN, 0, 0); /* E4M3 x E4M3 */
+            uint32_t stage = 0, phase = 0, block = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+                int part = unit % task.split;
+                int kb0 = part * task.k_blocks_per_split;
+                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++block) {
+                    uint32_t buffer = block & 1, use = block >> 1;
+                    if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                        report(task.status, abort, kRoleMmaTmemEmpty);
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&full[stage], phase, abort)) {
+                        report(task.status, abort, kRoleMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    uint64_t desc_p = desc_kmajor_sw128(p_address);
+                    uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
+                    uint32_t tmem_d = tmem_base + buffer * BN;
+#pragma unroll
+                    for (int k = 0; k < kBlockDepth / 32; ++k) /* 32 E4M3 = 32 bytes per MMA */
+                        umma_f8(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, k > 0 ? 1u : 0u);
+                    umma_commit(&empty[stage]);
+                    umma_commit(&tmem_full[buffer]);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        uint8_t *slab = staging + (warp - 2) * 8192;
+        uint32_t block = 0, slab_use = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+            int rb, cb, part;
+            decode(unit, rb, cb, part);
+            const int kb0 = part * task.k_blocks_per_split;
+            const int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+            const int row = rb * kBlockR + quarter * 32 + lane;
+            const int col0 = cb * BN;
+            float acc[BN];
+#pragma unroll
+            for (int i = 0; i < BN; ++i)
+                acc[i] = 0.f;
+            /* scale sources: one value per thread (lane side) and one per tile or column */
+            const float *lane_scale;
+            if (Mode == kStoreRows)
+                lane_scale = task.p_scale + static_cast<long long>(min(row, task.rows - 1)) * groups;
+            else
+                lane_scale = task.p_scale + static_cast<long long>(rb) * groups;
+            for (int kb = kb0; kb < kb1; ++kb, ++block) {
+                const uint32_t buffer = block & 1, use = block >> 1;
+                const float own = lane_scale[kb];
+                float band = 1.f;
+                if (Mode == kStoreRows)
+                    band = task.q_scale[static_cast<long long>(cb) * groups + kb];
+                if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
+                    report(task.status, abort, kRoleEpilogueFull);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t taddr =
+                    tmem_base + buffer * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+                constexpr int kPiece = BN >= 32 ? 32 : 16;
+#pragma unroll
+                for (int chunk = 0; chunk < BN / kPiece; ++chunk) {
+                    uint32_t piece[kPiece];
+                    if constexpr (kPiece == 32)
+                        tmem_ld_32x32(taddr + chunk * kPiece, piece);
+                    else
+                        tmem_ld_32x16(taddr + chunk * kPiece, piece);
+                    tmem_ld_wait();
+                    if (chunk == BN / kPiece - 1) {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&tmem_empty[buffer]);
+                    }
+                    if constexpr (Mode == kStoreRows) {
+                        const float s = __fmul_rn(own, band);
+#pragma unroll
+                        for (int i = 0; i < kPiece; ++i)
+                            acc[chunk * kPiece + i] =
+                                fmaf(__uint_as_float(piece[i]), s, acc[chunk * kPiece + i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kPiece; ++i) {
+                            const int c = min(col0 + chunk * kPiece + i, task.cols - 1);
+                            const float s = __fmul_rn(
+                                task.q_scale[static_cast<long long>(c) * groups + kb], own);
+                            acc[chunk * kPiece + i] =
+                                fmaf(__uint_as_float(piece[i]), s, acc[chunk * kPiece + i]);
+                        }
+                    }
+                }
+            }
+            if (!ok)
+                break;
+            if constexpr (Mode == kStoreRows) {
+#pragma unroll
+                for (int chunk = 0; chunk < BN / 64; ++chunk) {
+                    uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
+                    if (lane == 0)
+                        tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece) {
+                        const float *v = acc + chunk * 64 + piece * 8;
+                        uint4 packed;
+                        packed.x = pack_bf16(v[0], v[1]);
+                        packed.y = pack_bf16(v[2], v[3]);
+                        packed.z = pack_bf16(v[4], v[5]);
+                        packed.w = pack_bf16(v[6], v[7]);
+                        *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 +
+                                                   ((piece ^ (lane & 7)) << 4)) = packed;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_d, buffer_smem, col0 + chunk * 64,
+                                     rb * kBlockR + quarter * 32);
+                        tma_store_commit();
+                    }
+                    ++slab_use;
+                }
+            } else if constexpr (Mode == kStorePartial) {
+                const long long plane = static_cast<long long>(task.r_blocks) * kBlockR;
+                float *target =
+                    task.partial + (static_cast<long long>(part) * task.cols + col0) * plane + row;
+#pragma unroll
+                for (int i = 0; i < BN; ++i)
+                    if (col0 + i < task.cols)
+                        target[i * plane] = acc[i];
+            } else {
+                if (row < task.rows) {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i)
+                        if (col0 + i < task.cols)
+                            task.out[static_cast<long long>(col0 + i) * task.ld_out + row] =
+                                __float2bfloat16_rn(acc[i]);
+                }
+            }
+        }
+        if constexpr (Mode == kStoreRows) {
+            if (lane == 0)
+                tma_store_wait_all<0>();
+            __syncwarp();
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+/* ---- 3. single token, block-32 scales (reference ABI) ------------------------- */
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte)
+{
+    __half_raw half = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half *>(&half));
+}
+
+/* Power-of-two block-32 quantiser of one BF16 token; one warp per block
+ * (arithmetic of fp8_decode.cuh:60-72). */
+__device__ __forceinline__ uint8_t quantise_pow2(float value, float &scale)
+{
+    unsigned magnitude = __float_as_uint(fmaxf(fabsf(value), 1.e-10f));
+    float maximum = __uint_as_float(__reduce_max_sync(0xffffffffu, magnitude));
+    unsigned bits = __float_as_uint(__fmul_rn(maximum, 1.f / 448.f));
+    int exponent = int((bits >> 23) & 255) - 127 + int((bits & 0x7fffff) != 0);
+    scale = __uint_as_float(unsigned(exponent + 127) << 23);
+    float multiplier = __uint_as_float(unsigned(127 - exponent) << 23);
+    return __nv_cvt_float_to_fp8(fminf(__fmul_rn(value, multiplier), 448.f), __NV_SATFINITE,
+                                 __NV_E4M3);
+}
+
+/* One warp per output row. Lane l owns the 16 bytes [16l, 16l+16) of every
+ * 512-byte stretch of the row, so two neighbouring lanes hold one 32-element
+ * block; after each stretch the sixteen block sums are folded into the running
+ * sum in block order by every lane alike. */
+template <bool Quantise>
+__global__ void __launch_bounds__(256)
+    fp8_token_kernel(int outputs, int inner, const void *input, const float *sx, int sx_stride,
+                     const uint8_t *w, const float *sw, int sw_row, int sw_col,
+                     __nv_bfloat16 *out)
+{
+    extern __shared__ __align__(16) uint8_t shared[];
+    uint8_t *xq = shared;                                       /* [inner] */
+    float *xs = reinterpret_cast<float *>(shared + inner);      /* [inner/32] */
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = inner >> 5;
+    if (Quantise) {
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(input);
+        for (int g = warp; g < groups; g += 8) {
+            float scale;
+            uint8_t byte = quantise_pow2(__bfloat162float(x[g * 32 + lane]), scale);
+            xq[g * 32 + lane] = byte;
+            if (lane == 0)
+                xs[g] = scale;
+        }
+    } else {
+        const uint8_t *x = static_cast<const uint8_t *>(input);
+        for (int i = threadIdx.x; i < inner; i += 256)
+            xq[i] = x[i];
+        for (int g = threadIdx.x; g < groups; g += 256)
+            xs[g] = sx[static_cast<long long>(g) * sx_stride];
+    }
+    __syncthreads();
+    const int row = blockIdx.x * 8 + warp;
+    if (row >= outputs)
+        return;
+    const uint8_t *weights = w + static_cast<long long>(row) * inner;
+    const float *row_scale = sw + static_cast<long long>(row >> 5) * sw_row;
+    float sum = 0.f;
+    for (int base = 0; base < inner; base += 512) {
+        const int offset = base + lane * 16;
+        float dot = 0.f;
+        if (offset < inner) {
+            /* inner is a multiple of 32, so a lane's 16 bytes are all inside or all outside */
+            uint4 wv, xv = *reinterpret_cast<const uint4 *>(xq + offset);
+            if ((reinterpret_cast<uintptr_t>(weights + offset) & 15) == 0) {
+                wv = *reinterpret_cast<const uint4 *>(weights + offset);
+            } else {
+                const uint32_t *words = reinterpret_cast<const uint32_t *>(weights + offset);
+                wv = make_uint4(words[0], words[1], words[2], words[3]);
+            }
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    dot = fmaf(e4m3_to_float((ww[i] >> (8 * b)) & 255),
+                               e4m3_to_float((xw[i] >> (8 * b)) & 255), dot);
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        const int g = (base >> 5) + (lane >> 1);
+        float scaled = 0.f, xscale = 0.f;
+        if (g < groups) {
+            scaled = __fmul_rn(dot, row_scale[static_cast<long long>(g) * sw_col]);
+            xscale = xs[g];
+        }
+        const int live = min(16, groups - (base >> 5));
+        for (int j = 0; j < live; ++j)
+            sum = fmaf(__shfl_sync(0xffffffffu, scaled, 2 * j),
+                       __shfl_sync(0xffffffffu, xscale, 2 * j), sum);
+    }
+    if (lane == 0)
+        out[row] = __float2bfloat16_rn(sum);
+}
+
+/* ---- host side ----------------------------------------------------------------- */
+
+template <int BN, int Stages, int Mode> int prepare_kernel()
+{
+    return int(cudaFuncSetAttribute(fp8_block_gemm<BN, Stages, Mode>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    GemmSmem<BN, Stages, Mode>::kTotal));
+}
+
+inline int prepare_kernels()
+{
+    int status = prepare_kernel<128, 6, kStoreRows>();
+    status |= prepare_kernel<16, 8, kStoreColumns>();
+    status |= prepare_kernel<32, 8, kStoreColumns>();
+    status |= prepare_kernel<64, 8, kStoreColumns>();
+    status |= prepare_kernel<16, 8, kStorePartial>();
+    status |= prepare_kernel<32, 8, kStorePartial>();
+    status |= prepare_kernel<64, 8, kStorePartial>();
+    status |= int(cudaFuncSetAttribute(fp8_token_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 16384));
+    status |= int(cudaFuncSetAttribute(fp8_token_kernel<true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 16384));
+    return status;
+}
+
+template <int BN, int Stages, int Mode>
+void launch_block(camblas_cuda_context *context, const CUtensorMap &p, const CUtensorMap &q,
+                  const CUtensorMap &d, const BlockTask &task)
+{
+    int units = task.r_blocks * task.c_blocks * task.split;
+    int grid = units < context->sm_count ? units : context->sm_count;
+    fp8_block_gemm<BN, Stages, Mode>
+        <<<grid, sm100::kThreads, GemmSmem<BN, Stages, Mode>::kTotal, context->stream>>>(p, q, d,
+                                                                                         task);
+}
+
+inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int inner,
+                      const void *q, const float *q_scale, const void *w, const float *w_scale,
+                      void *out, int ldo)
+{
+    using host::encode_2d;
+    BlockTask task{};
+    task.depth = inner;
+    task.k_blocks = inner / 128;
+    task.out = static_cast<__nv_bfloat16 *>(out);
+    task.ld_out = ldo;
+    task.status = context->status;
+    CUtensorMap p, qm, d;
+    const auto type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    if (rows > 64) {
+        task.rows = rows, task.cols = outputs;
+        task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;
+        task.split = 1, task.k_blocks_per_split = task.k_blocks;
+        task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+        task.p_scale = q_scale, task.q_scale = w_scale;
+        bool ok = encode_2d(context, &p, type, 1, q, inner, rows, inner, 128, 128) &&
+                  encode_2d(context, &qm, type, 1, w, inner, outputs, inner, 128, 128) &&
+                  encode_2d(context, &d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, outputs, rows,
+                            size_t(ldo) * 2, 64, 32);
+        if (!ok)
+            return host::fail(context, "tensor map encoding", 1);
+        launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
+        return host::launched(context, "tcgen05 FP8 block GEMM");
+    }
+    /* few tokens: weights on the 128-row side, tokens on the narrow side */
+    task.rows = outputs, task.cols = rows;
+    task.r_blocks = (outputs + 127) / 128;
+    int bn = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
+    task.c_blocks = (rows + bn - 1) / bn;
+    task.split = host::choose_split(task.r_blocks * task.c_blocks, task.k_blocks * 2,
+                                    context->sm_count);
+    task.k_blocks_per_split = (task.k_blocks + task.split - 1) / task.split;
+    task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
+    task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    task.p_scale = w_scale, task.q_scale = q_scale;
+    long long plane = 1ll * task.r_blocks * 128;
+    if (task.split > 1) {
+        int status = host::reserve_scratch(context, size_t(task.split) * rows * plane * 4);
+        if (status != 0)
+            return status;
+        task.partial = static_cast<float *>(context->scratch);
+    }
+    bool ok = encode_2d(context, &p, type, 1, w, inner, outputs, inner, 128, 128) &&
+              encode_2d(context, &qm, type, 1, q, inner, rows, inner, 128, bn);
+    if (!ok)
+        return host::fail(context, "tensor map encoding", 1);
+    if (task.split > 1) {
+        if (bn == 16)
+            launch_block<16, 8, kStorePartial>(context, p, qm, p, task);
+        else if (bn == 32)
+            launch_block<32, 8, kStorePartial>(context, p, qm, p, task);
+        else
+            launch_block<64, 8, kStorePartial>(context, p, qm, p, task);
+        int status = host::launched(context, "tcgen05 FP8 split-K block GEMM");
+        if (status != 0)
+            return status;
+        dim3 grid((outputs + 255) / 256, rows);
+        sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(
+            outputs, rows, task.split, plane, 1.f, 0.f, task.partial, nullptr, 0, nullptr,
+            task.out, ldo);
+        return host::launched(context, "FP8 split-K reduction");
+    }
+    if (bn == 16)
+        launch_block<16, 8, kStoreColumns>(context, p, qm, p, task);
+    else if (bn == 32)
+        launch_block<32, 8, kStoreColumns>(context, p, qm, p, task);
+    else
+        launch_block<64, 8, kStoreColumns>(context, p, qm, p, task);
+    return host::launched(context, "tcgen05 FP8 swapped block GEMM");
+}
+
+} // namespace fp8
+
+/* ---- extern "C" ------------------------------------------------------------------ */
+
+extern "C" int camblas_cuda_fp8_quantize_rows(camblas_cuda_context *context, int rows, int inner,
+                                              const void *x, int ldx, void *q, float *scale)
+{
+    return host::guarded(context, [&] {
+        if (rows < 0 || inner < 128 || inner % 128 || ldx < inner || ldx % 4)
+            return host::fail(context, "invalid FP8 quantise dimensions", 1);
+        if (rows == 0)
+            return 0;
+        if (!x || !q || !scale || (uintptr_t(x) & 7) || (uintptr_t(q) & 3) || x == q)
+            return host::fail(context, "invalid FP8 quantise operands", 1);
+        long long groups = 1ll * rows * (inner / 128);
+        unsigned blocks = unsigned(std::min<long long>((groups + 7) / 8, 148 * 16));
+        fp8::quantize_rows_kernel<<<blocks, 256, 0, context->stream>>>(
+            rows, inner, ldx, static_cast<const __nv_bfloat16 *>(x), static_cast<uint8_t *>(q),
+            scale);
+        return host::launched(context, "FP8 row quantisation");
+    });
+}
+
+extern "C" int camblas_cuda_fp8_block_gemm(camblas_cuda_context *context, int rows, int outputs,
+                                           int inner, const void *q, const float *q_scale,
+                                           const void *w, const float *w_scale, void *out, int ldo)
+{
+    return host::guarded(context, [&] {
+        if (rows < 0 || outputs < 0 || inner < 128 || inner % 128 || ldo < outputs)
+            return host::fail(context, "invalid FP8 block GEMM dimensions", 1);
+        if (rows == 0 || outputs == 0)
+            return 0;
+        if (!q || !q_scale || !w || !w_scale || !out || out == q || out == w)
+            return host::fail(context, "missing or aliased FP8 block GEMM operand", 1);
+        if (!host::aligned16(q) || !host::aligned16(w) ||
+            (rows > 64 && (!host::aligned16(out) || ldo % 8 || outputs % 8)))
+            return host::fail(context, "FP8 block GEMM operands must be 16-byte aligned", 1);
+        context->counts[0]++;
+        return fp8::block_gemm(context, rows, outputs, inner, q, q_scale, w, w_scale, out, ldo);
+    });
+}
+
+extern "C" int camblas_cuda_fp8_decode_supported(const camblas_cuda_context *context)
+{
+    return context ? 1 : 0;
+}
+
+extern "C" size_t camblas_cuda_fp8_workspace_size(int, int, int)
+{
+    return 0;
+}
+
+namespace fp8
+{
+inline int token_arguments_bad(int outputs, int inner, const void *input, const void *weight,
+                               const float *weight_scale, int row_stride, int column_stride,
+                               const void *output)
+{
+    return outputs < 16 || outputs % 16 || inner < 32 || inner > 8192 || inner % 32 || !input ||
+           !weight || !weight_scale || !output || row_stride < 1 || column_stride < 1 ||
+           (uintptr_t(input) & 3) || (uintptr_t(weight) & 3) || (uintptr_t(weight_scale) & 3) ||
+           (uintptr_t(output) & 1) || output == input || output == weight ||
+           output == static_cast<const void *>(weight_scale);
+}
+} // namespace fp8
+
+extern "C" int camblas_cuda_fp8_decode(camblas_cuda_context *context, int outputs, int inner,
+                                       const void *input, const float *input_scale,
+                                       const void *weight, const float *weight_scale,
+                                       int input_scale_stride, int weight_scale_row_stride,
+                                       int weight_scale_column_stride, void *workspace,
+                                       size_t workspace_bytes, void *output)
+{
+    return host::guarded(context, [&] {
+        (void)workspace;
+        (void)workspace_bytes;
+        if (fp8::token_arguments_bad(outputs, inner, input, weight, weight_scale,
+                                     weight_scale_row_stride, weight_scale_column_stride, output) ||
+            !input_scale || input_scale_stride < 1 || (uintptr_t(input_scale) & 3))
+            return host::fail(context, "invalid FP8 decode arguments", 1);
+        size_t shared = size_t(inner) + size_t(inner / 32) * sizeof(float);
+        fp8::fp8_token_kernel<false><<<(outputs + 7) / 8, 256, shared, context->stream>>>(
+            outputs, inner, input, input_scale, input_scale_stride,
+            static_cast<const uint8_t *>(weight), weight_scale, weight_scale_row_stride,
+            weight_scale_column_stride, static_cast<__nv_bfloat16 *>(output));
+        return host::launched(context, "FP8 decode");
+    });
+}
+
+extern "C" int camblas_cuda_fp8_linear(camblas_cuda_context *context, int outputs, int inner,
+                                       const void *input, const void *weight,
+                                       const float *weight_scale, int weight_scale_row_stride,
+                                       int weight_scale_column_stride, void *workspace,
+                                       size_t workspace_bytes, void *output)
+{
+    return host::guarded(context, [&] {
+        (void)workspace;
+        (void)workspace_bytes;
+        if (fp8::token_arguments_bad(outputs, inner, input, weight, weight_scale,
+                                     weight_scale_row_stride, weight_scale_column_stride, output))
+            return host::fail(context, "invalid FP8 linear arguments", 1);
+        size_t shared = size_t(inner) + size_t(inner / 32) * sizeof(float);
+        fp8::fp8_token_kernel<true><<<(outputs + 7) / 8, 256, shared, context->stream>>>(
+            outputs, inner, input, nullptr, 1, static_cast<const uint8_t *>(weight), weight_scale,
+            weight_scale_row_stride, weight_scale_column_stride,
+            static_cast<__nv_bfloat16 *>(output));
+        return host::launched(context, "FP8 linear");
+    });
+}
+
+/* One-level Strassen for BF16 squares lives in strassen.cuh. */
+#include "strassen.cuh"
