@@ -67,6 +67,7 @@ _SIGNATURES = {
         _I,
     ),
     "linear_bf16": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P, _I], _I),
+    "linear_bf16_static": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _I], _I),
     "qkv_linear_bf16": ([_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I], _I),
     "rms_norm": ([_P, _I, _I, _I, _F, _P, _P, _P], _I),
     "rms_norm_decode": ([_P, _I, _I, _I, _F, _I, _I, _P, _P, _P], _I),

@@ -9,6 +9,7 @@
 #include "dispatch_bf16.cuh"
 #include "fp8_block.cuh"
 #include "rms_norm.cuh"
+#include "static_scratch.cuh"
 
 #include <algorithm>
 #include <cmath>

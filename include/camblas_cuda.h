@@ -112,6 +112,27 @@ int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int in
                                  int k_out, int v_out, const void *x, int ldx, const void *w,
                                  int ldw, void *q, int ldq, void *k, int ldk, void *v, int ldv);
 
+/* Has no counterpart in the reference. A linear layer for one to four token
+ * rows, out[rows,outputs] = x[rows,inner] . w[outputs,inner]^T (row strides
+ * ldx/ldw/ldo in elements, BF16, FP32 accumulation, one rounding), for callers
+ * that may not allocate device memory when they need the product: code that
+ * runs while its stream is under CUDA-graph capture, processes whose own
+ * memory pool owns the whole device and forbids later driver allocations, and
+ * latency-bound paths. It takes a cudaStream_t (as void*) instead of a context,
+ * runs on the calling thread's current device, and calls no allocator: the FP32
+ * partial sums of its K split live in a fixed 8 MiB array inside the library
+ * image (held by every GPU that loads the library until the process exits).
+ * A product whose partial sums (K splits x rows x outputs x 4 bytes) exceed
+ * 8 MiB is rejected with -1 and a message that names both sizes. Weight rows
+ * must be 16-byte aligned (w aligned, ldw a multiple of 8). The first call on
+ * each device looks up the array's device address; make that call before any
+ * stream capture. All calls on a device share the array: it needs no clearing
+ * (every partial is written before it is read), but two calls that overlap on
+ * the GPU race on it - keep them ordered. Failure text is read with
+ * camblas_cuda_error(NULL). */
+int camblas_cuda_linear_bf16_static(void *stream, int rows, int inner, int outputs, const void *x,
+                                    int ldx, const void *w, int ldw, void *out, int ldo);
+
 /* ---- residual add + RMS normalisation ---------------------------------- */
 
 /* Replaces camblas_cuda_rms_norm (camblas_cuda.h:171-175; backend.cu:1423-1440).
