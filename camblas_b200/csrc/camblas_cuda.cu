@@ -60,11 +60,21 @@ extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_contex
     }
     if (status == 0) {
         what = "status word allocation";
-        status = int(cudaMalloc(reinterpret_cast<void **>(&context->status), sizeof(unsigned)));
+        status = int(cudaMalloc(reinterpret_cast<void **>(&context->status), 2 * sizeof(unsigned)));
     }
     if (status == 0) {
         what = "status word initialisation";
-        status = int(cudaMemsetAsync(context->status, 0, sizeof(unsigned), context->stream));
+        status = int(cudaMemsetAsync(context->status, 0, 2 * sizeof(unsigned), context->stream));
+    }
+    if (status == 0) {
+        what = "guard counter allocation";
+        status = int(cudaHostAlloc(reinterpret_cast<void **>(&context->guard_hits),
+                                   sizeof(unsigned long long), cudaHostAllocMapped));
+        if (status == 0) {
+            *context->guard_hits = 0;
+            status = int(cudaHostGetDevicePointer(
+                reinterpret_cast<void **>(&context->guard_hits_device), context->guard_hits, 0));
+        }
     }
     if (status == 0) {
         what = "kernel attributes";
@@ -97,6 +107,8 @@ extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
         cudaFree(allocation);
     if (context->status)
         cudaFree(context->status);
+    if (context->guard_hits)
+        cudaFreeHost(context->guard_hits);
     delete context;
     return error == cudaSuccess ? 0 : fail(nullptr, "stream completion during destruction", error);
 }
@@ -128,6 +140,9 @@ extern "C" int camblas_cuda_stats(const camblas_cuda_context *context, uint64_t 
         return fail(nullptr, "invalid stats output", 1);
     for (int i = 0; i < length; ++i)
         counts[i] = context->counts[i].load(std::memory_order_relaxed);
+    /* guard fall-backs are decided on the device and counted in pinned host memory */
+    if (context->guard_hits)
+        counts[5] += *static_cast<volatile unsigned long long *>(context->guard_hits);
     return 0;
 }
 
@@ -137,6 +152,8 @@ extern "C" int camblas_cuda_reset_stats(camblas_cuda_context *context)
         return fail(nullptr, "missing context", 1);
     for (auto &count : context->counts)
         count.store(0, std::memory_order_relaxed);
+    if (context->guard_hits)
+        *static_cast<volatile unsigned long long *>(context->guard_hits) = 0;
     return 0;
 }
 

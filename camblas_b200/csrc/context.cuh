@@ -34,7 +34,10 @@ struct camblas_cuda_context {
     size_t scratch_bytes = 0;
     bool scratch_captured = false;
     std::vector<void *> retired;
-    unsigned *status = nullptr; /* device word written by bounded waits that gave up */
+    unsigned *status = nullptr; /* device words: [0] written by bounded waits that gave up,
+                                   [1] Strassen range-guard flag of the call in flight */
+    unsigned long long *guard_hits = nullptr;        /* pinned host counter of guard fall-backs */
+    unsigned long long *guard_hits_device = nullptr; /* the same word as the device sees it */
     EncodeTiledFn encode = nullptr;
     std::atomic<uint64_t> counts[8] = {};
     char error[256] = "";

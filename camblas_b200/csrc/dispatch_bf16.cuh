@@ -42,20 +42,33 @@ struct Product {
     int cut0, cut1;
     __nv_bfloat16 *c1, *c2;
     long long ldc1, ldc2;
+    /* device word: when non-NULL the tensor-core row kernel runs only if it is non-zero */
+    const unsigned *run_if_set;
 };
 
-template <int BN, int Stages, int Mode> int prepare_kernel()
+template <int BN, int Stages, int Mode, int PMajor = sm100::kMajorK, int QMajor = sm100::kMajorK>
+int prepare_kernel()
 {
-    return int(cudaFuncSetAttribute(sm100::gemm_bf16_tcgen05<BN, Stages, Mode>,
+    return int(cudaFuncSetAttribute(sm100::gemm_bf16_tcgen05<BN, Stages, Mode, PMajor, QMajor>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     sm100::GemmSmem<BN, Stages, Mode>::kTotal));
 }
 
+template <int PMajor, int QMajor> int prepare_row_kernels()
+{
+    return prepare_kernel<256, 4, sm100::kStoreRows, PMajor, QMajor>() |
+           prepare_kernel<128, 6, sm100::kStoreRows, PMajor, QMajor>() |
+           prepare_kernel<64, 8, sm100::kStoreRows, PMajor, QMajor>();
+}
+
 inline int prepare_kernels()
 {
-    int status = prepare_kernel<256, 4, sm100::kStoreRows>();
-    status |= prepare_kernel<128, 6, sm100::kStoreRows>();
-    status |= prepare_kernel<64, 8, sm100::kStoreRows>();
+    using namespace sm100;
+    int status = prepare_row_kernels<kMajorK, kMajorK>();
+    status |= prepare_row_kernels<kMajorK, kMajorMN>();
+    status |= prepare_row_kernels<kMajorMN, kMajorK>();
+    status |= prepare_row_kernels<kMajorMN, kMajorMN>();
+    status |= prepare_kernel<256, 4, kStoreFloat, kMajorK, kMajorMN>();
     status |= prepare_kernel<16, 8, sm100::kStoreColumns>();
     status |= prepare_kernel<32, 8, sm100::kStoreColumns>();
     status |= prepare_kernel<64, 8, sm100::kStoreColumns>();
@@ -65,23 +78,42 @@ inline int prepare_kernels()
     return status;
 }
 
-template <int BN, int Stages, int Mode>
+template <int BN, int Stages, int Mode, int PMajor = sm100::kMajorK, int QMajor = sm100::kMajorK>
 void launch_tensor(camblas_cuda_context *context, const CUtensorMap &p, const CUtensorMap &q,
                    const CUtensorMap &d0, const CUtensorMap &d1, const CUtensorMap &d2,
                    const sm100::GemmTask &task)
 {
-    int units = task.r_blocks * task.c_blocks * task.split;
-    int grid = units < context->sm_count ? units : context->sm_count;
-    sm100::gemm_bf16_tcgen05<BN, Stages, Mode>
+    long long units = 1ll * task.r_blocks * task.c_blocks * task.split * task.batch;
+    int grid = units < context->sm_count ? int(units) : context->sm_count;
+    sm100::gemm_bf16_tcgen05<BN, Stages, Mode, PMajor, QMajor>
         <<<grid, sm100::kThreads, sm100::GemmSmem<BN, Stages, Mode>::kTotal, context->stream>>>(
             p, q, d0, d1, d2, task);
 }
 
+template <int PMajor, int QMajor>
+void launch_rows(camblas_cuda_context *context, int bn, const CUtensorMap &p, const CUtensorMap &q,
+                 const CUtensorMap &d0, const CUtensorMap &d1, const CUtensorMap &d2,
+                 const sm100::GemmTask &task)
+{
+    if (bn == 256)
+        launch_tensor<256, 4, sm100::kStoreRows, PMajor, QMajor>(context, p, q, d0, d1, d2, task);
+    else if (bn == 128)
+        launch_tensor<128, 6, sm100::kStoreRows, PMajor, QMajor>(context, p, q, d0, d1, d2, task);
+    else
+        launch_tensor<64, 8, sm100::kStoreRows, PMajor, QMajor>(context, p, q, d0, d1, d2, task);
+}
+
+/* Operands the TMA pipeline can take: 16-byte aligned base and row pitch. */
 inline bool tensor_operands_ok(const Product &x)
 {
-    /* both operands K-major with 16-byte aligned rows */
-    return x.ta && !x.tb && aligned16(x.a) && aligned16(x.b) && x.lda % 8 == 0 &&
-           (x.ldb % 8 == 0 || x.n == 1);
+    return aligned16(x.a) && aligned16(x.b) && x.lda % 8 == 0 &&
+           (x.ldb % 8 == 0 || (x.n == 1 && !x.tb));
+}
+
+/* The few-token kernels take only the layout a linear layer produces. */
+inline bool swapped_operands_ok(const Product &x)
+{
+    return x.ta && !x.tb && tensor_operands_ok(x);
 }
 
 inline bool rows_store_ok(const Product &x)
@@ -126,6 +158,8 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     task.bias = x.bias;
     task.status = context->status;
     task.cut0 = x.cut0, task.cut1 = x.cut1;
+    task.batch = 1;
+    task.run_if_set = x.run_if_set;
     bool packed = x.cut0 < x.m;
     /* Tile width: compare the padded cost (waves x tile width) of 256- and
      * 128-column tiles over the SMs. */
@@ -148,10 +182,13 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
 
     CUtensorMap p, q, d0, d1, d2;
-    bool ok = encode_2d(context, &p, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.b, x.k, x.n, x.ldb * 2,
-                        64, 128) &&
-              encode_2d(context, &q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.a, x.k, x.m, x.lda * 2,
-                        64, bn);
+    const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    /* P = op(B): 'N' stores row j contiguous along k (K-major); 'T' stores b[j + l*ldb]
+     * (MN-major, 64 x 64 boxes). Q = op(A): 'T' is K-major, 'N' is a[i + l*lda]. */
+    bool ok = x.tb ? encode_2d(context, &p, bf16, 2, x.b, x.n, x.k, x.ldb * 2, 64, 64)
+                   : encode_2d(context, &p, bf16, 2, x.b, x.k, x.n, x.ldb * 2, 64, 128);
+    ok = ok && (x.ta ? encode_2d(context, &q, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, bn)
+                     : encode_2d(context, &q, bf16, 2, x.a, x.m, x.k, x.lda * 2, 64, 64));
     if (packed) {
         ok = ok &&
              encode_2d(context, &d0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.c, x.cut0, x.n,
@@ -167,12 +204,15 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     }
     if (!ok)
         return fail(context, "tensor map encoding", 1);
-    if (bn == 256)
-        launch_tensor<256, 4, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
-    else if (bn == 128)
-        launch_tensor<128, 6, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
+    using namespace sm100;
+    if (!x.tb && x.ta)
+        launch_rows<kMajorK, kMajorK>(context, bn, p, q, d0, d1, d2, task);
+    else if (!x.tb && !x.ta)
+        launch_rows<kMajorK, kMajorMN>(context, bn, p, q, d0, d1, d2, task);
+    else if (x.tb && x.ta)
+        launch_rows<kMajorMN, kMajorK>(context, bn, p, q, d0, d1, d2, task);
     else
-        launch_tensor<64, 8, sm100::kStoreRows>(context, p, q, d0, d1, d2, task);
+        launch_rows<kMajorMN, kMajorMN>(context, bn, p, q, d0, d1, d2, task);
     return launched(context, "tcgen05 BF16 GEMM");
 }
 
@@ -194,6 +234,7 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     task.bias = x.bias;
     task.status = context->status;
     task.cut0 = task.cut1 = x.m;
+    task.batch = 1;
     long long plane = 1ll * task.r_blocks * 128;
     if (task.split > 1) {
         size_t bytes = size_t(task.split) * x.n * plane * sizeof(float);
@@ -320,22 +361,22 @@ inline int run_generic(camblas_cuda_context *context, const Product &x)
 inline int run_product(camblas_cuda_context *context, const Product &x)
 {
     bool packed = x.cut0 < x.m;
-    bool tensor = tensor_operands_ok(x);
+    bool tensor = tensor_operands_ok(x) && rows_store_ok(x);
+    bool swapped = swapped_operands_ok(x);
     bool skinny_ok = x.ta && !x.tb && aligned16(x.a) && x.lda % 8 == 0 && x.n <= 4;
     int family = context->forced_family;
     if (family == kAuto) {
         if (skinny_ok)
             family = kSkinny;
-        else if (tensor && x.n <= 64)
+        else if (swapped && x.n <= 64)
             family = kTensorSwapped;
-        else if (tensor && rows_store_ok(x))
+        else if (tensor)
             family = kTensor;
         else
             family = kGeneric;
     } else {
         bool possible = family == kGeneric || (family == kSkinny && skinny_ok) ||
-                        (family == kTensorSwapped && tensor) ||
-                        (family == kTensor && tensor && rows_store_ok(x));
+                        (family == kTensorSwapped && swapped) || (family == kTensor && tensor);
         if (!possible)
             return fail(context, "forced kernel family cannot take these operands", 1);
     }

@@ -25,7 +25,12 @@
 namespace sm100
 {
 
-enum StoreMode : int { kStoreRows = 0, kStoreColumns = 1, kStorePartial = 2 };
+enum StoreMode : int { kStoreRows = 0, kStoreColumns = 1, kStorePartial = 2, kStoreFloat = 3 };
+/* Operand storage: kMajorK = rows contiguous along K (a 64-wide K slice of a row
+ * is one 128-byte swizzled line); kMajorMN = contiguous along the row index (a
+ * 64-row slice of one K index is one line; a tile is a sequence of 64 x 64
+ * boxes of 8 KB). */
+enum OperandMajor : int { kMajorK = 0, kMajorMN = 1 };
 
 struct GemmTask {
     int rows, cols, depth;         /* R, C, K */
@@ -45,6 +50,13 @@ struct GemmTask {
      * [0,cut0) go to out, [cut0,cut1) to out1, [cut1,cols) to out2. cut0 and
      * cut1 are multiples of BN; cut0 == cols disables the feature. */
     int cut0, cut1;
+    /* Batch of independent products over stacked operands (batch >= 1): product
+     * b reads P rows (K-major) or P K indices (MN-major) offset by b*batch_p,
+     * likewise Q by b*batch_q, and writes FP32 plane b of out_float. */
+    int batch, batch_p, batch_q;
+    float *out_float; /* kStoreFloat: [batch][rows][ld_out] */
+    const unsigned *skip_if_set; /* when non-NULL and *skip_if_set != 0 the kernel does nothing */
+    const unsigned *run_if_set;  /* when non-NULL and *run_if_set == 0 the kernel does nothing */
 };
 
 constexpr int kBlockR = 128;
@@ -71,10 +83,13 @@ __device__ __forceinline__ void report(unsigned *status, volatile uint32_t *abor
 }
 
 __device__ __forceinline__ void decode_unit(const GemmTask &task, int unit, int &rb, int &cb,
-                                            int &part)
+                                            int &part, int &batch)
 {
     part = unit % task.split;
     int tile = unit / task.split;
+    const int per_batch = task.r_blocks * task.c_blocks;
+    batch = tile / per_batch;
+    tile -= batch * per_batch;
     int per_panel = task.panel * task.c_blocks;
     int panel = tile / per_panel;
     int local = tile - panel * per_panel;
@@ -83,7 +98,7 @@ __device__ __forceinline__ void decode_unit(const GemmTask &task, int unit, int 
     rb = panel * task.panel + local - cb * height;
 }
 
-template <int BN, int Stages, int Mode>
+template <int BN, int Stages, int Mode, int PMajor = kMajorK, int QMajor = kMajorK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_p,
                       const __grid_constant__ CUtensorMap map_q,
@@ -96,6 +111,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     static_assert((kTmemColumns & (kTmemColumns - 1)) == 0 && kTmemColumns <= 512, "TMEM size");
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
     static_assert(Mode != kStoreRows || BN % 64 == 0, "row store works on 64-column slabs");
+    static_assert(QMajor == kMajorK || BN % 64 == 0, "MN-major tiles are made of 64-row boxes");
 
     extern __shared__ uint8_t raw_smem[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -110,7 +126,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int units = task.r_blocks * task.c_blocks * task.split;
+    const int units = task.r_blocks * task.c_blocks * task.split * task.batch;
+    if (task.skip_if_set != nullptr && *task.skip_if_set != 0)
+        return;
+    if (task.run_if_set != nullptr && *task.run_if_set == 0)
+        return;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Stages; ++s) {
@@ -151,10 +171,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t armed = 0, armed_parity = 0;
             bool ok = true;
             for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
-                int rb, cb, part;
-                decode_unit(task, unit, rb, cb, part);
+                int rb, cb, part, batch;
+                decode_unit(task, unit, rb, cb, part, batch);
                 int kb0 = part * task.k_blocks_per_split;
                 int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+                const int p_shift = batch * task.batch_p, q_shift = batch * task.batch_q;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
                         report(task.status, abort, kRoleProducer);
@@ -164,10 +185,25 @@ __global__ void __launch_bounds__(kThreads, 1)
                     uint8_t *p_tile = smem + stage * Layout::kStageBytes;
                     uint8_t *q_tile = p_tile + Layout::kPBytes;
                     mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
-                    tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockK, rb * kBlockR,
-                                     policy_p);
-                    tma_load_2d_hint(q_tile, &map_q, &full[stage], kb * kBlockK, cb * BN,
-                                     policy_q);
+                    if constexpr (PMajor == kMajorK) {
+                        tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockK,
+                                         rb * kBlockR + p_shift, policy_p);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < kBlockR / 64; ++g)
+                            tma_load_2d_hint(p_tile + g * 8192, &map_p, &full[stage],
+                                             rb * kBlockR + g * 64, kb * kBlockK + p_shift,
+                                             policy_p);
+                    }
+                    if constexpr (QMajor == kMajorK) {
+                        tma_load_2d_hint(q_tile, &map_q, &full[stage], kb * kBlockK,
+                                         cb * BN + q_shift, policy_q);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < BN / 64; ++g)
+                            tma_load_2d_hint(q_tile + g * 8192, &map_q, &full[stage],
+                                             cb * BN + g * 64, kb * kBlockK + q_shift, policy_q);
+                    }
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == Stages) {
@@ -188,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == 1) {
         if (lane == 0) {
             /* ---- MMA issuer ---- */
-            constexpr uint32_t idesc = make_idesc(1, kBlockR, BN, 0, 0);
+            constexpr uint32_t idesc = make_idesc(1, kBlockR, BN, PMajor, QMajor);
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
@@ -210,14 +246,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tcgen05_fence_after();
-                    uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
-                    uint64_t desc_p = desc_kmajor_sw128(p_address);
-                    uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
+                    const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    const uint32_t q_address = p_address + Layout::kPBytes;
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        /* 16 BF16 along K = 32 bytes = 2 descriptor address units */
-                        umma_f16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc,
-                                 (kb > kb0 || k > 0) ? 1u : 0u);
+                        /* K-major: 16 BF16 along K are 32 bytes further in the same
+                         * swizzled lines. MN-major: 16 K indices are 16 lines = 2048 bytes. */
+                        const uint64_t desc_p = PMajor == kMajorK
+                                                    ? desc_kmajor_sw128(p_address) + 2 * k
+                                                    : desc_mnmajor_sw128(p_address + k * 2048, 8192);
+                        const uint64_t desc_q = QMajor == kMajorK
+                                                    ? desc_kmajor_sw128(q_address) + 2 * k
+                                                    : desc_mnmajor_sw128(q_address + k * 2048, 8192);
+                        umma_f16(tmem_d, desc_p, desc_q, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[stage]);
                     if (++stage == Stages) {
@@ -236,8 +277,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t local = 0;
         uint32_t slab_use = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
-            int rb, cb, part;
-            decode_unit(task, unit, rb, cb, part);
+            int rb, cb, part, batch;
+            decode_unit(task, unit, rb, cb, part, batch);
             uint32_t buffer = local & 1, use = local >> 1;
             if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
                 report(task.status, abort, kRoleEpilogueFull);
@@ -317,6 +358,33 @@ __global__ void __launch_bounds__(kThreads, 1)
                     ++slab_use;
                 }
                 (void)out;
+            } else if constexpr (Mode == kStoreFloat) {
+                /* FP32 plane of a batched product: this thread owns one row and
+                 * writes 32 consecutive floats per piece (128 bytes). */
+                float *plane = task.out_float +
+                               static_cast<long long>(batch) * task.rows * task.ld_out +
+                               static_cast<long long>(row) * task.ld_out;
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(taddr + chunk * 32, acc);
+                    tmem_ld_wait();
+                    if (chunk == BN / 32 - 1) {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&tmem_empty[buffer]);
+                    }
+                    const int cbase = col0 + chunk * 32;
+                    if (row < task.rows) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            if (cbase + i < task.cols)
+                                *reinterpret_cast<float4 *>(plane + cbase + i) = make_float4(
+                                    __uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                    __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+                    }
+                }
             } else {
                 /* Operands are swapped: this thread owns output feature `row`,
                  * the registers run over tokens col0 + i. */

@@ -282,3 +282,27 @@ def test_full_size_properties(tokens, outputs, inner):
         half = outputs // 2
         assert torch.equal(_kernels.linear(x, w[:half]), y[:, :half])
         assert torch.equal(_kernels.linear(x, w[half:]), y[:, half:])
+
+
+@pytest.mark.parametrize("ta,tb", [("N", "N"), ("N", "T"), ("T", "N"), ("T", "T")])
+@pytest.mark.parametrize("m,n,k", [(256, 128, 64), (264, 136, 200), (520, 300, 72), (1024, 384, 1032)])
+def test_tensor_family_takes_every_transpose_pair(rng, ta, tb, m, n, k):
+    """Aligned operands of any transpose pair run on the tensor cores: 'N' for A
+    and 'T' for B are read as MN-major tiles (64 x 64 TMA boxes)."""
+    def pitch(rows, extra):
+        return (rows + 7) // 8 * 8 + extra  # TMA needs 16-byte row pitches
+
+    lda = pitch(m if ta == "N" else k, 8)
+    ldb = pitch(k if tb == "N" else n, 16)
+    ldc = pitch(m, 8)
+    a = padded(rng, m if ta == "N" else k, k if ta == "N" else m, lda)
+    b = padded(rng, k if tb == "N" else n, n if tb == "N" else k, ldb)
+    c = padded(rng, m, n, ldc)
+    for alpha, beta in ((1.0, 0.0), (-0.5, 2.0)):
+        expected = c.copy()
+        expected[:, m:] = 0
+        oracle.bgemm(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, expected, ldc)
+        actual = run_bgemm(ta, tb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc, "tensor")
+        assert np.all(actual[:, m:] == NAN)
+        error = oracle.rel_l2(oracle.bf16_values(actual[:, :m]), oracle.bf16_values(expected[:, :m]))
+        assert error <= BF16_TOLERANCE, error
