@@ -41,7 +41,8 @@ _COUNTERS = (
     "attention",
     "backward",
 )
-_FAMILIES = {"auto": 0, "generic": 1, "skinny": 2, "tensor": 3, "tensor_swapped": 4}
+_FAMILIES = {"auto": 0, "generic": 1, "skinny": 2, "tensor": 3, "tensor_swapped": 4,
+             "tensor_pair": 5}
 
 _P = ct.c_void_p
 _I = ct.c_int

@@ -128,7 +128,7 @@ extern "C" int camblas_cuda_set_algorithm(camblas_cuda_context *context, int alg
 
 extern "C" int camblas_cuda_force_kernel(camblas_cuda_context *context, int family)
 {
-    if (!context || family < 0 || family > 4)
+    if (!context || family < 0 || family > 5)
         return fail(context, "invalid kernel family", 1);
     context->forced_family = family;
     return 0;

@@ -13,11 +13,13 @@
  *   family 4 (tcgen05, swapped) P = op(A) rows (outputs), Q = op(B) rows (tokens),
  *                               D^T stored, optional split-K through scratch
  *   family 2 (skinny)           up to four tokens, CUDA cores, split-K
+ *   family 5 (tcgen05, two SMs) as family 3 with 256-row tiles computed by CTA pairs
  *   family 1 (generic)          anything else
  */
 #pragma once
 
 #include "context.cuh"
+#include "gemm_bf16_pair.cuh"
 #include "gemm_bf16_tcgen05.cuh"
 #include "gemm_generic.cuh"
 #include "gemv_skinny.cuh"
@@ -25,7 +27,14 @@
 namespace host
 {
 
-enum Family : int { kAuto = 0, kGeneric = 1, kSkinny = 2, kTensor = 3, kTensorSwapped = 4 };
+enum Family : int {
+    kAuto = 0,
+    kGeneric = 1,
+    kSkinny = 2,
+    kTensor = 3,
+    kTensorSwapped = 4,
+    kTensorPair = 5
+};
 
 struct Product {
     bool ta, tb;
@@ -61,10 +70,26 @@ template <int PMajor, int QMajor> int prepare_row_kernels()
            prepare_kernel<64, 8, sm100::kStoreRows, PMajor, QMajor>();
 }
 
+template <int PMajor, int QMajor> int prepare_pair_kernels()
+{
+    using namespace sm100;
+    int status = int(cudaFuncSetAttribute(gemm_bf16_pair<256, 6, PMajor, QMajor>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          PairSmem<256, 6>::kTotal));
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<128, 8, PMajor, QMajor>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       PairSmem<128, 8>::kTotal));
+    return status;
+}
+
 inline int prepare_kernels()
 {
     using namespace sm100;
     int status = prepare_row_kernels<kMajorK, kMajorK>();
+    status |= prepare_pair_kernels<kMajorK, kMajorK>();
+    status |= prepare_pair_kernels<kMajorK, kMajorMN>();
+    status |= prepare_pair_kernels<kMajorMN, kMajorK>();
+    status |= prepare_pair_kernels<kMajorMN, kMajorMN>();
     status |= prepare_row_kernels<kMajorK, kMajorMN>();
     status |= prepare_row_kernels<kMajorMN, kMajorK>();
     status |= prepare_row_kernels<kMajorMN, kMajorMN>();
@@ -83,8 +108,8 @@ void launch_tensor(camblas_cuda_context *context, const CUtensorMap &p, const CU
                    const CUtensorMap &d0, const CUtensorMap &d1, const CUtensorMap &d2,
                    const sm100::GemmTask &task)
 {
-    long long units = 1ll * task.r_blocks * task.c_blocks * task.split * task.batch;
-    int grid = units < context->sm_count ? int(units) : context->sm_count;
+    long long units = sm100::unit_count(task);
+    int grid = (units < context->sm_count && task.sk_cols == 0) ? int(units) : context->sm_count;
     sm100::gemm_bf16_tcgen05<BN, Stages, Mode, PMajor, QMajor>
         <<<grid, sm100::kThreads, sm100::GemmSmem<BN, Stages, Mode>::kTotal, context->stream>>>(
             p, q, d0, d1, d2, task);
@@ -161,18 +186,13 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     task.batch = 1;
     task.run_if_set = x.run_if_set;
     bool packed = x.cut0 < x.m;
-    /* Tile width: compare the padded cost (waves x tile width) of 256- and
-     * 128-column tiles over the SMs. */
-    int sms = context->sm_count;
-    auto cost = [&](int bn) {
-        long long tiles = 1ll * task.r_blocks * ((x.m + bn - 1) / bn);
-        return ((tiles + sms - 1) / sms) * bn;
-    };
-    int bn = 256;
-    if (x.m <= 64)
-        bn = 64;
-    else if (x.m <= 128 || cost(128) * 1.15 < cost(256))
-        bn = 128;
+    /* Tile width: 256 columns unless the product is narrower. When the tiles do
+     * not fill the SMs evenly, the last partial wave is spread over all SMs by
+     * K range (stream-K) if the idle time it recovers outweighs the second pass
+     * over the partial sums. Rates are rough steady-state figures of this kernel
+     * on a B200; only their ratio matters. */
+    const int sms = context->sm_count;
+    int bn = x.m <= 64 ? 64 : (x.m <= 128 ? 128 : 256);
     if (packed && (x.cut0 % bn != 0 || x.cut1 % bn != 0)) {
         bn = 128;
         if (x.cut0 % bn != 0 || x.cut1 % bn != 0)
@@ -180,6 +200,22 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     }
     task.c_blocks = (x.m + bn - 1) / bn;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    if (task.r_blocks <= 8 && sms / task.r_blocks >= 2) {
+        const int teams = sms / task.r_blocks;
+        const int rest = task.c_blocks % teams;
+        const double tile_us = 2.0 * 128 * bn * x.k / (1.35e15 / 148.0 / 1e6);
+        const double recovered = (1.0 - double(rest) / teams) * tile_us;
+        const double second_pass =
+            3.0 + double(rest + teams) * task.r_blocks * 128 * bn * 8 / 5.0e6;
+        if (rest != 0 && task.k_blocks >= 16 && x.run_if_set == nullptr &&
+            recovered > second_pass) {
+            task.dp_cols = task.c_blocks - rest, task.sk_cols = rest;
+            int status = reserve_scratch(context, size_t(2) * sms * 128 * bn * sizeof(float));
+            if (status != 0)
+                return status;
+            task.sk_partial = static_cast<float *>(context->scratch);
+        }
+    }
 
     CUtensorMap p, q, d0, d1, d2;
     const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -213,7 +249,137 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
         launch_rows<kMajorMN, kMajorK>(context, bn, p, q, d0, d1, d2, task);
     else
         launch_rows<kMajorMN, kMajorMN>(context, bn, p, q, d0, d1, d2, task);
-    return launched(context, "tcgen05 BF16 GEMM");
+    int status = launched(context, "tcgen05 BF16 GEMM");
+    if (status != 0 || task.sk_cols == 0)
+        return status;
+    dim3 grid(task.sk_cols, 128 * bn / 8 / 256, task.r_blocks);
+    if (bn == 256)
+        sm100::sk_fixup<256><<<grid, 256, 0, context->stream>>>(task, sms, x.c1, x.ldc1, x.c2,
+                                                                x.ldc2);
+    else if (bn == 128)
+        sm100::sk_fixup<128><<<grid, 256, 0, context->stream>>>(task, sms, x.c1, x.ldc1, x.c2,
+                                                                x.ldc2);
+    else
+        sm100::sk_fixup<64><<<grid, 256, 0, context->stream>>>(task, sms, x.c1, x.ldc1, x.c2,
+                                                               x.ldc2);
+    return launched(context, "stream-K fix-up");
+}
+
+template <int BN, int Stages, int PMajor, int QMajor>
+cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensorMap &p,
+                        const CUtensorMap &q, const CUtensorMap &d0, const CUtensorMap &d1,
+                        const CUtensorMap &d2, const sm100::GemmTask &task)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * pairs);
+    config.blockDim = dim3(sm100::kThreads);
+    config.dynamicSmemBytes = sm100::PairSmem<BN, Stages>::kTotal;
+    config.stream = context->stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, sm100::gemm_bf16_pair<BN, Stages, PMajor, QMajor>, p, q, d0,
+                              d1, d2, task);
+}
+
+template <int PMajor, int QMajor>
+cudaError_t launch_pair_width(camblas_cuda_context *context, int bn, int pairs, const CUtensorMap &p,
+                              const CUtensorMap &q, const CUtensorMap &d0, const CUtensorMap &d1,
+                              const CUtensorMap &d2, const sm100::GemmTask &task)
+{
+    if (bn == 256)
+        return launch_pair<256, 6, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
+    return launch_pair<128, 8, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
+}
+
+/* Two-SM tiles: 256 token rows x bn outputs per CTA pair. */
+inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
+{
+    sm100::GemmTask task{};
+    task.rows = x.n, task.cols = x.m, task.depth = x.k;
+    task.r_blocks = (x.n + 255) / 256;
+    task.k_blocks = (x.k + 63) / 64;
+    task.split = 1, task.k_blocks_per_split = task.k_blocks;
+    task.alpha = x.alpha, task.beta = x.beta;
+    task.out = x.c, task.ld_out = x.ldc;
+    task.addend = x.addend, task.ld_add = x.ld_add;
+    task.bias = x.bias;
+    task.status = context->status;
+    task.cut0 = x.cut0, task.cut1 = x.cut1;
+    task.batch = 1;
+    task.run_if_set = x.run_if_set;
+    const bool packed = x.cut0 < x.m;
+    const int pairs_max = context->sm_count / 2;
+    int bn = x.m <= 128 ? 128 : 256;
+    if (packed && (x.cut0 % bn != 0 || x.cut1 % bn != 0)) {
+        bn = 128;
+        if (x.cut0 % bn != 0 || x.cut1 % bn != 0)
+            return fail(context, "packed projection widths must be multiples of 128", 1);
+    }
+    task.c_blocks = (x.m + bn - 1) / bn;
+    task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    if (task.r_blocks <= 8 && pairs_max / task.r_blocks >= 2) {
+        const int teams = pairs_max / task.r_blocks;
+        const int rest = task.c_blocks % teams;
+        const double tile_us = 2.0 * 128 * bn * x.k / (1.45e15 / 148.0 / 1e6);
+        const double recovered = (1.0 - double(rest) / teams) * tile_us;
+        const double second_pass =
+            3.0 + double(rest + teams) * task.r_blocks * 256 * bn * 8 / 5.0e6;
+        if (rest != 0 && task.k_blocks >= 16 && x.run_if_set == nullptr &&
+            recovered > second_pass) {
+            task.dp_cols = task.c_blocks - rest, task.sk_cols = rest;
+            int status =
+                reserve_scratch(context, size_t(4) * pairs_max * 128 * bn * sizeof(float));
+            if (status != 0)
+                return status;
+            task.sk_partial = static_cast<float *>(context->scratch);
+        }
+    }
+    long long units = 1ll * task.r_blocks * task.c_blocks;
+    int pairs = (units < pairs_max && task.sk_cols == 0) ? int(units) : pairs_max;
+
+    CUtensorMap p, q, d0, d1, d2;
+    const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    bool ok = x.tb ? encode_2d(context, &p, bf16, 2, x.b, x.n, x.k, x.ldb * 2, 64, 64)
+                   : encode_2d(context, &p, bf16, 2, x.b, x.k, x.n, x.ldb * 2, 64, 128);
+    ok = ok && (x.ta ? encode_2d(context, &q, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, bn / 2)
+                     : encode_2d(context, &q, bf16, 2, x.a, x.m, x.k, x.lda * 2, 64, 64));
+    if (packed) {
+        ok = ok && encode_2d(context, &d0, bf16, 2, x.c, x.cut0, x.n, x.ldc * 2, 64, 32) &&
+             encode_2d(context, &d1, bf16, 2, x.c1, x.cut1 - x.cut0, x.n, x.ldc1 * 2, 64, 32) &&
+             encode_2d(context, &d2, bf16, 2, x.c2, x.m - x.cut1, x.n, x.ldc2 * 2, 64, 32);
+    } else {
+        ok = ok && encode_2d(context, &d0, bf16, 2, x.c, x.m, x.n, x.ldc * 2, 64, 32);
+        d1 = d0, d2 = d0;
+    }
+    if (!ok)
+        return fail(context, "tensor map encoding", 1);
+    using namespace sm100;
+    cudaError_t error;
+    if (!x.tb && x.ta)
+        error = launch_pair_width<kMajorK, kMajorK>(context, bn, pairs, p, q, d0, d1, d2, task);
+    else if (!x.tb && !x.ta)
+        error = launch_pair_width<kMajorK, kMajorMN>(context, bn, pairs, p, q, d0, d1, d2, task);
+    else if (x.tb && x.ta)
+        error = launch_pair_width<kMajorMN, kMajorK>(context, bn, pairs, p, q, d0, d1, d2, task);
+    else
+        error = launch_pair_width<kMajorMN, kMajorMN>(context, bn, pairs, p, q, d0, d1, d2, task);
+    if (error != cudaSuccess)
+        return fail(context, "two-SM tcgen05 BF16 GEMM", error);
+    if (task.sk_cols == 0)
+        return 0;
+    dim3 grid(task.sk_cols, 256 * bn / 8 / 256, task.r_blocks);
+    if (bn == 256)
+        sm100::sk_fixup_pair<256><<<grid, 256, 0, context->stream>>>(task, pairs, x.c1, x.ldc1,
+                                                                     x.c2, x.ldc2);
+    else
+        sm100::sk_fixup_pair<128><<<grid, 256, 0, context->stream>>>(task, pairs, x.c1, x.ldc1,
+                                                                     x.c2, x.ldc2);
+    return launched(context, "stream-K fix-up");
 }
 
 inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
@@ -371,16 +537,17 @@ inline int run_product(camblas_cuda_context *context, const Product &x)
         else if (swapped && x.n <= 64)
             family = kTensorSwapped;
         else if (tensor)
-            family = kTensor;
+            family = x.n > 128 ? kTensorPair : kTensor;
         else
             family = kGeneric;
     } else {
         bool possible = family == kGeneric || (family == kSkinny && skinny_ok) ||
-                        (family == kTensorSwapped && swapped) || (family == kTensor && tensor);
+                        (family == kTensorSwapped && swapped) ||
+                        ((family == kTensor || family == kTensorPair) && tensor);
         if (!possible)
             return fail(context, "forced kernel family cannot take these operands", 1);
     }
-    if (packed && family != kTensor) {
+    if (packed && family != kTensor && family != kTensorPair) {
         Product part = x;
         part.cut0 = part.cut1 = 0;
         const int starts[4] = {0, x.cut0, x.cut1, x.m};
@@ -408,6 +575,8 @@ inline int run_product(camblas_cuda_context *context, const Product &x)
         return run_tensor_swapped(context, x);
     case kTensor:
         return run_tensor_rows(context, x);
+    case kTensorPair:
+        return run_tensor_pair(context, x);
     default:
         return run_generic(context, x);
     }

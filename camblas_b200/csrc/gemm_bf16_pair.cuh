@@ -1,0 +1,409 @@
+/*
+ * BF16 GEMM with two-SM tensor-core instructions (tcgen05.mma.cta_group::2).
+ *
+ * Two CTAs on neighbouring SMs form a cluster and compute one 256 x BN tile of
+ * D[R,C] = P[R,K] . Q[C,K]^T together: each CTA stages its own 128 rows of P and
+ * its own BN/2 rows of Q, the leader CTA (cluster rank 0) issues one MMA of
+ * shape M=256, N=BN, K=16 that reads both CTAs' shared memory, and each CTA
+ * receives its 128 accumulator rows in its own tensor memory. Compared with the
+ * one-SM kernel this halves the Q bytes every SM pulls from L2 and keeps in
+ * shared memory per multiply (32 KB instead of 48 KB per 64-deep stage at
+ * BN=256), which is what that kernel is short of, and lets the ring hold six
+ * stages instead of four.
+ *
+ * Roles per CTA (192 threads): warp 0 = TMA producer for this CTA's halves
+ * (every CTA fetches its own bytes; no load is shared between CTAs), warp 1 =
+ * MMA issuer in the leader and idle in the peer, warps 2-5 = epilogue for this
+ * CTA's 128 rows.
+ *
+ * Barriers. Every CTA has the same barrier objects at the same shared-memory
+ * offsets; the ones that synchronise the pair live in the leader:
+ *   full[s]        leader: one arrival (leader's producer, which also posts the
+ *                  byte count of BOTH CTAs' loads) + the bytes of both CTAs'
+ *                  TMA loads (the peer's loads name the leader's barrier);
+ *   empty[s]       one per CTA, arrived by two tcgen05.commit of the leader,
+ *                  one to its own barrier and one to the peer's;
+ *   tmem_full[b]   one per CTA, same mechanism;
+ *   tmem_empty[b]  leader: eight arrivals, four epilogue warps of each CTA (the
+ *                  peer's arrive remotely).
+ * Waits are bounded as in the one-SM kernel. The two CTAs meet at a cluster
+ * barrier after set-up and before tear-down so that neither touches the other's
+ * shared memory outside that window.
+ */
+#pragma once
+
+#include "gemm_bf16_tcgen05.cuh"
+
+namespace sm100
+{
+
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+/* Shared-memory address of the same object in the CTA of rank `rank`. */
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_address, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address)
+                 : "memory");
+}
+
+/* TMA load whose completion bytes are counted on a barrier that may live in the
+ * other CTA of the pair (address in the cluster's shared window). */
+__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map,
+                                                 uint32_t barrier_cluster_address, int x, int y,
+                                                 uint64_t policy)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_u32(smem)),
+                 "l"(map), "r"(barrier_cluster_address), "r"(x), "r"(y), "l"(policy)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(smem_result)),
+                 "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                              uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+/* Arrive on a barrier (cluster shared address, this CTA's or the peer's) once
+ * every MMA issued so far by this thread is done. */
+__device__ __forceinline__ void umma_commit_pair(uint32_t barrier_cluster_address)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     barrier_cluster_address)
+                 : "memory");
+}
+
+constexpr int kPairRows = 256;
+
+template <int BN, int Stages> struct PairSmem {
+    static constexpr int kPBytes = kBlockR * kBlockK * 2;      /* this CTA's 128 rows of P */
+    static constexpr int kQBytes = (BN / 2) * kBlockK * 2;     /* this CTA's half of the Q tile */
+    static constexpr int kStageBytes = kPBytes + kQBytes;
+    static constexpr int kTotal = Stages * kStageBytes + kStagingBytes + 256 + 1024;
+};
+
+/* task.r_blocks counts 256-row blocks here; everything else as in GemmTask. */
+template <int BN, int Stages, int PMajor = kMajorK, int QMajor = kMajorK>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_bf16_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_d0,
+                   const __grid_constant__ CUtensorMap map_d1,
+                   const __grid_constant__ CUtensorMap map_d2, const GemmTask task)
+{
+    using Layout = PairSmem<BN, Stages>;
+    constexpr uint32_t kTmemColumns = BN * 2;
+    constexpr int kHalf = BN / 2;
+    static_assert(BN == 256 || BN == 128, "pair tiles are 256 or 128 columns wide");
+
+    extern __shared__ uint8_t raw_smem[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *staging = smem + Stages * Layout::kStageBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(staging + kStagingBytes);
+    uint64_t *empty = full + Stages;
+    uint64_t *tmem_full = empty + Stages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 8);
+        }
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_d0);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, kTmemColumns);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            /* ---- producer: this CTA's rows of P and its half of the Q tile ---- */
+            const uint64_t keep = policy_evict_last(), stream = policy_evict_first();
+            const uint64_t policy_p = task.r_blocks <= task.panel ? keep : stream;
+            const uint64_t policy_q = task.r_blocks <= task.panel ? stream : keep;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            Unit u;
+            for (int item = 0; ok && fetch_unit(task, item, pair, pairs, u); ++item) {
+                const int p_row = u.rb * kPairRows + rank * kBlockR;
+                const int q_row = u.cb * BN + rank * kHalf;
+                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                        report(task.status, abort, kRoleProducer);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *p_tile = smem + stage * Layout::kStageBytes;
+                    uint8_t *q_tile = p_tile + Layout::kPBytes;
+                    const uint32_t barrier = map_to_rank(smem_u32(&full[stage]), 0);
+                    if (leader)
+                        mbar_arrive_expect_tx(&full[stage], 2 * Layout::kStageBytes);
+                    if constexpr (PMajor == kMajorK) {
+                        tma_load_2d_pair(p_tile, &map_p, barrier, kb * kBlockK, p_row, policy_p);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < kBlockR / 64; ++g)
+                            tma_load_2d_pair(p_tile + g * 8192, &map_p, barrier, p_row + g * 64,
+                                             kb * kBlockK, policy_p);
+                    }
+                    if constexpr (QMajor == kMajorK) {
+                        tma_load_2d_pair(q_tile, &map_q, barrier, kb * kBlockK, q_row, policy_q);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < kHalf / 64; ++g)
+                            tma_load_2d_pair(q_tile + g * 8192, &map_q, barrier, q_row + g * 64,
+                                             kb * kBlockK, policy_q);
+                    }
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                /* let copies already in flight land before the pair retires */
+                for (int wait = 0; wait < 64; ++wait)
+                    __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            /* ---- MMA issuer (leader only) ---- */
+            constexpr uint32_t idesc = make_idesc(1, kPairRows, BN, PMajor, QMajor);
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool ok = true;
+            Unit u;
+            for (int item = 0; ok && fetch_unit(task, item, pair, pairs, u); ++item, ++local) {
+                const uint32_t buffer = local & 1, use = local >> 1;
+                if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                    report(task.status, abort, kRoleMmaTmemEmpty);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + buffer * BN;
+                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort)) {
+                        report(task.status, abort, kRoleMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    const uint32_t q_address = p_address + Layout::kPBytes;
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        const uint64_t desc_p = PMajor == kMajorK
+                                                    ? desc_kmajor_sw128(p_address) + 2 * k
+                                                    : desc_mnmajor_sw128(p_address + k * 2048, 8192);
+                        const uint64_t desc_q = QMajor == kMajorK
+                                                    ? desc_kmajor_sw128(q_address) + 2 * k
+                                                    : desc_mnmajor_sw128(q_address + k * 2048, 8192);
+                        umma_f16_pair(tmem_d, desc_p, desc_q, idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
+                    }
+                    /* free the stage in both CTAs */
+                    const uint32_t local_empty = smem_u32(&empty[stage]);
+                    umma_commit_pair(local_empty);
+                    umma_commit_pair(map_to_rank(local_empty, 1));
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) {
+                    const uint32_t local_full = smem_u32(&tmem_full[buffer]);
+                    umma_commit_pair(local_full);
+                    umma_commit_pair(map_to_rank(local_full, 1));
+                }
+            }
+        }
+    } else {
+        /* ---- epilogue: this CTA's 128 accumulator rows ---- */
+        const int quarter = warp & 3;
+        uint8_t *slab = staging + (warp - 2) * 8192;
+        uint32_t local = 0, slab_use = 0;
+        Unit u;
+        for (int item = 0; fetch_unit(task, item, pair, pairs, u); ++item, ++local) {
+            const uint32_t buffer = local & 1, use = local >> 1;
+            if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
+                report(task.status, abort, kRoleEpilogueFull);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t taddr =
+                tmem_base + buffer * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int row0 = u.rb * kPairRows + rank * kBlockR + quarter * 32;
+            const int col0 = u.cb * BN;
+            auto release = [&]() {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive_cluster(map_to_rank(smem_u32(&tmem_empty[buffer]), 0));
+            };
+            if (u.slot >= 0) {
+                float *slot = task.sk_partial +
+                              ((static_cast<long long>(u.slot) * 2 + rank) * kBlockR +
+                               quarter * 32 + lane) * BN;
+                epilogue_partial<BN>(slot, taddr, release);
+            } else {
+                const CUtensorMap *map_d = &map_d0;
+                int col_shift = 0;
+                if (col0 >= task.cut0) {
+                    const bool third = col0 >= task.cut1;
+                    map_d = third ? &map_d2 : &map_d1;
+                    col_shift = third ? task.cut1 : task.cut0;
+                }
+                epilogue_rows<BN>(task, map_d, taddr, row0 + lane, row0, col0, col_shift, lane, slab,
+                                  slab_use, release);
+            }
+        }
+        if (lane == 0)
+            tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemColumns);
+    }
+}
+
+/* Second pass of the stream-K tail of the pair kernel: like sk_fixup, with
+ * 256-row tiles whose two 128-row halves were written by the two CTAs of a
+ * pair (slot = (2*pair + piece)*2 + half). blockIdx.z = 256-row block. */
+template <int BN>
+__global__ void __launch_bounds__(256)
+    sk_fixup_pair(const GemmTask task, int pairs, __nv_bfloat16 *out1, long long ld1,
+                  __nv_bfloat16 *out2, long long ld2)
+{
+    const int vector = blockIdx.y * 256 + threadIdx.x;
+    const int r = vector / (BN / 8), c8 = (vector % (BN / 8)) * 8; /* r in [0, 256) */
+    const int rb = blockIdx.z, cb = task.dp_cols + blockIdx.x;
+    const int row = rb * kPairRows + r, col = cb * BN + c8;
+    if (row >= task.rows || col >= task.cols)
+        return;
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int teams = pairs / task.r_blocks;
+    const long long total = 1ll * task.sk_cols * task.k_blocks;
+    const long long tile_begin = 1ll * blockIdx.x * task.k_blocks, tile_end = tile_begin + task.k_blocks;
+    int team = static_cast<int>(tile_begin * teams / total);
+    team = team > 0 ? team - 1 : 0;
+    for (; team < teams; ++team) {
+        const long long begin = team * total / teams, end = (team + 1) * total / teams;
+        if (begin >= tile_end)
+            break;
+        if (end <= tile_begin || begin >= end)
+            continue;
+        const int piece = begin < tile_begin ? 1 : 0;
+        const long long slot = (2ll * (team * task.r_blocks + rb) + piece) * 2 + (r >> 7);
+        const float *source = task.sk_partial + (slot * kBlockR + (r & 127)) * BN + c8;
+        const float4 low = *reinterpret_cast<const float4 *>(source);
+        const float4 high = *reinterpret_cast<const float4 *>(source + 4);
+        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
+        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
+    }
+    __nv_bfloat16 *out = task.out;
+    long long ld = task.ld_out;
+    int shift = 0, limit = min(task.cols, task.cut0);
+    if (col >= task.cut0) {
+        const bool third = col >= task.cut1;
+        out = third ? out2 : out1;
+        ld = third ? ld2 : ld1;
+        shift = third ? task.cut1 : task.cut0;
+        limit = third ? task.cols : task.cut1;
+    }
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[i] = task.alpha * sum[i];
+        if (col + i < task.cols) {
+            if (task.bias != nullptr)
+                v[i] += __bfloat162float(task.bias[col + i]);
+            if (task.beta != 0.f)
+                v[i] = fmaf(task.beta,
+                            __bfloat162float(
+                                task.addend[static_cast<long long>(row) * task.ld_add + col + i]),
+                            v[i]);
+        }
+    }
+    __nv_bfloat16 *target = out + static_cast<long long>(row) * ld + (col - shift);
+    if (col + 8 <= limit) {
+        uint4 packed;
+        packed.x = pack_bf16(v[0], v[1]);
+        packed.y = pack_bf16(v[2], v[3]);
+        packed.z = pack_bf16(v[4], v[5]);
+        packed.w = pack_bf16(v[6], v[7]);
+        *reinterpret_cast<uint4 *>(target) = packed;
+    } else {
+        for (int i = 0; i < 8 && col + i < limit; ++i)
+            target[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+} // namespace sm100

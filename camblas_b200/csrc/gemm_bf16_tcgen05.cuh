@@ -55,6 +55,18 @@ struct GemmTask {
      * likewise Q by b*batch_q, and writes FP32 plane b of out_float. */
     int batch, batch_p, batch_q;
     float *out_float; /* kStoreFloat: [batch][rows][ld_out] */
+    /* Stream-K tail (kStoreRows, at most eight row blocks). CTAs form teams of
+     * r_blocks members, member i owning row block i, so that the members of a
+     * team walk the same weight tiles at the same time and share them through
+     * L2. The first dp_cols column blocks are processed whole, column block c by
+     * team c mod teams. The (column block, K block) iterations of the remaining
+     * sk_cols column blocks (fewer than there are teams) are cut into equal
+     * contiguous ranges, one per team; a range touches at most two column
+     * blocks, and each piece leaves its raw FP32 sums in slot 2*cta + piece of
+     * sk_partial ([slot][128][BN]). sk_fixup then adds the pieces of every tile
+     * in K order and applies the epilogue. sk_cols == 0 switches this off. */
+    int dp_cols, sk_cols;
+    float *sk_partial;
     const unsigned *skip_if_set; /* when non-NULL and *skip_if_set != 0 the kernel does nothing */
     const unsigned *run_if_set;  /* when non-NULL and *run_if_set == 0 the kernel does nothing */
 };
@@ -82,11 +94,9 @@ __device__ __forceinline__ void report(unsigned *status, volatile uint32_t *abor
     }
 }
 
-__device__ __forceinline__ void decode_unit(const GemmTask &task, int unit, int &rb, int &cb,
-                                            int &part, int &batch)
+__device__ __forceinline__ void locate_tile(const GemmTask &task, int tile, int &rb, int &cb,
+                                            int &batch)
 {
-    part = unit % task.split;
-    int tile = unit / task.split;
     const int per_batch = task.r_blocks * task.c_blocks;
     batch = tile / per_batch;
     tile -= batch * per_batch;
@@ -96,6 +106,155 @@ __device__ __forceinline__ void decode_unit(const GemmTask &task, int unit, int 
     int height = min(task.panel, task.r_blocks - panel * task.panel);
     cb = local / height;
     rb = panel * task.panel + local - cb * height;
+}
+
+/* One piece of work of a CTA: a tile, a K-block range and, for a stream-K
+ * piece, the slot its partial sums go to (slot < 0: the piece owns the whole K
+ * of its tile or is one of the uniform splits of the few-token modes). */
+struct Unit {
+    int rb, cb, part, batch, kb0, kb1, slot;
+};
+
+/* The item-th piece of work of worker `worker` out of `workers` (a worker is a
+ * CTA, or a pair of CTAs in the two-SM kernel); false when it has no more. */
+__device__ __forceinline__ bool fetch_unit(const GemmTask &task, int item, int worker, int workers,
+                                           Unit &u)
+{
+    int tile;
+    u.slot = -1;
+    if (task.sk_cols == 0) {
+        const long long unit = worker + static_cast<long long>(item) * workers;
+        if (unit >= 1ll * task.r_blocks * task.c_blocks * task.split * task.batch)
+            return false;
+        u.part = static_cast<int>(unit % task.split);
+        tile = static_cast<int>(unit / task.split);
+        u.kb0 = u.part * task.k_blocks_per_split;
+        u.kb1 = min(task.k_blocks, u.kb0 + task.k_blocks_per_split);
+        locate_tile(task, tile, u.rb, u.cb, u.batch);
+        return true;
+    }
+    const int teams = workers / task.r_blocks, team = worker / task.r_blocks;
+    if (team >= teams)
+        return false;
+    u.rb = worker - team * task.r_blocks;
+    u.part = 0, u.batch = 0;
+    const int whole = task.dp_cols > team ? (task.dp_cols - team + teams - 1) / teams : 0;
+    if (item < whole) {
+        u.cb = team + item * teams;
+        u.kb0 = 0, u.kb1 = task.k_blocks;
+        return true;
+    }
+    const int piece = item - whole;
+    if (piece > 1)
+        return false;
+    const long long total = 1ll * task.sk_cols * task.k_blocks;
+    const long long begin = team * total / teams, end = (team + 1) * total / teams;
+    if (begin >= end)
+        return false;
+    const long long first = begin / task.k_blocks;
+    const long long cut = min(end, (first + 1) * task.k_blocks);
+    if (piece == 0) {
+        u.cb = task.dp_cols + static_cast<int>(first);
+        u.kb0 = static_cast<int>(begin - first * task.k_blocks);
+        u.kb1 = static_cast<int>(cut - first * task.k_blocks);
+    } else {
+        if (end <= cut)
+            return false;
+        u.cb = task.dp_cols + static_cast<int>(first) + 1;
+        u.kb0 = 0;
+        u.kb1 = static_cast<int>(end - cut);
+    }
+    u.slot = 2 * worker + piece;
+    return true;
+}
+
+__host__ __device__ inline long long unit_count(const GemmTask &task)
+{
+    return 1ll * task.r_blocks * task.c_blocks * task.split * task.batch;
+}
+
+/* Epilogue of a stream-K piece: the raw FP32 sums of this thread's accumulator
+ * row, 128 bytes per step, to its row of the partial slot. `release` is called
+ * once every lane of the warp has read the last column of the accumulator. */
+template <int BN, typename Release>
+__device__ __forceinline__ void epilogue_partial(float *slot, uint32_t taddr, Release release)
+{
+#pragma unroll 1
+    for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + chunk * 32, acc);
+        tmem_ld_wait();
+        if (chunk == BN / 32 - 1)
+            release();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<uint4 *>(slot + chunk * 32 + i) =
+                make_uint4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    }
+}
+
+/* Epilogue of a whole tile, token rows on TMEM lanes: alpha, bias and
+ * beta*addend in FP32, one rounding, 64-column slabs staged with the 128-byte
+ * swizzle in this warp's two 4 KB buffers and written with TMA stores (which
+ * clip rows and columns beyond the matrix). `row` is this thread's row,
+ * `store_row` the first row of the warp's slab. */
+template <int BN, typename Release>
+__device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtensorMap *map_d,
+                                              uint32_t taddr, int row, int store_row, int col0,
+                                              int col_shift, int lane, uint8_t *slab,
+                                              uint32_t &slab_use, Release release)
+{
+#pragma unroll 1
+    for (int chunk = 0; chunk < BN / 64; ++chunk) {
+        uint32_t acc[2][32];
+        tmem_ld_32x32(taddr + chunk * 64, acc[0]);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+        tmem_ld_wait();
+        if (chunk == BN / 64 - 1)
+            release();
+        uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
+        /* the TMA store that last read this buffer must be done */
+        if (lane == 0)
+            tma_store_wait_read<1>();
+        __syncwarp();
+        const int cbase = col0 + chunk * 64;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = task.alpha * __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
+            const int c = cbase + piece * 8;
+            if (task.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (c + i < task.cols)
+                        v[i] += __bfloat162float(task.bias[c + i]);
+            }
+            if (task.beta != 0.f && row < task.rows) {
+                const __nv_bfloat16 *source =
+                    task.addend + static_cast<long long>(row) * task.ld_add + c;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (c + i < task.cols)
+                        v[i] = fmaf(task.beta, __bfloat162float(source[i]), v[i]);
+            }
+            uint4 packed;
+            packed.x = pack_bf16(v[0], v[1]);
+            packed.y = pack_bf16(v[2], v[3]);
+            packed.z = pack_bf16(v[4], v[5]);
+            packed.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                packed;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_d, buffer_smem, cbase - col_shift, store_row);
+            tma_store_commit();
+        }
+        ++slab_use;
+    }
 }
 
 template <int BN, int Stages, int Mode, int PMajor = kMajorK, int QMajor = kMajorK>
@@ -126,7 +285,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int units = task.r_blocks * task.c_blocks * task.split * task.batch;
     if (task.skip_if_set != nullptr && *task.skip_if_set != 0)
         return;
     if (task.run_if_set != nullptr && *task.run_if_set == 0)
@@ -165,18 +323,20 @@ __global__ void __launch_bounds__(kThreads, 1)
             /* The operand that is re-read by many tiles stays in L2; the one
              * that is read once per panel is streamed. With few row blocks the
              * column operand (weights) is the streamed one. */
+#ifdef CAMBLAS_EXPERIMENT_NOHINT
+            const uint64_t policy_p = keep, policy_q = keep;
+#else
             const uint64_t policy_p = task.r_blocks <= task.panel ? keep : stream;
             const uint64_t policy_q = task.r_blocks <= task.panel ? stream : keep;
+#endif
             uint32_t stage = 0, phase = 0;
             uint32_t armed = 0, armed_parity = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
-                int rb, cb, part, batch;
-                decode_unit(task, unit, rb, cb, part, batch);
-                int kb0 = part * task.k_blocks_per_split;
-                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
-                const int p_shift = batch * task.batch_p, q_shift = batch * task.batch_q;
-                for (int kb = kb0; kb < kb1; ++kb) {
+            Unit u;
+            for (int item = 0; ok && fetch_unit(task, item, blockIdx.x, gridDim.x, u); ++item) {
+                const int rb = u.rb, cb = u.cb;
+                const int p_shift = u.batch * task.batch_p, q_shift = u.batch * task.batch_q;
+                for (int kb = u.kb0; kb < u.kb1; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
                         report(task.status, abort, kRoleProducer);
                         ok = false;
@@ -228,10 +388,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x, ++local) {
-                int part = unit % task.split;
-                int kb0 = part * task.k_blocks_per_split;
-                int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
+            Unit u;
+            for (int item = 0; ok && fetch_unit(task, item, blockIdx.x, gridDim.x, u); ++item, ++local) {
+                const int kb0 = u.kb0, kb1 = u.kb1;
                 uint32_t buffer = local & 1, use = local >> 1;
                 if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
                     report(task.status, abort, kRoleMmaTmemEmpty);
@@ -276,9 +435,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint8_t *slab = staging + (warp - 2) * 8192;
         uint32_t local = 0;
         uint32_t slab_use = 0;
-        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
-            int rb, cb, part, batch;
-            decode_unit(task, unit, rb, cb, part, batch);
+        Unit u;
+        for (int item = 0; fetch_unit(task, item, blockIdx.x, gridDim.x, u); ++item, ++local) {
+            const int rb = u.rb, cb = u.cb, part = u.part, batch = u.batch;
             uint32_t buffer = local & 1, use = local >> 1;
             if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
                 report(task.status, abort, kRoleEpilogueFull);
@@ -289,75 +448,27 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int row = rb * kBlockR + quarter * 32 + lane;
             const int col0 = cb * BN;
 
-            if constexpr (Mode == kStoreRows) {
+            auto release = [&]() {
+                /* accumulator fully read: hand the TMEM buffer back */
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&tmem_empty[buffer]);
+            };
+            if (Mode == kStoreRows && u.slot >= 0) {
+                float *slot = task.sk_partial +
+                              (static_cast<long long>(u.slot) * kBlockR + quarter * 32 + lane) * BN;
+                epilogue_partial<BN>(slot, taddr, release);
+            } else if constexpr (Mode == kStoreRows) {
                 const CUtensorMap *map_d = &map_d0;
-                __nv_bfloat16 *out = task.out;
-                const __nv_bfloat16 *addend = task.addend;
                 int col_shift = 0;
                 if (col0 >= task.cut0) {
                     bool third = col0 >= task.cut1;
                     map_d = third ? &map_d2 : &map_d1;
                     col_shift = third ? task.cut1 : task.cut0;
                 }
-#pragma unroll 1
-                for (int chunk = 0; chunk < BN / 64; ++chunk) {
-                    uint32_t acc[2][32];
-                    tmem_ld_32x32(taddr + chunk * 64, acc[0]);
-                    tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
-                    tmem_ld_wait();
-                    if (chunk == BN / 64 - 1) {
-                        /* accumulator fully read: hand the TMEM buffer back */
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0)
-                            mbar_arrive(&tmem_empty[buffer]);
-                    }
-                    uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
-                    /* the TMA store that last read this buffer must be done */
-                    if (lane == 0)
-                        tma_store_wait_read<1>();
-                    __syncwarp();
-                    const int cbase = col0 + chunk * 64;
-#pragma unroll
-                    for (int piece = 0; piece < 8; ++piece) {
-                        float v[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            v[i] = task.alpha *
-                                   __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
-                        const int c = cbase + piece * 8;
-                        if (task.bias != nullptr) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (c + i < task.cols)
-                                    v[i] += __bfloat162float(task.bias[c + i]);
-                        }
-                        if (task.beta != 0.f && row < task.rows) {
-                            const __nv_bfloat16 *source =
-                                addend + static_cast<long long>(row) * task.ld_add + c;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (c + i < task.cols)
-                                    v[i] = fmaf(task.beta, __bfloat162float(source[i]), v[i]);
-                        }
-                        uint4 packed;
-                        packed.x = pack_bf16(v[0], v[1]);
-                        packed.y = pack_bf16(v[2], v[3]);
-                        packed.z = pack_bf16(v[4], v[5]);
-                        packed.w = pack_bf16(v[6], v[7]);
-                        *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 +
-                                                   ((piece ^ (lane & 7)) << 4)) = packed;
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(map_d, buffer_smem, cbase - col_shift,
-                                     rb * kBlockR + quarter * 32);
-                        tma_store_commit();
-                    }
-                    ++slab_use;
-                }
-                (void)out;
+                epilogue_rows<BN>(task, map_d, taddr, row, rb * kBlockR + quarter * 32, col0,
+                                  col_shift, lane, slab, slab_use, release);
             } else if constexpr (Mode == kStoreFloat) {
                 /* FP32 plane of a batched product: this thread owns one row and
                  * writes 32 consecutive floats per piece (128 bytes). */
@@ -471,6 +582,83 @@ __global__ void gemm_split_reduce(int rows, int cols, int split, long long plane
     if (beta != 0.f)
         v = fmaf(beta, __bfloat162float(addend[c * ld_add + r]), v);
     out[c * ld_out + r] = __float2bfloat16_rn(v);
+}
+
+/* Second pass of the stream-K tail: add the pieces of every stream-K tile in
+ * ascending K order, apply alpha, bias and beta*addend, round once, store BF16.
+ * One thread per eight consecutive columns; blockIdx.x is the stream-K column
+ * block, blockIdx.z the row block, `grid` the number of CTAs the product kernel
+ * ran with. out1/out2 are the extra outputs of a packed projection (columns
+ * from cut0 and cut1 on). */
+template <int BN>
+__global__ void __launch_bounds__(256)
+    sk_fixup(const GemmTask task, int grid, __nv_bfloat16 *out1, long long ld1,
+             __nv_bfloat16 *out2, long long ld2)
+{
+    const int vector = blockIdx.y * 256 + threadIdx.x;
+    const int r = vector / (BN / 8), c8 = (vector % (BN / 8)) * 8;
+    const int rb = blockIdx.z, cb = task.dp_cols + blockIdx.x;
+    const int row = rb * kBlockR + r, col = cb * BN + c8;
+    if (row >= task.rows || col >= task.cols)
+        return;
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int teams = grid / task.r_blocks;
+    const long long total = 1ll * task.sk_cols * task.k_blocks;
+    const long long tile_begin = 1ll * blockIdx.x * task.k_blocks, tile_end = tile_begin + task.k_blocks;
+    int team = static_cast<int>(tile_begin * teams / total);
+    team = team > 0 ? team - 1 : 0;
+    for (; team < teams; ++team) {
+        const long long begin = team * total / teams, end = (team + 1) * total / teams;
+        if (begin >= tile_end)
+            break;
+        if (end <= tile_begin || begin >= end)
+            continue;
+        /* a team's first piece lies in the column block its range starts in */
+        const int piece = begin < tile_begin ? 1 : 0;
+        const int cta = team * task.r_blocks + rb;
+        const float *source =
+            task.sk_partial + ((static_cast<long long>(2 * cta + piece)) * kBlockR + r) * BN + c8;
+        const float4 low = *reinterpret_cast<const float4 *>(source);
+        const float4 high = *reinterpret_cast<const float4 *>(source + 4);
+        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
+        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
+    }
+    __nv_bfloat16 *out = task.out;
+    long long ld = task.ld_out;
+    int shift = 0, limit = min(task.cols, task.cut0);
+    if (col >= task.cut0) {
+        const bool third = col >= task.cut1;
+        out = third ? out2 : out1;
+        ld = third ? ld2 : ld1;
+        shift = third ? task.cut1 : task.cut0;
+        limit = third ? task.cols : task.cut1;
+    }
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[i] = task.alpha * sum[i];
+        if (col + i < task.cols) {
+            if (task.bias != nullptr)
+                v[i] += __bfloat162float(task.bias[col + i]);
+            if (task.beta != 0.f)
+                v[i] = fmaf(task.beta,
+                            __bfloat162float(
+                                task.addend[static_cast<long long>(row) * task.ld_add + col + i]),
+                            v[i]);
+        }
+    }
+    __nv_bfloat16 *target = out + static_cast<long long>(row) * ld + (col - shift);
+    if (col + 8 <= limit) {
+        uint4 packed;
+        packed.x = pack_bf16(v[0], v[1]);
+        packed.y = pack_bf16(v[2], v[3]);
+        packed.z = pack_bf16(v[4], v[5]);
+        packed.w = pack_bf16(v[6], v[7]);
+        *reinterpret_cast<uint4 *>(target) = packed;
+    } else {
+        for (int i = 0; i < 8 && col + i < limit; ++i)
+            target[i] = __float2bfloat16_rn(v[i]);
+    }
 }
 
 } // namespace sm100

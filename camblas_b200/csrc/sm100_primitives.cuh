@@ -1,8 +1,8 @@
 /*
  * Thin inline-PTX wrappers for the Blackwell (sm_100a) data path: mbarriers,
  * TMA tensor copies, tensor memory (TMEM) management and tcgen05 MMA issue.
- * Everything here is single-CTA (cta_group::1); no copy in this file uses a
- * cluster multicast qualifier.
+ * Everything here is single-CTA (cta_group::1); every copy has exactly one
+ * destination CTA.
  */
 #pragma once
 
@@ -14,10 +14,18 @@
 namespace sm100
 {
 
-/* Upper bound on polls of one barrier before a role gives up. Each poll of
- * mbarrier.try_wait may itself block for a hardware-defined slice, so the bound
- * is in the range of seconds; a healthy pipeline needs microseconds. */
+/* Bounds of one barrier wait: a poll count and, because a poll of
+ * mbarrier.try_wait may itself block for a hardware-defined slice, a wall-clock
+ * limit of two seconds. A healthy pipeline needs microseconds. */
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    return now;
+}
 
 /* Status codes written to the context status word when a bounded wait gives up. */
 enum StatusRole : unsigned {
@@ -78,11 +86,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
  * raised the CTA-wide abort flag; the caller then leaves its loop. */
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort)
 {
+    unsigned long long started = 0;
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity))
             return true;
-        if ((spin & 255u) == 255u && *abort)
-            return false;
+        if ((spin & 255u) == 255u) {
+            if (*abort)
+                return false;
+            const unsigned long long now = global_timer_ns();
+            if (started == 0)
+                started = now;
+            else if (now - started > kWaitLimitNs)
+                return false;
+        }
     }
     return false;
 }

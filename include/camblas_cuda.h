@@ -224,7 +224,7 @@ int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status);
 /* No counterpart in the reference ABI. Chooses the BF16 kernel family for the
  * next calls on this context: 0 automatic, 1 generic CUDA-core kernel,
  * 2 skinny weight-streaming kernel, 3 tcgen05 kernel, 4 tcgen05 with swapped
- * operands and split-K. A forced family that cannot take the operands fails
+ * operands and split-K, 5 tcgen05 kernel with two-SM (CTA pair) tiles. A forced family that cannot take the operands fails
  * with status -1 instead of silently using another one. For tests. */
 int camblas_cuda_force_kernel(camblas_cuda_context *context, int family);
 
