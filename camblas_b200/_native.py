@@ -61,6 +61,7 @@ _SIGNATURES = {
     "reset_stats": ([_P], _I),
     "device_status": ([_P, ct.POINTER(ct.c_uint)], _I),
     "force_kernel": ([_P, _I], _I),
+    "kernel_launches": ([_P, ct.POINTER(_U64)], _I),
     "bgemm": ([_P, ct.c_char, ct.c_char, _I, _I, _I, _F, _P, _I, _P, _I, _F, _P, _I], _I),
     "sgemm": ([_P, ct.c_char, ct.c_char, _I, _I, _I, _F, _P, _I, _P, _I, _F, _P, _I], _I),
     "dgemm": (
@@ -167,6 +168,12 @@ class Context:
     def call(self, name, *arguments):
         """Call ``camblas_cuda_<name>(handle, *arguments)`` and check its status."""
         _check(getattr(library(), "camblas_cuda_" + name)(self.handle, *arguments), self.handle)
+
+    def kernel_launches(self):
+        """Return how many CUDA kernels this context has enqueued so far."""
+        count = _U64(0)
+        _check(library().camblas_cuda_kernel_launches(self.handle, ct.byref(count)), self.handle)
+        return count.value
 
     def device_status(self):
         """Wait for the stream and return (then clear) the device status word."""

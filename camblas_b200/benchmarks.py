@@ -209,28 +209,33 @@ def config5(results):
         del a, b
 
 
-def single(kind, tokens, outputs, inner, launches=5):
-    """Run one product `launches` times without a graph and print the mean time."""
+def single(kind, tokens, outputs, inner, launches=20):
+    """Run one product `launches` times without a graph; print its mean time and, for
+    BF16, the time of torch's own (cuBLAS) linear on the same tensors in the same process."""
     x = torch.randn(tokens, inner, device="cuda").bfloat16()
     weight = (torch.randn(outputs, inner, device="cuda") * 0.02).bfloat16()
     if kind == "fp8":
         q, q_scale = _kernels.fp8_quantize(x)
         w8, w_scale = quantise_weight_blocks(weight)
-        call = lambda: _kernels.fp8_block_gemm(q, q_scale, w8, w_scale)  # noqa: E731
+        calls = {"ours": lambda: _kernels.fp8_block_gemm(q, q_scale, w8, w_scale)}
     else:
-        call = lambda: _kernels.linear(x, weight)  # noqa: E731
-    call()
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for _ in range(launches):
+        calls = {"ours": lambda: _kernels.linear(x, weight),
+                 "cublas": lambda: torch.nn.functional.linear(x, weight)}
+    result = {"single": [kind, tokens, outputs, inner]}
+    for name, call in calls.items():
         call()
-    end.record()
-    torch.cuda.synchronize()
-    microseconds = begin.elapsed_time(end) * 1e3 / launches
-    print(json.dumps({"single": [kind, tokens, outputs, inner], "us": round(microseconds, 1),
-                      "tflops": round(2 * tokens * outputs * inner / microseconds / 1e6, 1),
-                      "status": _native.context(0).device_status()}), flush=True)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(launches):
+            call()
+        end.record()
+        torch.cuda.synchronize()
+        microseconds = begin.elapsed_time(end) * 1e3 / launches
+        result[name + "_us"] = round(microseconds, 1)
+        result[name + "_tflops"] = round(2 * tokens * outputs * inner / microseconds / 1e6, 1)
+    result["status"] = _native.context(0).device_status()
+    print(json.dumps(result), flush=True)
 
 
 CONFIGS = {1: config1, 2: config2, 3: config3, 4: config4, 5: config5}

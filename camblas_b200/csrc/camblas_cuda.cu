@@ -157,6 +157,14 @@ extern "C" int camblas_cuda_reset_stats(camblas_cuda_context *context)
     return 0;
 }
 
+extern "C" int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *count)
+{
+    if (!context || !count)
+        return fail(nullptr, "invalid launch count output", 1);
+    *count = context->kernel_launches.load(std::memory_order_relaxed);
+    return 0;
+}
+
 extern "C" int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status)
 {
     return guarded(context, [&] {

@@ -40,6 +40,7 @@ struct camblas_cuda_context {
     unsigned long long *guard_hits_device = nullptr; /* the same word as the device sees it */
     EncodeTiledFn encode = nullptr;
     std::atomic<uint64_t> counts[8] = {};
+    std::atomic<uint64_t> kernel_launches{0}; /* every kernel this context put on its stream */
     char error[256] = "";
 };
 
@@ -109,6 +110,8 @@ template <typename Function> int guarded(camblas_cuda_context *context, Function
 inline int launched(camblas_cuda_context *context, const char *what)
 {
     cudaError_t error = cudaGetLastError();
+    if (context && error == cudaSuccess)
+        context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
     return error == cudaSuccess ? 0 : fail(context, what, error);
 }
 

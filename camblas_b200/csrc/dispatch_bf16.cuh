@@ -79,6 +79,10 @@ template <int PMajor, int QMajor> int prepare_pair_kernels()
     status |= int(cudaFuncSetAttribute(gemm_bf16_pair<128, 8, PMajor, QMajor>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        PairSmem<128, 8>::kTotal));
+    if constexpr (QMajor == kMajorK)
+        status |= int(cudaFuncSetAttribute(gemm_bf16_pair<0, 6, PMajor, QMajor>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           PairSmem<256, 6>::kTotal));
     return status;
 }
 
@@ -273,7 +277,7 @@ cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensor
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(2 * pairs);
     config.blockDim = dim3(sm100::kThreads);
-    config.dynamicSmemBytes = sm100::PairSmem<BN, Stages>::kTotal;
+    config.dynamicSmemBytes = sm100::PairSmem<(BN ? BN : 256), Stages>::kTotal;
     config.stream = context->stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
@@ -291,6 +295,12 @@ cudaError_t launch_pair_width(camblas_cuda_context *context, int bn, int pairs, 
                               const CUtensorMap &q, const CUtensorMap &d0, const CUtensorMap &d1,
                               const CUtensorMap &d2, const sm100::GemmTask &task)
 {
+    if (task.width != 0) {
+        if constexpr (QMajor == sm100::kMajorK)
+            return launch_pair<0, 6, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
+        else
+            return cudaErrorInvalidValue;
+    }
     if (bn == 256)
         return launch_pair<256, 6, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
     return launch_pair<128, 8, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
@@ -314,30 +324,68 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
     task.run_if_set = x.run_if_set;
     const bool packed = x.cut0 < x.m;
     const int pairs_max = context->sm_count / 2;
+    task.out1 = x.c1, task.out2 = x.c2;
+    task.ld_out1 = x.ldc1, task.ld_out2 = x.ldc2;
+    /* Tile width. With a K-major weight the width may be any multiple of 16:
+     * take the one whose tile count fills whole waves of CTA pairs best (wide
+     * tiles are a little more efficient per flop, hence the weight on width).
+     * The alternative for 256-column tiles is the stream-K tail. Costs are in
+     * microseconds from rough steady-state rates; only their order matters. */
+    const double pair_flops_per_us = 2 * 1.45e15 / 148.0 / 1e6;
+    auto tile_us = [&](int width) {
+        return 2.0 * 256 * width * x.k / pair_flops_per_us * (1.0 + 0.25 * (256 - width) / 256.0);
+    };
     int bn = x.m <= 128 ? 128 : 256;
-    if (packed && (x.cut0 % bn != 0 || x.cut1 % bn != 0)) {
+    double best = 1e30;
+    int best_width = 0;
+    if (x.ta && x.m > 128 && (!packed || (x.cut0 % 16 == 0 && x.cut1 % 16 == 0))) {
+        for (int width = 128; width <= 256; width += 16) {
+            long long tiles = 1ll * task.r_blocks * ((x.m + width - 1) / width);
+            double cost = double((tiles + pairs_max - 1) / pairs_max) * tile_us(width);
+            if (cost < best - 1e-9)
+                best = cost, best_width = width;
+        }
+    }
+    if (packed && best_width == 0 && (x.cut0 % bn != 0 || x.cut1 % bn != 0)) {
         bn = 128;
         if (x.cut0 % bn != 0 || x.cut1 % bn != 0)
             return fail(context, "packed projection widths must be multiples of 128", 1);
     }
+    bool stream_k = false;
+    if (task.r_blocks <= 8 && pairs_max / task.r_blocks >= 2 && task.k_blocks >= 16 &&
+        x.run_if_set == nullptr && !(packed && (x.cut0 % bn != 0 || x.cut1 % bn != 0))) {
+        const int columns = (x.m + bn - 1) / bn;
+        const int teams = pairs_max / task.r_blocks;
+        const int rest = columns % teams;
+        if (rest != 0) {
+            const double second_pass =
+                6.0 + double(rest + teams) * task.r_blocks * 256 * bn * 8 / 5.0e6;
+            const double cost = (double(columns) / teams) * tile_us(bn) + second_pass;
+            const double plain = double((columns + teams - 1) / teams) * tile_us(bn);
+            if (cost < plain && cost < best) {
+                stream_k = true;
+                best_width = 0;
+            }
+        }
+    }
+    if (best_width != 0) {
+        const long long tiles = 1ll * task.r_blocks * ((x.m + bn - 1) / bn);
+        const double plain = double((tiles + pairs_max - 1) / pairs_max) * tile_us(bn);
+        if (plain <= best)
+            best_width = 0; /* the fixed-width kernel does as well */
+    }
+    if (best_width != 0)
+        bn = best_width, task.width = best_width;
     task.c_blocks = (x.m + bn - 1) / bn;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
-    if (task.r_blocks <= 8 && pairs_max / task.r_blocks >= 2) {
+    if (stream_k) {
         const int teams = pairs_max / task.r_blocks;
         const int rest = task.c_blocks % teams;
-        const double tile_us = 2.0 * 128 * bn * x.k / (1.45e15 / 148.0 / 1e6);
-        const double recovered = (1.0 - double(rest) / teams) * tile_us;
-        const double second_pass =
-            3.0 + double(rest + teams) * task.r_blocks * 256 * bn * 8 / 5.0e6;
-        if (rest != 0 && task.k_blocks >= 16 && x.run_if_set == nullptr &&
-            recovered > second_pass) {
-            task.dp_cols = task.c_blocks - rest, task.sk_cols = rest;
-            int status =
-                reserve_scratch(context, size_t(4) * pairs_max * 128 * bn * sizeof(float));
-            if (status != 0)
-                return status;
-            task.sk_partial = static_cast<float *>(context->scratch);
-        }
+        task.dp_cols = task.c_blocks - rest, task.sk_cols = rest;
+        int status = reserve_scratch(context, size_t(4) * pairs_max * 128 * bn * sizeof(float));
+        if (status != 0)
+            return status;
+        task.sk_partial = static_cast<float *>(context->scratch);
     }
     long long units = 1ll * task.r_blocks * task.c_blocks;
     int pairs = (units < pairs_max && task.sk_cols == 0) ? int(units) : pairs_max;
@@ -370,6 +418,7 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
         error = launch_pair_width<kMajorMN, kMajorMN>(context, bn, pairs, p, q, d0, d1, d2, task);
     if (error != cudaSuccess)
         return fail(context, "two-SM tcgen05 BF16 GEMM", error);
+    context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
     if (task.sk_cols == 0)
         return 0;
     dim3 grid(task.sk_cols, 256 * bn / 8 / 256, task.r_blocks);
@@ -532,7 +581,9 @@ inline int run_product(camblas_cuda_context *context, const Product &x)
     bool skinny_ok = x.ta && !x.tb && aligned16(x.a) && x.lda % 8 == 0 && x.n <= 4;
     int family = context->forced_family;
     if (family == kAuto) {
-        if (skinny_ok)
+        /* one token streams best on CUDA cores; from two tokens on the swapped
+         * tensor-core kernel stays at HBM speed while the FMA loop would not */
+        if (skinny_ok && (x.n == 1 || !swapped))
             family = kSkinny;
         else if (swapped && x.n <= 64)
             family = kTensorSwapped;

@@ -125,18 +125,26 @@ template <int BN, int Stages> struct PairSmem {
     static constexpr int kTotal = Stages * kStageBytes + kStagingBytes + 256 + 1024;
 };
 
-/* task.r_blocks counts 256-row blocks here; everything else as in GemmTask. */
-template <int BN, int Stages, int PMajor = kMajorK, int QMajor = kMajorK>
+/* task.r_blocks counts 256-row blocks here; everything else as in GemmTask.
+ * BNT is the tile width, or 0 when the width comes from task.width at run time
+ * (any multiple of 16 from 64 to 256; Q must then be K-major and the stage
+ * layout and TMEM buffers are those of the 256-column tile). */
+template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_d0,
                    const __grid_constant__ CUtensorMap map_d1,
                    const __grid_constant__ CUtensorMap map_d2, const GemmTask task)
 {
-    using Layout = PairSmem<BN, Stages>;
-    constexpr uint32_t kTmemColumns = BN * 2;
-    constexpr int kHalf = BN / 2;
-    static_assert(BN == 256 || BN == 128, "pair tiles are 256 or 128 columns wide");
+    constexpr bool kDynamic = BNT == 0;
+    constexpr int kLayoutWidth = kDynamic ? 256 : BNT;
+    using Layout = PairSmem<kLayoutWidth, Stages>;
+    constexpr uint32_t kTmemColumns = kLayoutWidth * 2;
+    static_assert(BNT == 256 || BNT == 128 || BNT == 0, "pair tiles: 256, 128 or run-time width");
+    static_assert(!kDynamic || QMajor == kMajorK, "run-time width needs a K-major Q operand");
+    const int BN = kDynamic ? task.width : BNT;
+    const int kHalf = BN / 2;
+    const uint32_t stage_bytes = Layout::kPBytes + kHalf * kBlockK * 2; /* bytes one CTA loads */
 
     extern __shared__ uint8_t raw_smem[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -201,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     uint8_t *q_tile = p_tile + Layout::kPBytes;
                     const uint32_t barrier = map_to_rank(smem_u32(&full[stage]), 0);
                     if (leader)
-                        mbar_arrive_expect_tx(&full[stage], 2 * Layout::kStageBytes);
+                        mbar_arrive_expect_tx(&full[stage], 2 * stage_bytes);
                     if constexpr (PMajor == kMajorK) {
                         tma_load_2d_pair(p_tile, &map_p, barrier, kb * kBlockK, p_row, policy_p);
                     } else {
@@ -213,7 +221,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if constexpr (QMajor == kMajorK) {
                         tma_load_2d_pair(q_tile, &map_q, barrier, kb * kBlockK, q_row, policy_q);
                     } else {
-#pragma unroll
                         for (int g = 0; g < kHalf / 64; ++g)
                             tma_load_2d_pair(q_tile + g * 8192, &map_q, barrier, q_row + g * 64,
                                              kb * kBlockK, policy_q);
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             /* ---- MMA issuer (leader only) ---- */
-            constexpr uint32_t idesc = make_idesc(1, kPairRows, BN, PMajor, QMajor);
+            const uint32_t idesc = make_idesc(1, kPairRows, BN, PMajor, QMajor);
             uint32_t stage = 0, phase = 0, local = 0;
             bool ok = true;
             Unit u;
@@ -244,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + buffer * BN;
+                const uint32_t tmem_d = tmem_base + buffer * kLayoutWidth;
                 for (int kb = u.kb0; kb < u.kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
@@ -294,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tcgen05_fence_after();
             const uint32_t taddr =
-                tmem_base + buffer * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+                tmem_base + buffer * kLayoutWidth + (static_cast<uint32_t>(quarter * 32) << 16);
             const int row0 = u.rb * kPairRows + rank * kBlockR + quarter * 32;
             const int col0 = u.cb * BN;
             auto release = [&]() {
@@ -303,11 +310,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                     mbar_arrive_cluster(map_to_rank(smem_u32(&tmem_empty[buffer]), 0));
             };
-            if (u.slot >= 0) {
+            if constexpr (kDynamic) {
+                epilogue_rows_dynamic(task, &map_d0, &map_d1, &map_d2, taddr, row0 + lane, row0, col0,
+                                      BN, lane, slab, slab_use, release);
+            } else if (u.slot >= 0) {
                 float *slot = task.sk_partial +
                               ((static_cast<long long>(u.slot) * 2 + rank) * kBlockR +
-                               quarter * 32 + lane) * BN;
-                epilogue_partial<BN>(slot, taddr, release);
+                               quarter * 32 + lane) * BNT;
+                epilogue_partial<kLayoutWidth>(slot, taddr, release);
             } else {
                 const CUtensorMap *map_d = &map_d0;
                 int col_shift = 0;
@@ -316,8 +326,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                     map_d = third ? &map_d2 : &map_d1;
                     col_shift = third ? task.cut1 : task.cut0;
                 }
-                epilogue_rows<BN>(task, map_d, taddr, row0 + lane, row0, col0, col_shift, lane, slab,
-                                  slab_use, release);
+                epilogue_rows<kLayoutWidth>(task, map_d, taddr, row0 + lane, row0, col0, col_shift,
+                                            lane, slab, slab_use, release);
             }
         }
         if (lane == 0)

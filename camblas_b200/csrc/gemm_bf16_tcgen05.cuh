@@ -50,6 +50,9 @@ struct GemmTask {
      * [0,cut0) go to out, [cut0,cut1) to out1, [cut1,cols) to out2. cut0 and
      * cut1 are multiples of BN; cut0 == cols disables the feature. */
     int cut0, cut1;
+    __nv_bfloat16 *out1, *out2; /* second and third output of a packed projection */
+    long long ld_out1, ld_out2;
+    int width; /* tile width of the two-SM kernel when it is chosen at run time */
     /* Batch of independent products over stacked operands (batch >= 1): product
      * b reads P rows (K-major) or P K indices (MN-major) offset by b*batch_p,
      * likewise Q by b*batch_q, and writes FP32 plane b of out_float. */
@@ -254,6 +257,139 @@ __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtens
             tma_store_commit();
         }
         ++slab_use;
+    }
+}
+
+/* alpha*acc + bias + beta*addend for eight consecutive columns of one row. */
+__device__ __forceinline__ void finish8(const GemmTask &task, int row, int c, const uint32_t *acc,
+                                        float (&v)[8])
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        v[i] = task.alpha * __uint_as_float(acc[i]);
+    if (task.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c + i < task.cols)
+                v[i] += __bfloat162float(task.bias[c + i]);
+    }
+    if (task.beta != 0.f && row < task.rows) {
+        const __nv_bfloat16 *source = task.addend + static_cast<long long>(row) * task.ld_add + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c + i < task.cols)
+                v[i] = fmaf(task.beta, __bfloat162float(source[i]), v[i]);
+    }
+}
+
+/* Store sixteen consecutive columns of one row straight from registers,
+ * choosing the output of a packed projection by column. Used for the ragged
+ * right edge of a tile whose width is not a multiple of 64 and for slabs that
+ * straddle two outputs; cut points are multiples of 16, so a group of sixteen
+ * never does. */
+__device__ __forceinline__ void store_direct16(const GemmTask &task, int row, int c,
+                                               const uint32_t *acc)
+{
+    if (row >= task.rows || c >= task.cols)
+        return;
+    __nv_bfloat16 *out = task.out;
+    long long ld = task.ld_out;
+    int shift = 0, limit = min(task.cols, task.cut0);
+    if (c >= task.cut0) {
+        const bool third = c >= task.cut1;
+        out = third ? task.out2 : task.out1;
+        ld = third ? task.ld_out2 : task.ld_out1;
+        shift = third ? task.cut1 : task.cut0;
+        limit = third ? task.cols : task.cut1;
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float v[8];
+        const int cc = c + half * 8;
+        finish8(task, row, cc, acc + half * 8, v);
+        __nv_bfloat16 *target = out + static_cast<long long>(row) * ld + (cc - shift);
+        if (cc + 8 <= limit) {
+            uint4 packed;
+            packed.x = pack_bf16(v[0], v[1]);
+            packed.y = pack_bf16(v[2], v[3]);
+            packed.z = pack_bf16(v[4], v[5]);
+            packed.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4 *>(target) = packed;
+        } else {
+            for (int i = 0; i < 8 && cc + i < limit; ++i)
+                target[i] = __float2bfloat16_rn(v[i]);
+        }
+    }
+}
+
+/* Epilogue of a whole tile whose width (a multiple of 16 up to 256) is chosen
+ * at run time. Full 64-column slabs that lie in one output go through the
+ * swizzled staging buffers and TMA stores like epilogue_rows; a slab that
+ * straddles two outputs of a packed projection and the ragged right edge are
+ * stored straight from registers. */
+template <typename Release>
+__device__ __forceinline__ void
+epilogue_rows_dynamic(const GemmTask &task, const CUtensorMap *map0, const CUtensorMap *map1,
+                      const CUtensorMap *map2, uint32_t taddr, int row, int store_row, int col0,
+                      int width, int lane, uint8_t *slab, uint32_t &slab_use, Release release)
+{
+    const int full = width >> 6, tail = (width & 63) >> 4;
+#pragma unroll 1
+    for (int chunk = 0; chunk < full; ++chunk) {
+        uint32_t acc[2][32];
+        tmem_ld_32x32(taddr + chunk * 64, acc[0]);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+        tmem_ld_wait();
+        if (chunk == full - 1 && tail == 0)
+            release();
+        const int cbase = col0 + chunk * 64;
+        const bool straddles = (cbase < task.cut0 && task.cut0 < cbase + 64) ||
+                               (cbase < task.cut1 && task.cut1 < cbase + 64);
+        if (straddles) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+                store_direct16(task, row, cbase + g * 16, &acc[g >> 1][(g & 1) * 16]);
+            continue;
+        }
+        const CUtensorMap *map_d = map0;
+        int col_shift = 0;
+        if (cbase >= task.cut0) {
+            const bool third = cbase >= task.cut1;
+            map_d = third ? map2 : map1;
+            col_shift = third ? task.cut1 : task.cut0;
+        }
+        uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
+        if (lane == 0)
+            tma_store_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            float v[8];
+            finish8(task, row, cbase + piece * 8, &acc[piece >> 2][(piece & 3) * 8], v);
+            uint4 packed;
+            packed.x = pack_bf16(v[0], v[1]);
+            packed.y = pack_bf16(v[2], v[3]);
+            packed.z = pack_bf16(v[4], v[5]);
+            packed.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                packed;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_d, buffer_smem, cbase - col_shift, store_row);
+            tma_store_commit();
+        }
+        ++slab_use;
+    }
+#pragma unroll 1
+    for (int g = 0; g < tail; ++g) {
+        uint32_t acc[16];
+        tmem_ld_32x16(taddr + full * 64 + g * 16, acc);
+        tmem_ld_wait();
+        if (g == tail - 1)
+            release();
+        store_direct16(task, row, col0 + full * 64 + g * 16, acc);
     }
 }
 

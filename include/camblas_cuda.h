@@ -221,6 +221,10 @@ int camblas_cuda_swiglu(camblas_cuda_context *context, int dtype, uint64_t count
  * inside the pipelined kernels completed; otherwise a code naming the wait that
  * gave up (role in bits 0-3, CTA index above). Clears the word. */
 int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status);
+/* No counterpart in the reference ABI. Number of CUDA kernels this context has
+ * enqueued since it was created (every launch, including reduction and fix-up
+ * passes; graph replays are not counted). */
+int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *count);
 /* No counterpart in the reference ABI. Chooses the BF16 kernel family for the
  * next calls on this context: 0 automatic, 1 generic CUDA-core kernel,
  * 2 skinny weight-streaming kernel, 3 tcgen05 kernel, 4 tcgen05 with swapped
