@@ -24,6 +24,10 @@
 #include "gemm_generic.cuh"
 #include "gemv_skinny.cuh"
 
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
 namespace host
 {
 
@@ -332,14 +336,28 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
      * The alternative for 256-column tiles is the stream-K tail. Costs are in
      * microseconds from rough steady-state rates; only their order matters. */
     const double pair_flops_per_us = 2 * 1.45e15 / 148.0 / 1e6;
+    /* A K block costs the longer of its MMA time (two cycles per tile column)
+     * and the time to bring its operands in (16 KB of P plus 64 bytes per column
+     * at about 65 bytes per cycle and SM), so narrow tiles are bound by loads. */
     auto tile_us = [&](int width) {
-        return 2.0 * 256 * width * x.k / pair_flops_per_us * (1.0 + 0.25 * (256 - width) / 256.0);
+        const double cycles = std::max(2.0 * width, (16384.0 + 64.0 * width) / 65.0);
+        return 2.0 * 256 * 256 * x.k / pair_flops_per_us * cycles / 512.0;
     };
+    const char *mode = std::getenv("CAMBLAS_B200_PAIR_MODE"); /* tuning aid: sk, width=<n>, plain */
     int bn = x.m <= 128 ? 128 : 256;
     double best = 1e30;
     int best_width = 0;
-    if (x.ta && x.m > 128 && (!packed || (x.cut0 % 16 == 0 && x.cut1 % 16 == 0))) {
+    int forced_width = 0;
+    if (mode != nullptr && std::strncmp(mode, "width=", 6) == 0)
+        forced_width = std::atoi(mode + 6);
+    /* Measured on B200, tiles narrower than 256 columns are bound by operand
+     * loads and never beat 256-column tiles with or without the stream-K tail on
+     * the Llama shapes, so a run-time width is used only on request. */
+    if (forced_width != 0 && x.ta && x.m > 128 &&
+        (!packed || (x.cut0 % 16 == 0 && x.cut1 % 16 == 0))) {
         for (int width = 128; width <= 256; width += 16) {
+            if (forced_width != 0 && width != forced_width)
+                continue;
             long long tiles = 1ll * task.r_blocks * ((x.m + width - 1) / width);
             double cost = double((tiles + pairs_max - 1) / pairs_max) * tile_us(width);
             if (cost < best - 1e-9)
@@ -357,12 +375,15 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
         const int columns = (x.m + bn - 1) / bn;
         const int teams = pairs_max / task.r_blocks;
         const int rest = columns % teams;
-        if (rest != 0) {
+        /* a long tail (most teams busy anyway) gains less than the second pass costs */
+        if (rest != 0 && (2 * rest <= teams || (mode != nullptr && std::strcmp(mode, "sk") == 0))) {
             const double second_pass =
                 6.0 + double(rest + teams) * task.r_blocks * 256 * bn * 8 / 5.0e6;
             const double cost = (double(columns) / teams) * tile_us(bn) + second_pass;
             const double plain = double((columns + teams - 1) / teams) * tile_us(bn);
-            if (cost < plain && cost < best) {
+            const bool forced = mode != nullptr && std::strcmp(mode, "sk") == 0;
+            if ((cost < plain && cost < best && forced_width == 0 &&
+                 !(mode != nullptr && std::strcmp(mode, "plain") == 0)) || forced) {
                 stream_k = true;
                 best_width = 0;
             }
@@ -371,7 +392,7 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
     if (best_width != 0) {
         const long long tiles = 1ll * task.r_blocks * ((x.m + bn - 1) / bn);
         const double plain = double((tiles + pairs_max - 1) / pairs_max) * tile_us(bn);
-        if (plain <= best)
+        if (plain <= best && forced_width == 0)
             best_width = 0; /* the fixed-width kernel does as well */
     }
     if (best_width != 0)

@@ -343,6 +343,8 @@ epilogue_rows_dynamic(const GemmTask &task, const CUtensorMap *map0, const CUten
         if (chunk == full - 1 && tail == 0)
             release();
         const int cbase = col0 + chunk * 64;
+        if (cbase >= task.cols)
+            continue; /* a slab wholly beyond the last column of the matrix */
         const bool straddles = (cbase < task.cut0 && task.cut0 < cbase + 64) ||
                                (cbase < task.cut1 && task.cut1 < cbase + 64);
         if (straddles) {

@@ -312,3 +312,25 @@ def test_tensor_family_takes_every_transpose_pair(rng, ta, tb, m, n, k):
             assert np.all(actual[:, m:] == NAN)
             error = oracle.rel_l2(oracle.bf16_values(actual[:, :m]), oracle.bf16_values(expected[:, :m]))
             assert error <= BF16_TOLERANCE, (family, error)
+
+
+@pytest.mark.parametrize("width", [128, 144, 208, 240])
+def test_two_sm_kernel_with_a_run_time_tile_width(rng, monkeypatch, width):
+    """CAMBLAS_B200_PAIR_MODE=width=<n> makes the two-SM kernel use tiles of n
+    columns (any multiple of 16): ragged last tiles, slabs beyond the matrix and a
+    packed projection whose outputs meet inside a tile all have to come out right."""
+    monkeypatch.setenv("CAMBLAS_B200_PAIR_MODE", f"width={width}")
+    for m, n, k in [(264, 130, 136), (1000, 300, 520), (592, 512, 2048)]:
+        w, x, c = normal_bits(rng, (m, k)), normal_bits(rng, (n, k)), normal_bits(rng, (n, m))
+        expected = c.copy()
+        oracle.bgemm("T", "N", m, n, k, 0.5, w, k, x, k, -1.0, expected, m)
+        actual = run_bgemm("T", "N", m, n, k, 0.5, w, k, x, k, -1.0, c, m, "tensor_pair")
+        error = oracle.rel_l2(oracle.bf16_values(actual), oracle.bf16_values(expected))
+        assert error <= BF16_TOLERANCE, (width, m, n, k, error)
+    rows, inner, widths = 200, 256, (400, 112, 112)
+    x, w = normal_bits(rng, (rows, inner)), normal_bits(rng, (sum(widths), inner))
+    expected = oracle.bf16_values(oracle.linear_bf16(x, w))
+    with _native.kernel_family("tensor_pair"):
+        q, k, v = _kernels.qkv_linear(bits_to_tensor(x), bits_to_tensor(w), *widths)
+    packed = torch.cat([q, k, v], dim=1).float().cpu().numpy()
+    assert oracle.rel_l2(packed, expected) <= BF16_TOLERANCE
