@@ -526,7 +526,7 @@ template <int Tokens> int launch_skinny(camblas_cuda_context *context, skinny::T
     /* K split: slices of at most 4096 elements (the staged tokens must fit in
      * shared memory) and enough CTAs for four per SM */
     int split = (task.depth + 4095) / 4096;
-    while (1ll * row_blocks * split < 4ll * sms && task.depth / (split * 2) >= 512)
+    while (1ll * row_blocks * split < 2ll * sms && task.depth / (split * 2) >= 512)
         split *= 2;
     int per = ((task.depth + split - 1) / split + 7) & ~7;
     split = (task.depth + per - 1) / per;

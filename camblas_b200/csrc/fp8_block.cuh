@@ -98,6 +98,13 @@ struct BlockTask {
 
 constexpr int kBlockDepth = 128; /* bytes = E4M3 elements per stage row */
 
+/* Dynamic shared memory of fp8_block_gemm: the BF16 kernel's layout plus, in the
+ * swapped modes, BN scale products for each of the four epilogue warps. */
+template <int BN, int Stages, int Mode> constexpr int block_smem_bytes()
+{
+    return GemmSmem<BN, Stages, Mode>::kTotal + (Mode == kStoreRows ? 0 : 4 * BN * 4);
+}
+
 template <int BN, int Stages, int Mode>
 __global__ void __launch_bounds__(sm100::kThreads, 1)
     fp8_block_gemm(const __grid_constant__ CUtensorMap map_p,
@@ -119,6 +126,9 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile uint32_t *abort = tmem_slot + 1;
+    /* swapped modes: the token-side scale products of the K block in flight, BN
+     * floats per epilogue warp, behind the 256-byte barrier area */
+    float *scale_area = reinterpret_cast<float *>(full) + 64;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = task.r_blocks * task.c_blocks * task.split;
@@ -264,6 +274,16 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                 float band = 1.f;
                 if (Mode == kStoreRows)
                     band = task.q_scale[static_cast<long long>(cb) * groups + kb];
+                float *column_scale = scale_area + (warp - 2) * BN;
+                if (Mode != kStoreRows) {
+                    __syncwarp(); /* every lane is done with the previous block's products */
+                    for (int i = lane; i < BN; i += 32) {
+                        const int c = min(col0 + i, task.cols - 1);
+                        column_scale[i] =
+                            __fmul_rn(task.q_scale[static_cast<long long>(c) * groups + kb], own);
+                    }
+                    __syncwarp();
+                }
                 if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
                     report(task.status, abort, kRoleEpilogueFull);
                     ok = false;
@@ -297,13 +317,10 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                                 fmaf(__uint_as_float(piece[i]), s, acc[chunk * kPiece + i]);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < kPiece; ++i) {
-                            const int c = min(col0 + chunk * kPiece + i, task.cols - 1);
-                            const float s = __fmul_rn(
-                                task.q_scale[static_cast<long long>(c) * groups + kb], own);
+                        for (int i = 0; i < kPiece; ++i)
                             acc[chunk * kPiece + i] =
-                                fmaf(__uint_as_float(piece[i]), s, acc[chunk * kPiece + i]);
-                        }
+                                fmaf(__uint_as_float(piece[i]), column_scale[chunk * kPiece + i],
+                                     acc[chunk * kPiece + i]);
                     }
                 }
             }
@@ -471,7 +488,7 @@ template <int BN, int Stages, int Mode> int prepare_kernel()
 {
     return int(cudaFuncSetAttribute(fp8_block_gemm<BN, Stages, Mode>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    GemmSmem<BN, Stages, Mode>::kTotal));
+                                    block_smem_bytes<BN, Stages, Mode>()));
 }
 
 inline int prepare_kernels()
@@ -497,7 +514,7 @@ void launch_block(camblas_cuda_context *context, const CUtensorMap &p, const CUt
     int units = task.r_blocks * task.c_blocks * task.split;
     int grid = units < context->sm_count ? units : context->sm_count;
     fp8_block_gemm<BN, Stages, Mode>
-        <<<grid, sm100::kThreads, GemmSmem<BN, Stages, Mode>::kTotal, context->stream>>>(p, q, d,
+        <<<grid, sm100::kThreads, block_smem_bytes<BN, Stages, Mode>(), context->stream>>>(p, q, d,
                                                                                          task);
 }
 

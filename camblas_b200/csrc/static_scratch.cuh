@@ -81,7 +81,7 @@ int launch(const DeviceSetup &entry, cudaStream_t stream, skinny::Task &task)
     const int row_blocks =
         (task.outputs + rows_per_warp * skinny::kWarps - 1) / (rows_per_warp * skinny::kWarps);
     int split = (task.depth + 4095) / 4096;
-    while (1ll * row_blocks * split < 4ll * sms && task.depth / (split * 2) >= 512)
+    while (1ll * row_blocks * split < 2ll * sms && task.depth / (split * 2) >= 512)
         split *= 2;
     const int per = ((task.depth + split - 1) / split + 7) & ~7;
     split = (task.depth + per - 1) / per;
