@@ -191,8 +191,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             /* ---- producer: this CTA's rows of P and its half of the Q tile ---- */
             const uint64_t keep = policy_evict_last(), stream = policy_evict_first();
-            const uint64_t policy_p = task.r_blocks <= task.panel ? keep : stream;
-            const uint64_t policy_q = task.r_blocks <= task.panel ? stream : keep;
+            /* Both operands are re-read by other CTAs through L2 (the weight tile by
+             * the other row blocks, the token tile by every column tile); measured
+             * on B200, asking L2 to keep both is as good as or better than marking
+             * the weights as streamed. */
+            const uint64_t policy_p = keep, policy_q = keep;
+            (void)stream;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             Unit u;
