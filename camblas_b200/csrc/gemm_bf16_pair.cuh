@@ -118,10 +118,11 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t barrier_cluster_addres
 
 constexpr int kPairRows = 256;
 
-template <int BN, int Stages> struct PairSmem {
+template <int BN, int Stages, int Sub = 1> struct PairSmem {
     static constexpr int kPBytes = kBlockR * kBlockK * 2;      /* this CTA's 128 rows of P */
     static constexpr int kQBytes = (BN / 2) * kBlockK * 2;     /* this CTA's half of the Q tile */
-    static constexpr int kStageBytes = kPBytes + kQBytes;
+    static constexpr int kBlockBytes = kPBytes + kQBytes;      /* one 64-deep K block */
+    static constexpr int kStageBytes = Sub * kBlockBytes;      /* Sub K blocks per stage */
     static constexpr int kTotal = Stages * kStageBytes + kStagingBytes + 256 + 1024;
 };
 
@@ -129,7 +130,7 @@ template <int BN, int Stages> struct PairSmem {
  * BNT is the tile width, or 0 when the width comes from task.width at run time
  * (any multiple of 16 from 64 to 256; Q must then be K-major and the stage
  * layout and TMEM buffers are those of the 256-column tile). */
-template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK>
+template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK, int Sub = 1>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_d0,
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 {
     constexpr bool kDynamic = BNT == 0;
     constexpr int kLayoutWidth = kDynamic ? 256 : BNT;
-    using Layout = PairSmem<kLayoutWidth, Stages>;
+    using Layout = PairSmem<kLayoutWidth, Stages, Sub>;
     constexpr uint32_t kTmemColumns = kLayoutWidth * 2;
     static_assert(BNT == 256 || BNT == 128 || BNT == 0, "pair tiles: 256, 128 or run-time width");
     static_assert(!kDynamic || QMajor == kMajorK, "run-time width needs a K-major Q operand");
@@ -203,31 +204,38 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int item = 0; ok && fetch_unit(task, item, pair, pairs, u); ++item) {
                 const int p_row = u.rb * kPairRows + rank * kBlockR;
                 const int q_row = u.cb * BN + rank * kHalf;
-                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                for (int kb = u.kb0; kb < u.kb1; kb += Sub) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
                         report(task.status, abort, kRoleProducer);
                         ok = false;
                         break;
                     }
-                    uint8_t *p_tile = smem + stage * Layout::kStageBytes;
-                    uint8_t *q_tile = p_tile + Layout::kPBytes;
                     const uint32_t barrier = map_to_rank(smem_u32(&full[stage]), 0);
+                    /* a stage holds up to Sub 64-deep K blocks; the last stage of a
+                     * piece of work may hold fewer */
+                    const int blocks = min(Sub, u.kb1 - kb);
                     if (leader)
-                        mbar_arrive_expect_tx(&full[stage], 2 * stage_bytes);
-                    if constexpr (PMajor == kMajorK) {
-                        tma_load_2d_pair(p_tile, &map_p, barrier, kb * kBlockK, p_row, policy_p);
-                    } else {
+                        mbar_arrive_expect_tx(&full[stage], 2 * blocks * stage_bytes);
+                    for (int sub = 0; sub < blocks; ++sub) {
+                        uint8_t *p_tile =
+                            smem + stage * Layout::kStageBytes + sub * Layout::kBlockBytes;
+                        uint8_t *q_tile = p_tile + Layout::kPBytes;
+                        const int k0 = (kb + sub) * kBlockK;
+                        if constexpr (PMajor == kMajorK) {
+                            tma_load_2d_pair(p_tile, &map_p, barrier, k0, p_row, policy_p);
+                        } else {
 #pragma unroll
-                        for (int g = 0; g < kBlockR / 64; ++g)
-                            tma_load_2d_pair(p_tile + g * 8192, &map_p, barrier, p_row + g * 64,
-                                             kb * kBlockK, policy_p);
-                    }
-                    if constexpr (QMajor == kMajorK) {
-                        tma_load_2d_pair(q_tile, &map_q, barrier, kb * kBlockK, q_row, policy_q);
-                    } else {
-                        for (int g = 0; g < kHalf / 64; ++g)
-                            tma_load_2d_pair(q_tile + g * 8192, &map_q, barrier, q_row + g * 64,
-                                             kb * kBlockK, policy_q);
+                            for (int g = 0; g < kBlockR / 64; ++g)
+                                tma_load_2d_pair(p_tile + g * 8192, &map_p, barrier, p_row + g * 64,
+                                                 k0, policy_p);
+                        }
+                        if constexpr (QMajor == kMajorK) {
+                            tma_load_2d_pair(q_tile, &map_q, barrier, k0, q_row, policy_q);
+                        } else {
+                            for (int g = 0; g < kHalf / 64; ++g)
+                                tma_load_2d_pair(q_tile + g * 8192, &map_q, barrier, q_row + g * 64,
+                                                 k0, policy_q);
+                        }
                     }
                     if (++stage == Stages) {
                         stage = 0;
@@ -256,14 +264,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buffer * kLayoutWidth;
-                for (int kb = u.kb0; kb < u.kb1; ++kb) {
+                for (int kb = u.kb0; kb < u.kb1; kb += Sub) {
                     if (!mbar_wait(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    const int blocks = min(Sub, u.kb1 - kb);
+                    for (int sub = 0; sub < blocks; ++sub) {
+                    const uint32_t p_address =
+                        smem_u32(smem + stage * Layout::kStageBytes + sub * Layout::kBlockBytes);
                     const uint32_t q_address = p_address + Layout::kPBytes;
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
@@ -273,7 +284,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                         const uint64_t desc_q = QMajor == kMajorK
                                                     ? desc_kmajor_sw128(q_address) + 2 * k
                                                     : desc_mnmajor_sw128(q_address + k * 2048, 8192);
-                        umma_f16_pair(tmem_d, desc_p, desc_q, idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
+                        umma_f16_pair(tmem_d, desc_p, desc_q, idesc,
+                                      (kb > u.kb0 || k > 0 || sub > 0) ? 1u : 0u);
+                    }
                     }
                     /* free the stage in both CTAs */
                     const uint32_t local_empty = smem_u32(&empty[stage]);
