@@ -84,9 +84,9 @@ template <int PMajor, int QMajor> int prepare_pair_kernels()
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        PairSmem<128, 4, 2>::kTotal));
     if constexpr (QMajor == kMajorK)
-        status |= int(cudaFuncSetAttribute(gemm_bf16_pair<0, 6, PMajor, QMajor>,
+        status |= int(cudaFuncSetAttribute(gemm_bf16_pair<0, 3, PMajor, QMajor, 2>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           PairSmem<256, 6>::kTotal));
+                                           PairSmem<256, 3, 2>::kTotal));
     return status;
 }
 
@@ -301,7 +301,7 @@ cudaError_t launch_pair_width(camblas_cuda_context *context, int bn, int pairs, 
 {
     if (task.width != 0) {
         if constexpr (QMajor == sm100::kMajorK)
-            return launch_pair<0, 6, PMajor, QMajor>(context, pairs, p, q, d0, d1, d2, task);
+            return launch_pair<0, 3, PMajor, QMajor, 2>(context, pairs, p, q, d0, d1, d2, task);
         else
             return cudaErrorInvalidValue;
     }
