@@ -70,6 +70,16 @@ _SIGNATURES = {
     ),
     "linear_bf16": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P, _I], _I),
     "linear_bf16_static": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _I], _I),
+    "peer_bytes": ([_I, ct.c_size_t], ct.c_size_t),
+    "peer_alloc": ([_P, ct.c_size_t, ct.POINTER(_P), _P], _I),
+    "peer_open": ([_P, _P, ct.POINTER(_P)], _I),
+    "peer_close": ([_P, _P], _I),
+    "peer_free": ([_P, _P], _I),
+    "peer_reset": ([_P, _P, _I, ct.c_size_t], _I),
+    "linear_bf16_allreduce": (
+        [_P, _I, _I, ct.c_size_t, ct.POINTER(_P), _I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I],
+        _I,
+    ),
     "qkv_linear_bf16": ([_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I], _I),
     "rms_norm": ([_P, _I, _I, _I, _F, _P, _P, _P], _I),
     "rms_norm_decode": ([_P, _I, _I, _I, _F, _I, _I, _P, _P, _P], _I),

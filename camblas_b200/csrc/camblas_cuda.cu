@@ -9,6 +9,7 @@
 #include "dispatch_bf16.cuh"
 #include "fp8_block.cuh"
 #include "rms_norm.cuh"
+#include "row_parallel.cuh"
 #include "static_scratch.cuh"
 
 #include <algorithm>

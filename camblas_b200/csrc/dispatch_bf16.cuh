@@ -98,6 +98,12 @@ inline int prepare_kernels()
     status |= prepare_pair_kernels<kMajorK, kMajorMN>();
     status |= prepare_pair_kernels<kMajorMN, kMajorK>();
     status |= prepare_pair_kernels<kMajorMN, kMajorMN>();
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       PairSmem<256, 3, 2>::kTotal));
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<128, 4, kMajorK, kMajorK, 2, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       PairSmem<128, 4, 2>::kTotal));
     status |= prepare_row_kernels<kMajorK, kMajorMN>();
     status |= prepare_row_kernels<kMajorMN, kMajorK>();
     status |= prepare_row_kernels<kMajorMN, kMajorMN>();
@@ -273,7 +279,7 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     return launched(context, "stream-K fix-up");
 }
 
-template <int BN, int Stages, int PMajor, int QMajor, int Sub = 1>
+template <int BN, int Stages, int PMajor, int QMajor, int Sub = 1, bool Push = false>
 cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensorMap &p,
                         const CUtensorMap &q, const CUtensorMap &d0, const CUtensorMap &d1,
                         const CUtensorMap &d2, const sm100::GemmTask &task)
@@ -290,8 +296,8 @@ cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensor
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, sm100::gemm_bf16_pair<BN, Stages, PMajor, QMajor, Sub>, p, q,
-                              d0, d1, d2, task);
+    return cudaLaunchKernelEx(&config, sm100::gemm_bf16_pair<BN, Stages, PMajor, QMajor, Sub, Push>,
+                              p, q, d0, d1, d2, task);
 }
 
 template <int PMajor, int QMajor>

@@ -130,7 +130,8 @@ template <int BN, int Stages, int Sub = 1> struct PairSmem {
  * BNT is the tile width, or 0 when the width comes from task.width at run time
  * (any multiple of 16 from 64 to 256; Q must then be K-major and the stage
  * layout and TMEM buffers are those of the 256-column tile). */
-template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK, int Sub = 1>
+template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK, int Sub = 1,
+          bool Push = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_d0,
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr uint32_t kTmemColumns = kLayoutWidth * 2;
     static_assert(BNT == 256 || BNT == 128 || BNT == 0, "pair tiles: 256, 128 or run-time width");
     static_assert(!kDynamic || QMajor == kMajorK, "run-time width needs a K-major Q operand");
+    static_assert(!Push || !kDynamic, "the push epilogue works on fixed-width tiles");
     const int BN = kDynamic ? task.width : BNT;
     const int kHalf = BN / 2;
     const uint32_t stage_bytes = Layout::kPBytes + kHalf * kBlockK * 2; /* bytes one CTA loads */
@@ -327,7 +329,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                     mbar_arrive_cluster(map_to_rank(smem_u32(&tmem_empty[buffer]), 0));
             };
-            if constexpr (kDynamic) {
+            if constexpr (Push) {
+                /* partial sums of a K range split over GPUs: to the tile's owner */
+                const int unit = ((u.rb * task.c_blocks + u.cb) * 2 + static_cast<int>(rank)) * 4 +
+                                 quarter;
+                epilogue_push<kLayoutWidth>(task, taddr, row0, col0, u.cb % task.push_world, unit,
+                                            lane, slab, release);
+            } else if constexpr (kDynamic) {
                 epilogue_rows_dynamic(task, &map_d0, &map_d1, &map_d2, taddr, row0 + lane, row0, col0,
                                       BN, lane, slab, slab_use, release);
             } else if (u.slot >= 0) {

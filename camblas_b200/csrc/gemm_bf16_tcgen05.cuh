@@ -72,6 +72,18 @@ struct GemmTask {
     float *sk_partial;
     const unsigned *skip_if_set; /* when non-NULL and *skip_if_set != 0 the kernel does nothing */
     const unsigned *run_if_set;  /* when non-NULL and *run_if_set == 0 the kernel does nothing */
+    /* Row-parallel product whose partial sums go to other GPUs (Push variant of
+     * the two-SM kernel, push_world >= 1). The epilogue scales the tile by alpha
+     * and, instead of storing it to `out`, writes it as BF16 into the staging
+     * area of the GPU that owns the tile's column block (owner = column block
+     * mod push_world): push_staging[owner] is the [rows][cols] slot that GPU
+     * keeps for this rank, in this process's address space. An epilogue warp
+     * covers a 32-row slab of the tile; when its rows are written it adds one to
+     * word `unit` of push_arrive[owner], unit = (row block * c_blocks + column
+     * block) * 8 + slab. */
+    int push_world;
+    __nv_bfloat16 *push_staging[8];
+    unsigned *push_arrive[8];
 };
 
 constexpr int kBlockR = 128;
@@ -258,6 +270,64 @@ __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtens
         }
         ++slab_use;
     }
+}
+
+/* Push variant of the row epilogue for a product whose K range is split over
+ * GPUs: alpha*acc rounded to BF16 (bias and addend are applied once, by the GPU
+ * that sums the partials), written to the owner's staging slot with ordinary
+ * stores. The warp's 32 rows x 64 columns go through one of its two swizzled
+ * 4 KB buffers so that eight lanes write one 128-byte row segment, then a
+ * system-scope release add tells the owner that this 32-row slab is complete.
+ * `unit` is the slab's flag index (see GemmTask::push_arrive). */
+template <int BN, typename Release>
+__device__ __forceinline__ void epilogue_push(const GemmTask &task, uint32_t taddr, int store_row,
+                                              int col0, int owner, int unit, int lane,
+                                              uint8_t *slab, Release release)
+{
+    __nv_bfloat16 *destination = task.push_staging[owner];
+#pragma unroll 1
+    for (int chunk = 0; chunk < BN / 64; ++chunk) {
+        uint32_t acc[2][32];
+        tmem_ld_32x32(taddr + chunk * 64, acc[0]);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+        tmem_ld_wait();
+        if (chunk == BN / 64 - 1)
+            release();
+        uint8_t *buffer_smem = slab + (chunk & 1) * 4096;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = task.alpha * __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
+            uint4 packed;
+            packed.x = pack_bf16(v[0], v[1]);
+            packed.y = pack_bf16(v[2], v[3]);
+            packed.z = pack_bf16(v[4], v[5]);
+            packed.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                packed;
+        }
+        /* Orders this chunk's buffer writes before the reads below, and the
+         * reads of the chunk before last (same buffer) before these writes. */
+        __syncwarp();
+        const int piece = lane & 7;
+        const int c = col0 + chunk * 64 + piece * 8;
+#pragma unroll
+        for (int step = 0; step < 8; ++step) {
+            const int r = step * 4 + (lane >> 3);
+            const uint4 value =
+                *reinterpret_cast<const uint4 *>(buffer_smem + r * 128 + ((piece ^ (r & 7)) << 4));
+            const int row = store_row + r;
+            if (row < task.rows && c < task.cols)
+                *reinterpret_cast<uint4 *>(destination + static_cast<long long>(row) * task.cols +
+                                           c) = value;
+        }
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0)
+        flag_add_release_system(task.push_arrive[owner] + unit, 1u);
 }
 
 /* alpha*acc + bias + beta*addend for eight consecutive columns of one row. */

@@ -1,0 +1,433 @@
+/*
+ * Row-parallel BF16 linear layer with the sum over GPUs done through peer
+ * memory: y = sum_r x[:, K_r] . W[:, K_r]^T (+ bias + residual), one process
+ * per GPU, every GPU ends with the full [rows][outputs] result.
+ *
+ * The reference has no multi-GPU code; in its published runs the sum is the
+ * all-reduce that SGLang's RowParallelLinear issues after the hooked F.linear
+ * (camblas/sglang.py:250-285). Here the product and the exchange are one
+ * sequence of three launches per GPU on one stream:
+ *
+ *   1. gemm_bf16_pair<.., Push>: the two-SM tcgen05 product of this GPU's K
+ *      range. Its epilogue does not store a local result: every 256 x BN tile
+ *      is written, rounded to BF16, straight into the staging slot that the
+ *      OWNER of the tile's column block keeps for this GPU (owner = column
+ *      block mod world), with ordinary stores over NVLink, 32-row slab by
+ *      slab, each followed by a system-scope release add on the owner's
+ *      arrival word for that slab. Tiles leave as they finish, so the transfer
+ *      of early tiles overlaps the multiplication of later ones.
+ *   2. peer_reduce_broadcast: on the owner, one CTA per slab waits (bounded)
+ *      until all `world` partial slabs are there, clears the word, adds the
+ *      partials in rank order in FP32, adds bias and residual, rounds once and
+ *      writes the finished slab into the result buffer of EVERY GPU, then adds
+ *      one to each GPU's delivery counter.
+ *   3. peer_wait_delivered: waits (bounded) until this GPU's delivery counter
+ *      has reached the number of slabs of the whole matrix, and clears it.
+ *
+ * Because every slab is summed by exactly one GPU in a fixed order, all GPUs
+ * hold bit-identical results and repeated calls give identical bits.
+ *
+ * Memory. Each GPU owns one region laid out as
+ *   [result: capacity BF16][staging: world slots of capacity BF16][flag words]
+ * obtained from camblas_cuda_peer_alloc and made visible to the other
+ * processes with CUDA IPC handles (camblas_cuda_peer_open). `capacity` bounds
+ * rows * outputs of a call. Flag words are cleared by their consumer, so the
+ * region is ready for the next call when phase 3 has run; nothing depends on
+ * a call count.
+ *
+ * Why reuse is safe without a barrier between calls: GPU A starts call i+1
+ * only after its phase 3 of call i, i.e. after every owner B has delivered all
+ * of B's slabs to A. B delivers a slab after it has read the slab's partials
+ * and cleared its arrival word, so A's next pushes can neither overwrite
+ * partials that B still needs nor be counted into call i. Deliveries of call
+ * i+1 into A's result buffer need A's own pushes of call i+1, which A's stream
+ * orders after whatever A enqueued to read the result of call i.
+ *
+ * Every wait is bounded (five seconds to allow for skew between processes);
+ * when one expires the kernel records role | cta << 4 in the context status
+ * word and returns. After such a failure the flag words are undefined:
+ * camblas_cuda_peer_reset on every GPU, with a host barrier around it, makes the
+ * region usable again.
+ *
+ * The phases can be run separately (`phases` bit mask). That is how the
+ * single-GPU tests drive several emulated ranks in turn: all phase-1 launches,
+ * then all phase-2 launches, then all phase-3 launches, so that no kernel ever
+ * waits for one that has not been launched.
+ */
+#pragma once
+
+#include "dispatch_bf16.cuh"
+
+namespace peer
+{
+
+constexpr int kMaxWorld = 8;
+constexpr int kFlagWords = 65536; /* word 0: delivery counter; words 64..: arrival words */
+constexpr int kFlagHeader = 64;
+constexpr int kMaxUnits = kFlagWords - kFlagHeader;
+
+inline size_t slot_bytes(size_t capacity)
+{
+    return (capacity * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
+}
+
+inline size_t region_bytes(int world, size_t capacity)
+{
+    return slot_bytes(capacity) * (1 + size_t(world)) + size_t(kFlagWords) * sizeof(unsigned);
+}
+
+struct Region {
+    __nv_bfloat16 *result;
+    __nv_bfloat16 *staging; /* slot s at staging + s * slot_elements */
+    unsigned *flags;
+    size_t slot_elements;
+};
+
+inline Region carve(void *memory, int world, size_t capacity)
+{
+    Region region;
+    uint8_t *base = static_cast<uint8_t *>(memory);
+    region.slot_elements = slot_bytes(capacity) / sizeof(__nv_bfloat16);
+    region.result = reinterpret_cast<__nv_bfloat16 *>(base);
+    region.staging = reinterpret_cast<__nv_bfloat16 *>(base + slot_bytes(capacity));
+    region.flags = reinterpret_cast<unsigned *>(base + slot_bytes(capacity) * (1 + size_t(world)));
+    return region;
+}
+
+struct ReduceTask {
+    int rank, world;
+    int rows, cols;
+    int r_blocks, c_blocks, width; /* 256-row blocks, column blocks of `width` */
+    const __nv_bfloat16 *staging;  /* this GPU's staging slots */
+    long long slot_elements;
+    unsigned *arrive;              /* this GPU's arrival words */
+    const __nv_bfloat16 *bias;     /* per column, may be NULL */
+    const __nv_bfloat16 *residual; /* [rows][ld_residual], may be NULL */
+    long long ld_residual;
+    __nv_bfloat16 *result[kMaxWorld]; /* every GPU's result buffer */
+    unsigned *delivered[kMaxWorld];   /* every GPU's delivery counter */
+    unsigned *status;
+};
+
+__device__ __forceinline__ void accumulate8(float (&sum)[8], const uint4 &packed)
+{
+    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sum[2 * i] += __uint_as_float(words[i] << 16);
+        sum[2 * i + 1] += __uint_as_float(words[i] & 0xffff0000u);
+    }
+}
+
+/* grid = (column blocks this GPU owns, 8 * r_blocks); 256 threads. Each CTA
+ * finishes one 32-row slab of one owned tile. */
+__global__ void __launch_bounds__(256) peer_reduce_broadcast(const ReduceTask task)
+{
+    __shared__ int failed;
+    const int cb = task.rank + blockIdx.x * task.world;
+    const int rb = blockIdx.y >> 3, slab = blockIdx.y & 7;
+    const int unit = (rb * task.c_blocks + cb) * 8 + slab;
+    if (threadIdx.x == 0) {
+        unsigned *word = task.arrive + unit;
+        const bool ok = sm100::flag_wait_system(word, unsigned(task.world));
+        if (ok)
+            sm100::flag_store_relaxed_system(word, 0u);
+        else
+            atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
+        failed = ok ? 0 : 1;
+    }
+    __syncthreads();
+    if (failed)
+        return;
+    const int row0 = rb * 256 + slab * 32;
+    const int pieces_per_row = task.width >> 3;
+    const int pieces = 32 * pieces_per_row;
+    for (int p = threadIdx.x; p < pieces; p += 256) {
+        const int r = p / pieces_per_row;
+        const int row = row0 + r;
+        const int c = cb * task.width + (p - r * pieces_per_row) * 8;
+        if (row >= task.rows || c >= task.cols)
+            continue;
+        const long long offset = static_cast<long long>(row) * task.cols + c;
+        uint4 part[kMaxWorld];
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (s < task.world)
+                part[s] = __ldcg(reinterpret_cast<const uint4 *>(task.staging +
+                                                                 s * task.slot_elements + offset));
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (s < task.world)
+                accumulate8(sum, part[s]);
+        if (task.bias != nullptr) {
+            const uint4 b = *reinterpret_cast<const uint4 *>(task.bias + c);
+            accumulate8(sum, b);
+        }
+        if (task.residual != nullptr) {
+            const uint4 b = *reinterpret_cast<const uint4 *>(
+                task.residual + static_cast<long long>(row) * task.ld_residual + c);
+            accumulate8(sum, b);
+        }
+        uint4 packed;
+        packed.x = sm100::pack_bf16(sum[0], sum[1]);
+        packed.y = sm100::pack_bf16(sum[2], sum[3]);
+        packed.z = sm100::pack_bf16(sum[4], sum[5]);
+        packed.w = sm100::pack_bf16(sum[6], sum[7]);
+        /* start with the next GPU so that the owners do not all write to the same one first */
+        for (int step = 1; step <= task.world; ++step) {
+            int target = task.rank + step;
+            if (target >= task.world)
+                target -= task.world;
+            *reinterpret_cast<uint4 *>(task.result[target] + offset) = packed;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < task.world)
+        sm100::flag_add_release_system(task.delivered[threadIdx.x], 1u);
+}
+
+/* One thread: wait until `expected` slabs have been delivered to this GPU. */
+__global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsigned *status)
+{
+    if (threadIdx.x != 0)
+        return;
+    if (sm100::flag_wait_system(delivered, expected))
+        sm100::flag_store_relaxed_system(delivered, 0u);
+    else
+        atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
+}
+
+struct Call {
+    int rank, world;
+    size_t capacity;
+    void *const *memory;
+    int phases;
+    int rows, inner, outputs;
+    const __nv_bfloat16 *x, *w, *bias, *residual;
+    int ldx, ldw, ldr;
+};
+
+inline int run(camblas_cuda_context *context, const Call &call)
+{
+    using namespace host;
+    Region regions[kMaxWorld];
+    for (int r = 0; r < call.world; ++r)
+        regions[r] = carve(call.memory[r], call.world, call.capacity);
+    const Region &own = regions[call.rank];
+
+    const char *width_text = std::getenv("CAMBLAS_B200_PUSH_WIDTH"); /* tuning aid: 128 or 256 */
+    int bn = call.outputs <= 128 ? 128 : 256;
+    if (width_text != nullptr && std::atoi(width_text) == 128)
+        bn = 128;
+    const int r_blocks = (call.rows + 255) / 256;
+    const int c_blocks = (call.outputs + bn - 1) / bn;
+    const long long units = 1ll * r_blocks * c_blocks * 8;
+    if (units > kMaxUnits)
+        return fail(context, "row-parallel product has more slabs than the region has flag words", 1);
+
+    if (call.phases & 1) {
+        sm100::GemmTask task{};
+        task.rows = call.rows, task.cols = call.outputs, task.depth = call.inner;
+        task.r_blocks = r_blocks, task.c_blocks = c_blocks;
+        task.k_blocks = (call.inner + 63) / 64;
+        task.split = 1, task.k_blocks_per_split = task.k_blocks;
+        task.alpha = 1.f, task.beta = 0.f;
+        task.status = context->status;
+        task.cut0 = task.cut1 = call.outputs;
+        task.batch = 1;
+        task.panel = r_blocks < 8 ? r_blocks : 8;
+        task.push_world = call.world;
+        for (int r = 0; r < call.world; ++r) {
+            task.push_staging[r] = regions[r].staging + size_t(call.rank) * regions[r].slot_elements;
+            task.push_arrive[r] = regions[r].flags + kFlagHeader;
+        }
+        const int pairs_max = context->sm_count / 2;
+        const long long tiles = 1ll * r_blocks * c_blocks;
+        const int pairs = tiles < pairs_max ? int(tiles) : pairs_max;
+        CUtensorMap p, q;
+        const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        bool ok = encode_2d(context, &p, bf16, 2, call.x, call.inner, call.rows,
+                            uint64_t(call.ldx) * 2, 64, 128) &&
+                  encode_2d(context, &q, bf16, 2, call.w, call.inner, call.outputs,
+                            uint64_t(call.ldw) * 2, 64, bn / 2);
+        if (!ok)
+            return fail(context, "tensor map encoding", 1);
+        using namespace sm100;
+        /* the kernel only prefetches its output maps in this mode; any valid map will do */
+        cudaError_t error =
+            bn == 256 ? launch_pair<256, 3, kMajorK, kMajorK, 2, true>(context, pairs, p, q, q, q, q,
+                                                                       task)
+                      : launch_pair<128, 4, kMajorK, kMajorK, 2, true>(context, pairs, p, q, q, q, q,
+                                                                       task);
+        if (error != cudaSuccess)
+            return fail(context, "two-SM tcgen05 BF16 GEMM with peer push", error);
+        context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    if (call.phases & 2) {
+        const int owned = (c_blocks - call.rank + call.world - 1) / call.world;
+        if (owned > 0) {
+            ReduceTask task{};
+            task.rank = call.rank, task.world = call.world;
+            task.rows = call.rows, task.cols = call.outputs;
+            task.r_blocks = r_blocks, task.c_blocks = c_blocks, task.width = bn;
+            task.staging = own.staging;
+            task.slot_elements = static_cast<long long>(own.slot_elements);
+            task.arrive = own.flags + kFlagHeader;
+            task.bias = call.bias;
+            task.residual = call.residual, task.ld_residual = call.ldr;
+            for (int r = 0; r < call.world; ++r) {
+                task.result[r] = regions[r].result;
+                task.delivered[r] = regions[r].flags;
+            }
+            task.status = context->status;
+            dim3 grid(owned, 8 * r_blocks);
+            peer_reduce_broadcast<<<grid, 256, 0, context->stream>>>(task);
+            int status = launched(context, "peer reduction and broadcast");
+            if (status != 0)
+                return status;
+        }
+    }
+    if (call.phases & 4) {
+        peer_wait_delivered<<<1, 32, 0, context->stream>>>(own.flags, unsigned(units),
+                                                           context->status);
+        return launched(context, "peer delivery wait");
+    }
+    return 0;
+}
+
+} // namespace peer
+
+extern "C" size_t camblas_cuda_peer_bytes(int world, size_t capacity)
+{
+    if (world < 1 || world > peer::kMaxWorld || capacity == 0)
+        return 0;
+    return peer::region_bytes(world, capacity);
+}
+
+extern "C" int camblas_cuda_peer_alloc(camblas_cuda_context *context, size_t bytes, void **memory,
+                                       void *handle)
+{
+    return host::guarded(context, [&] {
+        if (!memory || bytes == 0)
+            return host::fail(context, "missing peer allocation output or size", 1);
+        void *pointer = nullptr;
+        cudaError_t error = cudaMalloc(&pointer, bytes);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return host::fail(context, "peer region allocation", error);
+        }
+        error = cudaMemset(pointer, 0, bytes);
+        if (error == cudaSuccess && handle != nullptr) {
+            cudaIpcMemHandle_t exported;
+            error = cudaIpcGetMemHandle(&exported, pointer);
+            if (error == cudaSuccess)
+                std::memcpy(handle, &exported, sizeof(exported));
+        }
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(pointer);
+            return host::fail(context, "peer region export", error);
+        }
+        *memory = pointer;
+        return 0;
+    });
+}
+
+extern "C" int camblas_cuda_peer_open(camblas_cuda_context *context, const void *handle,
+                                      void **memory)
+{
+    return host::guarded(context, [&] {
+        if (!memory || !handle)
+            return host::fail(context, "missing peer handle or output", 1);
+        cudaIpcMemHandle_t imported;
+        std::memcpy(&imported, handle, sizeof(imported));
+        void *pointer = nullptr;
+        cudaError_t error =
+            cudaIpcOpenMemHandle(&pointer, imported, cudaIpcMemLazyEnablePeerAccess);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            return host::fail(context, "peer region import", error);
+        }
+        *memory = pointer;
+        return 0;
+    });
+}
+
+extern "C" int camblas_cuda_peer_close(camblas_cuda_context *context, void *memory)
+{
+    return host::guarded(context, [&] {
+        if (!memory)
+            return 0;
+        cudaError_t error = cudaStreamSynchronize(context->stream);
+        if (error == cudaSuccess)
+            error = cudaIpcCloseMemHandle(memory);
+        return error == cudaSuccess ? 0 : host::fail(context, "peer region close", error);
+    });
+}
+
+extern "C" int camblas_cuda_peer_free(camblas_cuda_context *context, void *memory)
+{
+    return host::guarded(context, [&] {
+        if (!memory)
+            return 0;
+        cudaError_t error = cudaStreamSynchronize(context->stream);
+        if (error == cudaSuccess)
+            error = cudaFree(memory);
+        return error == cudaSuccess ? 0 : host::fail(context, "peer region release", error);
+    });
+}
+
+extern "C" int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memory, int world,
+                                       size_t capacity)
+{
+    return host::guarded(context, [&] {
+        if (!memory || world < 1 || world > peer::kMaxWorld || capacity == 0)
+            return host::fail(context, "invalid peer region description", 1);
+        peer::Region region = peer::carve(memory, world, capacity);
+        cudaError_t error = cudaMemsetAsync(region.flags, 0, size_t(peer::kFlagWords) * 4,
+                                            context->stream);
+        return error == cudaSuccess ? 0 : host::fail(context, "peer flag reset", error);
+    });
+}
+
+extern "C" int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, int world,
+                                                  size_t capacity, void *const *memory, int phases,
+                                                  int rows, int inner, int outputs, const void *x,
+                                                  int ldx, const void *w, int ldw, const void *bias,
+                                                  const void *residual, int ldr)
+{
+    return host::guarded(context, [&] {
+        if (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world || !memory ||
+            capacity == 0 || (phases & ~7) != 0 || phases == 0)
+            return host::fail(context, "invalid row-parallel group description", 1);
+        for (int r = 0; r < world; ++r)
+            if (!memory[r])
+                return host::fail(context, "missing peer region", 1);
+        if (rows < 0 || inner < 1 || outputs < 0 || ldx < inner || ldw < inner ||
+            (residual && ldr < outputs))
+            return host::fail(context, "invalid row-parallel linear dimensions", 1);
+        if (rows == 0 || outputs == 0)
+            return 0;
+        if (size_t(rows) * size_t(outputs) > capacity)
+            return host::fail(context, "row-parallel result exceeds the peer region capacity", 1);
+        if (outputs % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (residual && ldr % 8 != 0) ||
+            !host::aligned16(x) || !host::aligned16(w) || (bias && !host::aligned16(bias)) ||
+            (residual && !host::aligned16(residual)))
+            return host::fail(context,
+                              "row-parallel linear needs 16-byte aligned rows (multiples of 8 elements)",
+                              1);
+        if (!x || !w)
+            return host::fail(context, "missing row-parallel linear operand", 1);
+        peer::Call call{};
+        call.rank = rank, call.world = world, call.capacity = capacity, call.memory = memory;
+        call.phases = phases;
+        call.rows = rows, call.inner = inner, call.outputs = outputs;
+        call.x = static_cast<const __nv_bfloat16 *>(x), call.ldx = ldx;
+        call.w = static_cast<const __nv_bfloat16 *>(w), call.ldw = ldw;
+        call.bias = static_cast<const __nv_bfloat16 *>(bias);
+        call.residual = static_cast<const __nv_bfloat16 *>(residual), call.ldr = ldr;
+        return peer::run(context, call);
+    });
+}

@@ -19,6 +19,8 @@ namespace sm100
  * limit of two seconds. A healthy pipeline needs microseconds. */
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+/* Waits on another GPU allow for the skew between processes: five seconds. */
+constexpr unsigned long long kPeerWaitLimitNs = 5000000000ull;
 
 __device__ __forceinline__ unsigned long long global_timer_ns()
 {
@@ -34,7 +36,30 @@ enum StatusRole : unsigned {
     kRoleEpilogueFull = 3,
     kRoleMmaTmemEmpty = 4,
     kRoleDrain = 5,
+    kRolePeerArrive = 6,    /* partial sums of another GPU did not arrive */
+    kRolePeerDelivered = 7, /* reduced tiles of another GPU did not arrive */
 };
+
+/* Flag words shared between GPUs: system-scope release add and acquire load. */
+__device__ __forceinline__ void flag_add_release_system(unsigned *word, unsigned value)
+{
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ unsigned flag_load_acquire_system(const unsigned *word)
+{
+    unsigned value;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(word) : "memory");
+    return value;
+}
+
+__device__ __forceinline__ void flag_store_relaxed_system(unsigned *word, unsigned value)
+{
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
+}
+
+/* Poll a flag word until it reaches `target`; gives up after kPeerWaitLimitNs. */
+__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target);
 
 __device__ __forceinline__ uint32_t smem_u32(const void *pointer)
 {
@@ -97,6 +122,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             if (started == 0)
                 started = now;
             else if (now - started > kWaitLimitNs)
+                return false;
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target)
+{
+    unsigned long long started = 0;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (flag_load_acquire_system(word) >= target)
+            return true;
+        if ((spin & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (started == 0)
+                started = now;
+            else if (now - started > kPeerWaitLimitNs)
                 return false;
         }
     }

@@ -18,7 +18,15 @@ one process per GPU:
 package. The CPU tests drive the same classes over the ``gloo`` backend with a
 host matmul passed in, which exercises the sharding arithmetic and the
 collective without a GPU.
+
+``PeerRegions`` is the alternative to the all-reduce for the row-parallel
+layer on GPUs of one machine: the product's epilogue writes its partial tiles
+straight into the memory of the GPU that sums them, and that GPU writes the
+finished tiles into every GPU's result buffer
+(``camblas_cuda_linear_bf16_allreduce``). Pass one to ``RowParallelLinear``.
 """
+
+import ctypes as ct
 
 import torch
 import torch.distributed as dist
@@ -61,6 +69,130 @@ def shard_qkv(weight, q_heads, kv_heads, head_dim, rank, world):
     return torch.cat(parts, dim=0).contiguous(), (q1 - q0, k1 - k0, k1 - k0)
 
 
+class _DeviceWords:
+    """Expose raw device memory to ``torch.as_tensor`` as 16-bit words."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {
+            "shape": (count,), "typestr": "<i2", "data": (pointer, False), "version": 2,
+        }
+
+
+class PeerRegions:
+    """The peer regions of one tensor-parallel group, seen from one rank.
+
+    Every rank owns a region that holds the result, one staging slot per rank
+    and flag words (``include/camblas_cuda.h``); ``memory[r]`` is rank ``r``'s
+    region as mapped here. ``capacity`` bounds ``rows * outputs`` of a call.
+
+    Use ``PeerRegions.create`` with one process per GPU (regions are exchanged
+    as CUDA IPC handles through ``all_gather_object``), or
+    ``PeerRegions.emulate`` to get all ranks' views in one process on one GPU,
+    which is how the single-GPU tests drive the kernels.
+    """
+
+    def __init__(self, device, rank, world, capacity, memory, owned, opened):
+        self.device, self.rank, self.world, self.capacity = device, rank, world, capacity
+        self.memory = list(memory)
+        self._owned, self._opened = owned, list(opened)
+        self._array = (ct.c_void_p * world)(*self.memory)
+
+    @staticmethod
+    def _native(device):
+        from . import _native
+
+        with torch.cuda.device(device):
+            return _native.context(device)
+
+    @classmethod
+    def create(cls, capacity, device, group=None):
+        """Allocate this rank's region and map every other rank's (collective)."""
+        from . import _native
+
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        native = cls._native(device)
+        size = _native.library().camblas_cuda_peer_bytes(world, capacity)
+        if size == 0:
+            raise ValueError("peer regions support 1 to 8 ranks and a non-zero capacity")
+        own, handle = ct.c_void_p(), ct.create_string_buffer(64)
+        native.call("peer_alloc", size, ct.byref(own), handle)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        memory, opened = [], []
+        for r in range(world):
+            if r == rank:
+                memory.append(own.value)
+                continue
+            mapped = ct.c_void_p()
+            native.call("peer_open", ct.create_string_buffer(handles[r], 64), ct.byref(mapped))
+            memory.append(mapped.value)
+            opened.append(mapped.value)
+        dist.barrier(group=group)
+        return cls(device, rank, world, capacity, memory, own.value, opened)
+
+    @classmethod
+    def emulate(cls, capacity, world, device):
+        """Return the views of all ``world`` ranks with every region on ``device``."""
+        from . import _native
+
+        native = cls._native(device)
+        size = _native.library().camblas_cuda_peer_bytes(world, capacity)
+        if size == 0:
+            raise ValueError("peer regions support 1 to 8 ranks and a non-zero capacity")
+        memory = []
+        for _ in range(world):
+            own = ct.c_void_p()
+            native.call("peer_alloc", size, ct.byref(own), None)
+            memory.append(own.value)
+        return [cls(device, r, world, capacity, memory, memory[r], []) for r in range(world)]
+
+    def result(self, rows, outputs):
+        """View the first ``rows * outputs`` elements of this rank's result buffer."""
+        words = torch.as_tensor(_DeviceWords(self._owned, rows * outputs),
+                                device=torch.device("cuda", self.device))
+        return words.view(torch.bfloat16).view(rows, outputs)
+
+    def linear(self, x, weight, bias=None, residual=None, phases=7):
+        """Enqueue ``sum_r x_r @ weight_r.T (+ bias + residual)``; return the result view.
+
+        ``x`` ``[rows, inner/world]`` and ``weight`` ``[outputs, inner/world]``
+        are this rank's slices. The returned tensor aliases the region: use it
+        (on the same stream) before the next call overwrites it.
+        """
+        if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+            raise ValueError("the peer row-parallel product takes BF16 operands")
+        if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
+            raise ValueError("expected x [rows, inner] and weight [outputs, inner]")
+        rows, inner, outputs = x.shape[0], x.shape[1], weight.shape[0]
+        x2 = x if x.stride(1) == 1 else x.contiguous()
+        w2 = weight if weight.stride(1) == 1 else weight.contiguous()
+        r2 = None
+        if residual is not None:
+            r2 = residual if residual.stride(-1) == 1 else residual.contiguous()
+        native = self._native(self.device)
+        native.call("linear_bf16_allreduce", self.rank, self.world, self.capacity, self._array,
+                    phases, rows, inner, outputs, x2.data_ptr(),
+                    x2.stride(0) if rows > 1 else inner, w2.data_ptr(), w2.stride(0),
+                    bias.data_ptr() if bias is not None else None,
+                    r2.data_ptr() if r2 is not None else None,
+                    (r2.stride(0) if rows > 1 else outputs) if r2 is not None else 0)
+        return self.result(rows, outputs)
+
+    def reset(self):
+        """Clear this rank's flag words (after a failed call; all ranks idle)."""
+        self._native(self.device).call("peer_reset", self._owned, self.world, self.capacity)
+
+    def close(self, free=True):
+        """Unmap the other ranks' regions and, with ``free``, release this rank's."""
+        native = self._native(self.device)
+        for mapped in self._opened:
+            native.call("peer_close", mapped)
+        self._opened = []
+        if free and self._owned:
+            native.call("peer_free", self._owned)
+            self._owned = None
+
+
 class ColumnParallelLinear:
     """``y_r = x @ W_r^T`` with ``W_r`` the rank's block of output rows; no communication."""
 
@@ -79,23 +211,33 @@ class RowParallelLinear:
     """``y = sum_r x[:, K_r] @ W[:, K_r]^T`` with one all-reduce of the BF16 partials.
 
     The bias, if any, is added by rank 0 only so that it enters the sum once.
-    ``group`` is the process group of the tensor-parallel ranks.
+    ``group`` is the process group of the tensor-parallel ranks. With ``peers``
+    (a ``PeerRegions``) the all-reduce is replaced by the product kernel
+    writing its tiles into peer memory; the result then aliases the peer region.
     """
 
-    def __init__(self, weight, rank, world, bias=None, linear=None, group=None, multiple=8):
+    def __init__(self, weight, rank, world, bias=None, linear=None, group=None, multiple=8,
+                 peers=None):
         start, stop = shard_bounds(weight.shape[1], rank, world, multiple)
         self.weight = weight[:, start:stop].contiguous()
+        self.full_bias = bias
         self.bias = bias if (bias is not None and rank == 0) else None
         self.bounds = (start, stop)
         self.world = world
         self.group = group
         self.linear = linear or _default_linear
+        self.peers = peers
 
     def slice_input(self, x):
         """Return the rank's columns of a replicated activation tensor."""
         return x[..., self.bounds[0]:self.bounds[1]].contiguous()
 
     def __call__(self, x_local):
+        if self.peers is not None:
+            # product and sum in one sequence of kernels over peer memory; the
+            # bias enters once, on the rank that sums each tile
+            return self.peers.linear(x_local.reshape(-1, x_local.shape[-1]), self.weight,
+                                     self.full_bias)
         partial = self.linear(x_local, self.weight, self.bias)
         if self.world > 1:
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)

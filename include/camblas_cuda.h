@@ -133,6 +133,68 @@ int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int in
 int camblas_cuda_linear_bf16_static(void *stream, int rows, int inner, int outputs, const void *x,
                                     int ldx, const void *w, int ldw, void *out, int ldo);
 
+/* ---- row-parallel linear layer over several GPUs ------------------------ */
+
+/* None of the following has a counterpart in the reference, which has no
+ * multi-GPU code: in its published runs the sum over tensor-parallel ranks is
+ * the all-reduce SGLang issues after the hooked F.linear (sglang.py:250-285).
+ *
+ * One process per GPU. Every GPU owns one *peer region*,
+ *   [result: capacity BF16][staging: world slots of capacity BF16][flag words],
+ * of camblas_cuda_peer_bytes(world, capacity) bytes, where capacity bounds
+ * rows * outputs of any later call. camblas_cuda_peer_alloc allocates and
+ * clears it and, when `handle` is not NULL, writes a 64-byte CUDA IPC handle
+ * that another process on the same machine passes to camblas_cuda_peer_open to
+ * map the region into its own address space (the caller carries the bytes
+ * between processes). camblas_cuda_peer_close unmaps an opened region,
+ * camblas_cuda_peer_free releases an allocated one; both synchronise the
+ * context's stream first. The regions must outlive all work that uses them. */
+size_t camblas_cuda_peer_bytes(int world, size_t capacity);
+int camblas_cuda_peer_alloc(camblas_cuda_context *context, size_t bytes, void **memory,
+                            void *handle);
+int camblas_cuda_peer_open(camblas_cuda_context *context, const void *handle, void **memory);
+int camblas_cuda_peer_close(camblas_cuda_context *context, void *memory);
+int camblas_cuda_peer_free(camblas_cuda_context *context, void *memory);
+/* Clears the flag words of this GPU's own region on the context's stream. Only
+ * needed after a call failed with a device status; all GPUs must be idle (host
+ * barrier before and after). */
+int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memory, int world,
+                            size_t capacity);
+
+/* result[rows,outputs] = sum over ranks of x_r[rows,inner] . w_r[outputs,inner]^T
+ * (+ bias[outputs] + residual[rows,outputs]), BF16 with FP32 accumulation, where
+ * rank r holds the r-th slice of the inner dimension of both operands (inner is
+ * the slice's depth). memory[r] is rank r's peer region as mapped in this
+ * process (memory[rank] the region this process allocated); the full result
+ * appears at the start of memory[rank] with row stride `outputs` on every rank,
+ * bit-identical on all of them. All ranks must make the same sequence of calls
+ * with the same rows and outputs. bias and residual are read on every rank from
+ * its own copies (they must be equal); they are added once, in FP32, before the
+ * single rounding of the sum of the BF16-rounded partial products.
+ *
+ * Three launches on the context's stream, asynchronous: (1) the two-SM tcgen05
+ * product whose epilogue writes each tile straight into the staging slot of
+ * the GPU that owns the tile (owner = column block mod world) over NVLink and
+ * raises that GPU's arrival word, tile by tile while later tiles are still
+ * being multiplied; (2) on the owner, a kernel that waits for the `world`
+ * partials of each 32-row slab, adds them in rank order, applies bias and
+ * residual and writes the finished slab into every GPU's result; (3) a wait
+ * until every slab has been delivered to this GPU. `phases` is a bit mask of
+ * the launches to issue, 7 in production; the parts exist so that a single
+ * process can drive several ranks on one GPU in turn (all of 1, then all of 2,
+ * then all of 4), where no kernel may wait for one that has not been launched.
+ * Waits inside the kernels give up after five seconds and record a device
+ * status (camblas_cuda_device_status), after which camblas_cuda_peer_reset is
+ * needed. The result may be overwritten by the next call: consume it with work
+ * enqueued on the same stream before that call. rows * outputs <= capacity;
+ * outputs, ldx, ldw and ldr multiples of 8; x, w, bias, residual 16-byte
+ * aligned; world <= 8. */
+int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, int world,
+                                       size_t capacity, void *const *memory, int phases, int rows,
+                                       int inner, int outputs, const void *x, int ldx,
+                                       const void *w, int ldw, const void *bias,
+                                       const void *residual, int ldr);
+
 /* ---- residual add + RMS normalisation ---------------------------------- */
 
 /* Replaces camblas_cuda_rms_norm (camblas_cuda.h:171-175; backend.cu:1423-1440).

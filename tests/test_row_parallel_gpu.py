@@ -1,0 +1,150 @@
+"""Row-parallel linear layer whose sum over ranks goes through peer memory.
+
+`camblas_cuda_linear_bf16_allreduce` is three launches per rank: the tcgen05
+product that writes its tiles into the owner's staging slots, the owner's
+reduction and broadcast, and the delivery wait. The reference has no such
+operation (its tensor parallelism is SGLang's all-reduce after the hooked
+`F.linear`, `camblas/sglang.py:250-285`), so the checker is the oracle's BF16
+linear layer on the whole inner dimension (tolerance rel-L2 <= 1e-2, the BF16
+bound of the other GEMM tests; the partial products are rounded to BF16 before
+they are summed, as SGLang's BF16 all-reduce does) and, for small-integer
+operands whose partial sums are exact, bit equality.
+
+One GPU is enough: all ranks' regions live on it and the phases of the ranks
+are issued in turn (all products, then all reductions, then all waits), so no
+kernel ever waits for one that has not been launched. The same entry point with
+one process per GPU is exercised by `tests/test_row_parallel_multi_gpu.py`.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from camblas_b200 import _native
+from camblas_b200.tp import PeerRegions
+from oracle import oracle
+from tests.helpers import BF16_TOLERANCE, bits_to_tensor, normal_bits, tensor_to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def run_emulated(views, xs, ws, bias=None, residual=None):
+    """Issue one call on every emulated rank, phase by phase; return each rank's result bits."""
+    for phase in (1, 2, 4):
+        for view, x, w in zip(views, xs, ws):
+            view.linear(x, w, bias, residual, phases=phase)
+    torch.cuda.synchronize()
+    assert _native.context(0).device_status() == 0
+    rows, outputs = xs[0].shape[0], ws[0].shape[0]
+    return [tensor_to_bits(view.result(rows, outputs)) for view in views]
+
+
+def make_case(rng, world, rows, inner, outputs, scale=1.0):
+    x = normal_bits(rng, (rows, world * inner), scale)
+    w = normal_bits(rng, (outputs, world * inner), 0.05)
+    xs = [bits_to_tensor(x[:, r * inner:(r + 1) * inner]) for r in range(world)]
+    ws = [bits_to_tensor(w[:, r * inner:(r + 1) * inner]) for r in range(world)]
+    return x, w, xs, ws
+
+
+def close_all(views):
+    for view in views:
+        view.close(free=True)
+
+
+@pytest.mark.parametrize("world,rows,inner,outputs", [
+    (1, 512, 256, 1024),
+    (2, 512, 512, 1024),
+    (2, 300, 200, 1000),   # ragged rows, columns and depth
+    (3, 257, 136, 520),    # owners get unequal numbers of column blocks
+    (4, 64, 128, 256),     # fewer column blocks than ranks: some own nothing
+    (8, 512, 192, 2048),
+    (8, 33, 72, 136),
+])
+def test_matches_oracle_and_ranks_agree(world, rows, inner, outputs):
+    rng = np.random.default_rng(20261004 + world * 1000 + rows)
+    x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
+    views = PeerRegions.emulate(rows * outputs, world, 0)
+    try:
+        first = run_emulated(views, xs, ws)
+        second = run_emulated(views, xs, ws)
+    finally:
+        close_all(views)
+    expected = oracle.bf16_values(oracle.linear_bf16(x, w))
+    assert oracle.rel_l2(oracle.bf16_values(first[0]), expected) <= BF16_TOLERANCE
+    for r in range(1, world):
+        assert np.array_equal(first[r], first[0]), f"rank {r} differs from rank 0"
+    # flag words were cleared by their consumers: the next call works and repeats the bits
+    for r in range(world):
+        assert np.array_equal(second[r], first[r])
+
+
+def test_bias_and_residual_enter_once():
+    world, rows, inner, outputs = 4, 384, 256, 768
+    rng = np.random.default_rng(73013)
+    x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
+    bias = normal_bits(rng, (outputs,))
+    residual = normal_bits(rng, (rows, outputs))
+    views = PeerRegions.emulate(rows * outputs, world, 0)
+    try:
+        got = run_emulated(views, xs, ws, bits_to_tensor(bias), bits_to_tensor(residual))
+    finally:
+        close_all(views)
+    expected = oracle.bf16_values(oracle.linear_bf16(x, w, bias, residual))
+    assert oracle.rel_l2(oracle.bf16_values(got[0]), expected) <= BF16_TOLERANCE
+    for r in range(1, world):
+        assert np.array_equal(got[r], got[0])
+
+
+def test_exact_integers_are_bit_exact():
+    """Entries in {-1,0,1}: every partial and the sum are integers below 256, exact in BF16."""
+    world, rows, inner, outputs = 8, 290, 24, 776
+    rng = np.random.default_rng(705537)
+    x = oracle.bf16_bits(rng.integers(-1, 2, (rows, world * inner)).astype(np.float32))
+    w = oracle.bf16_bits(rng.integers(-1, 2, (outputs, world * inner)).astype(np.float32))
+    bias = oracle.bf16_bits(rng.integers(-8, 9, (outputs,)).astype(np.float32))
+    residual = oracle.bf16_bits(rng.integers(-8, 9, (rows, outputs)).astype(np.float32))
+    xs = [bits_to_tensor(x[:, r * inner:(r + 1) * inner]) for r in range(world)]
+    ws = [bits_to_tensor(w[:, r * inner:(r + 1) * inner]) for r in range(world)]
+    views = PeerRegions.emulate(rows * outputs, world, 0)
+    try:
+        got = run_emulated(views, xs, ws, bits_to_tensor(bias), bits_to_tensor(residual))
+    finally:
+        close_all(views)
+    expected = oracle.linear_bf16(x, w, bias, residual)
+    for r in range(world):
+        assert np.array_equal(got[r], expected)
+
+
+def test_narrow_tiles_give_the_same_sum(monkeypatch):
+    """The 128-column tile variant (tuning aid) is the same arithmetic."""
+    world, rows, inner, outputs = 2, 512, 320, 1536
+    rng = np.random.default_rng(99)
+    x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
+    views = PeerRegions.emulate(rows * outputs, world, 0)
+    try:
+        wide = run_emulated(views, xs, ws)
+        monkeypatch.setenv("CAMBLAS_B200_PUSH_WIDTH", "128")
+        narrow = run_emulated(views, xs, ws)
+    finally:
+        close_all(views)
+    assert np.array_equal(wide[0], narrow[0])
+    assert np.array_equal(narrow[1], narrow[0])
+
+
+def test_rejects_what_it_cannot_do():
+    views = PeerRegions.emulate(64 * 64, 2, 0)
+    try:
+        x = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+        w = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+        with pytest.raises(RuntimeError, match="capacity"):
+            views[0].linear(x, w)
+        w_odd = torch.zeros((60, 64), dtype=torch.bfloat16, device="cuda")
+        with pytest.raises(RuntimeError, match="multiples of 8"):
+            views[0].linear(x, w_odd)
+        with pytest.raises(RuntimeError, match="group description"):
+            views[0].linear(x, w[:64], phases=8)
+    finally:
+        close_all(views)
+    with pytest.raises(ValueError):
+        PeerRegions.emulate(16, 9, 0)
