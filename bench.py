@@ -263,6 +263,52 @@ class Block:
         self.gemm_bytes = [2 * (w.numel() + TOKENS * w.shape[1] + TOKENS * w.shape[0])
                            for w in (self.qkv_weight, self.gate_up_weight, self.down_weight)]
         self.launches_per_step = 4
+        self.peers, self.exchange = None, None
+        if world > 1:
+            self.exchange = self.choose_exchange(rank, world, device)
+
+    def choose_exchange(self, rank, world, device):
+        """Pick how the down projection's partial sums meet; returns its description.
+
+        Default: the product kernel pushes its tiles through peer memory
+        (`camblas_cuda_linear_bf16_allreduce`). All ranks check one step of it
+        against the NCCL all-reduce of the same partial products and fall back to
+        NCCL together if the regions cannot be set up or the check fails;
+        CAMBLAS_B200_BENCH_EXCHANGE=nccl forces the NCCL path.
+        """
+        import torch.distributed as dist
+        from camblas_b200 import _kernels, _native, tp
+
+        torch = self.torch
+        nccl = "NCCL sum of BF16 partials after the down projection"
+        if os.environ.get("CAMBLAS_B200_BENCH_EXCHANGE", "peer") == "nccl":
+            return nccl + " (forced)"
+        try:
+            peers = tp.PeerRegions.create(TOKENS * HIDDEN, device.index)
+        except RuntimeError as error:
+            return nccl + f" (peer regions unavailable: {error})"
+        reason = None
+        try:
+            fused = peers.linear(self.down_input, self.down_weight).float()
+            expected = _kernels.linear(self.down_input, self.down_weight)
+            dist.all_reduce(expected, op=dist.ReduceOp.SUM)
+            torch.cuda.synchronize()
+            if _native.context(device.index).device_status() != 0:
+                reason = "a bounded wait expired"
+            else:
+                error = ((fused - expected.float()).norm() / expected.float().norm()).item()
+                if not error <= 2e-2:
+                    reason = f"rel-L2 {error:.2e} against the NCCL path"
+        except RuntimeError as error:
+            reason = str(error)
+        reasons = [None] * world
+        dist.all_gather_object(reasons, reason)
+        if any(reasons):
+            peers.close()
+            return nccl + " (peer path rejected: " + next(text for text in reasons if text) + ")"
+        self.peers = peers
+        return ("product epilogue writes BF16 partial tiles into the owner GPU's memory over NVLink; "
+                "owner sums in rank order and writes the result to every GPU")
 
     def step(self, x, residual, events=None):
         """One pass of the block; returns the down-projection output."""
@@ -284,6 +330,8 @@ class Block:
 
         timed(0, lambda: _kernels.qkv_linear(normed, self.qkv_weight, *self.qkv_widths))
         timed(1, lambda: _kernels.linear(self.mlp_input, self.gate_up_weight))
+        if self.peers is not None:
+            return timed(2, lambda: self.peers.linear(self.down_input, self.down_weight))
         out = timed(2, lambda: _kernels.linear(self.down_input, self.down_weight))
         if self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM)
@@ -379,6 +427,8 @@ def run_ours(args):
                 loaded[slot].record(upload)
             compute.wait_event(loaded[slot])
             out = block.step(*device_in[slot])
+            if block.peers is not None:
+                out = out.clone()  # the peer region is overwritten by the next step
             consumed[slot].record(compute)
             with torch.cuda.stream(download):
                 download.wait_event(consumed[slot])
@@ -439,7 +489,7 @@ def run_ours(args):
                 "tokens": TOKENS,
                 "parallelism": f"tp{world}" if world > 1 else "single",
                 "l2": "weights of one step (1.58 GB per GPU at tp1) exceed the 126 MB L2; no flush",
-                "all_reduce": "NCCL sum of BF16 partials after the down projection" if world > 1 else None,
+                "all_reduce": block.exchange,
             },
             "roofline": {
                 "bound": "tensor",
@@ -477,6 +527,12 @@ def run_ours(args):
             sample.close()
         print(json.dumps(line), flush=True)
     if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        if block.peers is not None:
+            block.peers.close(free=False)  # unmap the others' regions before anyone frees
+            dist.barrier()
+            block.peers.close(free=True)
         dist.barrier()
         dist.destroy_process_group()
 

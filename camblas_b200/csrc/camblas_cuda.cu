@@ -177,6 +177,7 @@ extern "C" int camblas_cuda_device_status(camblas_cuda_context *context, unsigne
             error = cudaMemsetAsync(context->status, 0, sizeof(unsigned), context->stream);
         if (error == cudaSuccess)
             error = cudaStreamSynchronize(context->stream);
+
         return error == cudaSuccess ? 0 : fail(context, "device status read", error);
     });
 }
@@ -569,3 +570,15 @@ extern "C" int camblas_cuda_reduce_groups(camblas_cuda_context *context, int, in
 {
     return host::unavailable(context, "camblas_cuda_reduce_groups");
 }
+
+#ifdef CAMBLAS_TRACE_PHASES
+/* Development aid, compiled only on request: copies the per-CTA phase timestamps
+ * of the last two-SM GEMM launch (148 x 16 words) to host memory. */
+extern "C" int camblas_cuda_debug_phase_trace(unsigned long long *host)
+{
+    cudaError_t error = cudaDeviceSynchronize();
+    if (error == cudaSuccess)
+        error = cudaMemcpyFromSymbol(host, sm100::phase_trace, sizeof(sm100::phase_trace));
+    return error == cudaSuccess ? 0 : -int(error);
+}
+#endif

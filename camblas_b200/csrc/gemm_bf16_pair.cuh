@@ -118,6 +118,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t barrier_cluster_addres
 
 constexpr int kPairRows = 256;
 
+
 template <int BN, int Stages, int Sub = 1> struct PairSmem {
     static constexpr int kPBytes = kBlockR * kBlockK * 2;      /* this CTA's 128 rows of P */
     static constexpr int kQBytes = (BN / 2) * kBlockK * 2;     /* this CTA's half of the Q tile */
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
+        CAMBLAS_TRACE(0);
         for (int s = 0; s < Stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -189,6 +191,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     cluster_sync();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0)
+        CAMBLAS_TRACE(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -239,12 +243,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                                                  k0, policy_q);
                         }
                     }
+                    if (item == 0 && kb == u.kb0)
+                        CAMBLAS_TRACE(9);
                     if (++stage == Stages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
             }
+            CAMBLAS_TRACE(10);
             if (!ok) {
                 /* let copies already in flight land before the pair retires */
                 for (int wait = 0; wait < 64; ++wait)
@@ -273,6 +280,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tcgen05_fence_after();
+                    if (item == 0 && kb == u.kb0)
+                        CAMBLAS_TRACE(2);
                     const int blocks = min(Sub, u.kb1 - kb);
                     for (int sub = 0; sub < blocks; ++sub) {
                     const uint32_t p_address =
@@ -304,21 +313,34 @@ __global__ void __launch_bounds__(kThreads, 1)
                     umma_commit_pair(local_full);
                     umma_commit_pair(map_to_rank(local_full, 1));
                 }
+                CAMBLAS_TRACE(item == 0 ? 3 : 4);
             }
         }
     } else {
         /* ---- epilogue: this CTA's 128 accumulator rows ---- */
         const int quarter = warp & 3;
-        uint8_t *slab = staging + (warp - 2) * 8192;
+        uint8_t *const own_slab = staging + (warp - 2) * 8192;
+        /* For the CTA's last piece of work the operand ring is idle once the
+         * accumulator is complete (all loads landed, all MMAs read them), so the
+         * epilogue borrows it: one 4 KB buffer per slab, none reused. */
+        uint8_t *const ring_slab = smem + (warp - 2) * (kLayoutWidth / 32) * 4096;
+        static_assert(4 * (kLayoutWidth / 32) * 4096 <= Stages * Layout::kStageBytes,
+                      "borrowed staging fits in the operand ring");
         uint32_t local = 0, slab_use = 0;
-        Unit u;
-        for (int item = 0; fetch_unit(task, item, pair, pairs, u); ++item, ++local) {
+        Unit u, following;
+        bool more = fetch_unit(task, 0, pair, pairs, u);
+        for (int item = 0; more; ++item, ++local, u = following) {
+            more = fetch_unit(task, item + 1, pair, pairs, following);
+            const bool roomy = !more;
+            uint8_t *slab = roomy ? ring_slab : own_slab;
             const uint32_t buffer = local & 1, use = local >> 1;
             if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
                 report(task.status, abort, kRoleEpilogueFull);
                 break;
             }
             tcgen05_fence_after();
+            if (warp == 2 && lane == 0)
+                CAMBLAS_TRACE(item == 0 ? 5 : 11);
             const uint32_t taddr =
                 tmem_base + buffer * kLayoutWidth + (static_cast<uint32_t>(quarter * 32) << 16);
             const int row0 = u.rb * kPairRows + rank * kBlockR + quarter * 32;
@@ -334,15 +356,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int unit = ((u.rb * task.c_blocks + u.cb) * 2 + static_cast<int>(rank)) * 4 +
                                  quarter;
                 epilogue_push<kLayoutWidth>(task, taddr, row0, col0, u.cb % task.push_world, unit,
-                                            lane, slab, release);
+                                            lane, own_slab, release);
             } else if constexpr (kDynamic) {
                 epilogue_rows_dynamic(task, &map_d0, &map_d1, &map_d2, taddr, row0 + lane, row0, col0,
-                                      BN, lane, slab, slab_use, release);
+                                      BN, lane, own_slab, slab_use, release);
             } else if (u.slot >= 0) {
                 float *slot = task.sk_partial +
-                              ((static_cast<long long>(u.slot) * 2 + rank) * kBlockR +
-                               quarter * 32 + lane) * BNT;
-                epilogue_partial<kLayoutWidth>(slot, taddr, release);
+                              (static_cast<long long>(u.slot) * 2 + rank) * kBlockR * BNT;
+                epilogue_partial<kLayoutWidth>(slot, taddr, quarter, lane, slab, slab_use, roomy,
+                                               release);
             } else {
                 const CUtensorMap *map_d = &map_d0;
                 int col_shift = 0;
@@ -352,12 +374,16 @@ __global__ void __launch_bounds__(kThreads, 1)
                     col_shift = third ? task.cut1 : task.cut0;
                 }
                 epilogue_rows<kLayoutWidth>(task, map_d, taddr, row0 + lane, row0, col0, col_shift,
-                                            lane, slab, slab_use, release);
+                                            lane, slab, slab_use, roomy, release);
             }
         }
+        if (warp == 2 && lane == 0)
+            CAMBLAS_TRACE(6);
         if (lane == 0)
             tma_store_wait_all<0>();
         __syncwarp();
+        if (warp == 2 && lane == 0)
+            CAMBLAS_TRACE(7);
     }
 
     tcgen05_fence_before();
@@ -367,6 +393,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         tcgen05_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemColumns);
     }
+    if (threadIdx.x == 0)
+        CAMBLAS_TRACE(8);
 }
 
 /* Second pass of the stream-K tail of the pair kernel: like sk_fixup, with
@@ -384,25 +412,12 @@ __global__ void __launch_bounds__(256)
     if (row >= task.rows || col >= task.cols)
         return;
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const int teams = pairs / task.r_blocks;
-    const long long total = 1ll * task.sk_cols * task.k_blocks;
-    const long long tile_begin = 1ll * blockIdx.x * task.k_blocks, tile_end = tile_begin + task.k_blocks;
-    int team = static_cast<int>(tile_begin * teams / total);
-    team = team > 0 ? team - 1 : 0;
-    for (; team < teams; ++team) {
-        const long long begin = team * total / teams, end = (team + 1) * total / teams;
-        if (begin >= tile_end)
-            break;
-        if (end <= tile_begin || begin >= end)
-            continue;
-        const int piece = begin < tile_begin ? 1 : 0;
-        const long long slot = (2ll * (team * task.r_blocks + rb) + piece) * 2 + (r >> 7);
-        const float *source = task.sk_partial + (slot * kBlockR + (r & 127)) * BN + c8;
-        const float4 low = *reinterpret_cast<const float4 *>(source);
-        const float4 high = *reinterpret_cast<const float4 *>(source + 4);
-        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
-        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
-    }
+    sum_pieces<BN>(
+        task, pairs / task.r_blocks, blockIdx.x, r & 127, c8,
+        [&](int team, int piece) {
+            return (2ll * (team * task.r_blocks + rb) + piece) * 2 + (r >> 7);
+        },
+        sum);
     __nv_bfloat16 *out = task.out;
     long long ld = task.ld_out;
     int shift = 0, limit = min(task.cols, task.cut0);

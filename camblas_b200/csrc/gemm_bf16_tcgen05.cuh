@@ -188,80 +188,211 @@ __host__ __device__ inline long long unit_count(const GemmTask &task)
     return 1ll * task.r_blocks * task.c_blocks * task.split * task.batch;
 }
 
-/* Epilogue of a stream-K piece: the raw FP32 sums of this thread's accumulator
- * row, 128 bytes per step, to its row of the partial slot. `release` is called
+/* Layout of a stream-K partial slot (128 accumulator rows x BN columns of raw
+ * FP32 sums): 32-column chunks, chunk-major, each chunk [128 rows][32 floats]
+ * with the eight 16-byte pieces of a row XOR-swizzled by (row & 7). A warp's 32
+ * rows of one chunk are therefore 4 KB of contiguous global memory, which it
+ * stages in shared memory (same swizzle, conflict-free) and writes with one bulk
+ * copy; per-lane stores of 128-byte row pieces would cost eight times the
+ * memory transactions. Float offset of the piece holding columns c..c+3: */
+__device__ __forceinline__ int partial_offset(int r, int c)
+{
+    return (c >> 5) * 4096 + r * 32 + ((((c & 31) >> 2) ^ (r & 7)) << 2);
+}
+
+/* Epilogue of a stream-K piece: the raw FP32 sums of this warp's 32 accumulator
+ * rows to rows quarter*32.. of the 128-row partial slot, one 4 KB bulk copy per
+ * 32-column chunk through the warp's two staging buffers. `release` is called
  * once every lane of the warp has read the last column of the accumulator. */
 template <int BN, typename Release>
-__device__ __forceinline__ void epilogue_partial(float *slot, uint32_t taddr, Release release)
+__device__ __forceinline__ void epilogue_partial(float *slot, uint32_t taddr, int quarter, int lane,
+                                                 uint8_t *slab, uint32_t &slab_use, bool roomy,
+                                                 Release release)
 {
-#pragma unroll 1
-    for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t acc[32];
-        tmem_ld_32x32(taddr + chunk * 32, acc);
-        tmem_ld_wait();
-        if (chunk == BN / 32 - 1)
-            release();
+    constexpr int kChunks = BN / 32;
+    static_assert(kChunks % 2 == 0, "chunks are processed in pairs");
+    /* with `roomy` the caller passes BN/32 buffers and none is reused */
+    auto store = [&](int chunk, const uint32_t (&acc)[32]) {
+        uint8_t *buffer_smem = slab + (roomy ? chunk : (slab_use & 1)) * 4096;
+        if (!roomy) {
+            /* the bulk copy that last read this buffer must be done */
+            if (lane == 0)
+                tma_store_wait_read<1>();
+            __syncwarp();
+        }
+        const uint32_t base = smem_u32(buffer_smem) + lane * 128;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4 *>(slot + chunk * 32 + i) =
-                make_uint4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        for (int piece = 0; piece < 8; ++piece)
+            st_shared_v4(base + ((piece ^ (lane & 7)) << 4), acc[piece * 4], acc[piece * 4 + 1],
+                         acc[piece * 4 + 2], acc[piece * 4 + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            bulk_store(slot + chunk * 4096 + quarter * 1024, buffer_smem, 4096);
+            tma_store_commit();
+        }
+        ++slab_use;
+    };
+    /* The tensor-memory load of the next chunk is in flight while this one is
+     * staged; its latency would otherwise be paid once per chunk. */
+    uint32_t even[32], odd[32];
+    tmem_ld_32x32(taddr, even);
+#pragma unroll 1
+    for (int chunk = 0; chunk < kChunks; chunk += 2) {
+        tmem_ld_wait();
+        tmem_ld_32x32(taddr + (chunk + 1) * 32, odd);
+        store(chunk, even);
+        tmem_ld_wait();
+        if (chunk + 2 < kChunks)
+            tmem_ld_32x32(taddr + (chunk + 2) * 32, even);
+        else
+            release();
+        store(chunk + 1, odd);
+    }
+}
+
+/* Adds, in ascending K order, the stream-K pieces of the tile in stream-K
+ * column block `sk_col` for row r (0..127 of its 128-row slot) and columns
+ * c8..c8+7. slot_of(team, piece) is the 128-row slot that team's piece went to.
+ * Loads are issued four pieces at a time so that their latencies overlap. */
+template <int BN, typename SlotOf>
+__device__ __forceinline__ void sum_pieces(const GemmTask &task, int teams, int sk_col, int r,
+                                           int c8, SlotOf slot_of, float (&sum)[8])
+{
+    const long long total = 1ll * task.sk_cols * task.k_blocks;
+    const long long tile_begin = 1ll * sk_col * task.k_blocks, tile_end = tile_begin + task.k_blocks;
+    /* start of team t's range; 32-bit division when the products are small enough */
+    const bool narrow = total * teams < 0x7fffffffll;
+    auto range_begin = [&](int t) -> long long {
+        return narrow ? static_cast<long long>(static_cast<unsigned>(t) * static_cast<unsigned>(total) /
+                                               static_cast<unsigned>(teams))
+                      : t * total / teams;
+    };
+    int team = narrow ? static_cast<int>(static_cast<unsigned>(tile_begin) *
+                                         static_cast<unsigned>(teams) / static_cast<unsigned>(total))
+                      : static_cast<int>(tile_begin * teams / total);
+    team = team > 0 ? team - 1 : 0;
+    const int low_offset = partial_offset(r, c8), high_offset = partial_offset(r, c8 + 4);
+    bool more = true;
+    long long end = range_begin(team);
+    while (more) {
+        const float *source[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            source[j] = nullptr;
+            while (more && source[j] == nullptr) {
+                if (team >= teams) {
+                    more = false;
+                    break;
+                }
+                const long long begin = end;
+                end = range_begin(team + 1);
+                if (begin >= tile_end) {
+                    more = false;
+                    break;
+                }
+                if (end > tile_begin && begin < end) {
+                    /* a team's first piece lies in the column block its range starts in */
+                    const int piece = begin < tile_begin ? 1 : 0;
+                    source[j] = task.sk_partial + slot_of(team, piece) * (128ll * BN);
+                }
+                ++team;
+            }
+        }
+        float4 low[4], high[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (source[j] != nullptr) {
+                low[j] = *reinterpret_cast<const float4 *>(source[j] + low_offset);
+                high[j] = *reinterpret_cast<const float4 *>(source[j] + high_offset);
+            }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (source[j] != nullptr) {
+                sum[0] += low[j].x, sum[1] += low[j].y, sum[2] += low[j].z, sum[3] += low[j].w;
+                sum[4] += high[j].x, sum[5] += high[j].y, sum[6] += high[j].z, sum[7] += high[j].w;
+            }
+    }
+}
+
+/* Rounds 64 accumulator columns of this thread's row (alpha applied; bias and
+ * beta*addend when present) to BF16 and writes them as eight 16-byte pieces to
+ * row `lane` of a 128-byte-swizzled 32 x 128 B staging buffer. The common case
+ * without bias and addend has its own straight-line code: with the tests of the
+ * general case inside the unrolled loop the block ran 2.5 times slower. */
+__device__ __forceinline__ void stage_row64(const GemmTask &task, const uint32_t (&acc)[2][32],
+                                            int row, int cbase, int lane, uint8_t *buffer_smem)
+{
+    const float alpha = task.alpha;
+    const uint32_t base = smem_u32(buffer_smem) + lane * 128;
+    if (task.bias == nullptr && task.beta == 0.f) {
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            const uint32_t *a = &acc[piece >> 2][(piece & 3) * 8];
+            st_shared_v4(base + ((piece ^ (lane & 7)) << 4),
+                         pack_bf16(alpha * __uint_as_float(a[0]), alpha * __uint_as_float(a[1])),
+                         pack_bf16(alpha * __uint_as_float(a[2]), alpha * __uint_as_float(a[3])),
+                         pack_bf16(alpha * __uint_as_float(a[4]), alpha * __uint_as_float(a[5])),
+                         pack_bf16(alpha * __uint_as_float(a[6]), alpha * __uint_as_float(a[7])));
+        }
+        return;
+    }
+    const bool has_bias = task.bias != nullptr;
+    const bool has_addend = task.beta != 0.f && row < task.rows;
+    const float beta = task.beta;
+    const __nv_bfloat16 *addend_row =
+        has_addend ? task.addend + static_cast<long long>(row) * task.ld_add : nullptr;
+#pragma unroll
+    for (int piece = 0; piece < 8; ++piece) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v[i] = alpha * __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
+        const int c = cbase + piece * 8;
+        if (has_bias) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c + i < task.cols)
+                    v[i] += __bfloat162float(task.bias[c + i]);
+        }
+        if (has_addend) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c + i < task.cols)
+                    v[i] = fmaf(beta, __bfloat162float(addend_row[c + i]), v[i]);
+        }
+        st_shared_v4(base + ((piece ^ (lane & 7)) << 4), pack_bf16(v[0], v[1]),
+                     pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
     }
 }
 
 /* Epilogue of a whole tile, token rows on TMEM lanes: alpha, bias and
  * beta*addend in FP32, one rounding, 64-column slabs staged with the 128-byte
- * swizzle in this warp's two 4 KB buffers and written with TMA stores (which
- * clip rows and columns beyond the matrix). `row` is this thread's row,
- * `store_row` the first row of the warp's slab. */
+ * swizzle and written with TMA stores (which clip rows and columns beyond the
+ * matrix). `row` is this thread's row, `store_row` the first row of the warp's
+ * slab. Normally `slab` is the warp's pair of 4 KB buffers, used in turn; a
+ * buffer is reused only after the TMA store that read it two slabs ago is done,
+ * and since such a store takes about 0.7 us from issue to that point, the
+ * second half of a tile waits for the first. With `roomy` the caller passes
+ * BN/64 buffers (the CTA's last tile borrows the operand ring, which is idle by
+ * then) and no slab waits. */
 template <int BN, typename Release>
 __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtensorMap *map_d,
                                               uint32_t taddr, int row, int store_row, int col0,
                                               int col_shift, int lane, uint8_t *slab,
-                                              uint32_t &slab_use, Release release)
+                                              uint32_t &slab_use, bool roomy, Release release)
 {
-#pragma unroll 1
-    for (int chunk = 0; chunk < BN / 64; ++chunk) {
-        uint32_t acc[2][32];
-        tmem_ld_32x32(taddr + chunk * 64, acc[0]);
-        tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
-        tmem_ld_wait();
-        if (chunk == BN / 64 - 1)
-            release();
-        uint8_t *buffer_smem = slab + (slab_use & 1) * 4096;
-        /* the TMA store that last read this buffer must be done */
-        if (lane == 0)
-            tma_store_wait_read<1>();
-        __syncwarp();
-        const int cbase = col0 + chunk * 64;
-#pragma unroll
-        for (int piece = 0; piece < 8; ++piece) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v[i] = task.alpha * __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
-            const int c = cbase + piece * 8;
-            if (task.bias != nullptr) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (c + i < task.cols)
-                        v[i] += __bfloat162float(task.bias[c + i]);
-            }
-            if (task.beta != 0.f && row < task.rows) {
-                const __nv_bfloat16 *source =
-                    task.addend + static_cast<long long>(row) * task.ld_add + c;
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (c + i < task.cols)
-                        v[i] = fmaf(task.beta, __bfloat162float(source[i]), v[i]);
-            }
-            uint4 packed;
-            packed.x = pack_bf16(v[0], v[1]);
-            packed.y = pack_bf16(v[2], v[3]);
-            packed.z = pack_bf16(v[4], v[5]);
-            packed.w = pack_bf16(v[6], v[7]);
-            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
-                packed;
+    constexpr int kChunks = BN / 64;
+    auto store = [&](int chunk, const uint32_t (&acc)[2][32]) {
+        uint8_t *buffer_smem = slab + (roomy ? chunk : (slab_use & 1)) * 4096;
+        if (!roomy) {
+            /* the TMA store that last read this buffer must be done */
+            if (lane == 0)
+                tma_store_wait_read<1>();
+            __syncwarp();
         }
+        const int cbase = col0 + chunk * 64;
+        stage_row64(task, acc, row, cbase, lane, buffer_smem);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -269,6 +400,35 @@ __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtens
             tma_store_commit();
         }
         ++slab_use;
+    };
+    auto load = [&](int chunk, uint32_t (&acc)[2][32]) {
+        tmem_ld_32x32(taddr + chunk * 64, acc[0]);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+    };
+    if constexpr (kChunks == 1) {
+        uint32_t acc[2][32];
+        load(0, acc);
+        tmem_ld_wait();
+        release();
+        store(0, acc);
+    } else {
+        /* The tensor-memory load of the next slab is in flight while this one is
+         * rounded and staged. */
+        static_assert(kChunks % 2 == 0, "slabs are processed in pairs");
+        uint32_t even[2][32], odd[2][32];
+        load(0, even);
+#pragma unroll 1
+        for (int chunk = 0; chunk < kChunks; chunk += 2) {
+            tmem_ld_wait();
+            load(chunk + 1, odd);
+            store(chunk, even);
+            tmem_ld_wait();
+            if (chunk + 2 < kChunks)
+                load(chunk + 2, even);
+            else
+                release();
+            store(chunk + 1, odd);
+        }
     }
 }
 
@@ -294,19 +454,19 @@ __device__ __forceinline__ void epilogue_push(const GemmTask &task, uint32_t tad
         if (chunk == BN / 64 - 1)
             release();
         uint8_t *buffer_smem = slab + (chunk & 1) * 4096;
+        {
+            const float alpha = task.alpha;
+            const uint32_t base = smem_u32(buffer_smem) + lane * 128;
 #pragma unroll
-        for (int piece = 0; piece < 8; ++piece) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v[i] = task.alpha * __uint_as_float(acc[piece >> 2][(piece & 3) * 8 + i]);
-            uint4 packed;
-            packed.x = pack_bf16(v[0], v[1]);
-            packed.y = pack_bf16(v[2], v[3]);
-            packed.z = pack_bf16(v[4], v[5]);
-            packed.w = pack_bf16(v[6], v[7]);
-            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
-                packed;
+            for (int piece = 0; piece < 8; ++piece) {
+                const uint32_t *a = &acc[piece >> 2][(piece & 3) * 8];
+                st_shared_v4(
+                    base + ((piece ^ (lane & 7)) << 4),
+                    pack_bf16(alpha * __uint_as_float(a[0]), alpha * __uint_as_float(a[1])),
+                    pack_bf16(alpha * __uint_as_float(a[2]), alpha * __uint_as_float(a[3])),
+                    pack_bf16(alpha * __uint_as_float(a[4]), alpha * __uint_as_float(a[5])),
+                    pack_bf16(alpha * __uint_as_float(a[6]), alpha * __uint_as_float(a[7])));
+            }
         }
         /* Orders this chunk's buffer writes before the reads below, and the
          * reads of the chunk before last (same buffer) before these writes. */
@@ -434,18 +594,7 @@ epilogue_rows_dynamic(const GemmTask &task, const CUtensorMap *map0, const CUten
         if (lane == 0)
             tma_store_wait_read<1>();
         __syncwarp();
-#pragma unroll
-        for (int piece = 0; piece < 8; ++piece) {
-            float v[8];
-            finish8(task, row, cbase + piece * 8, &acc[piece >> 2][(piece & 3) * 8], v);
-            uint4 packed;
-            packed.x = pack_bf16(v[0], v[1]);
-            packed.y = pack_bf16(v[2], v[3]);
-            packed.z = pack_bf16(v[4], v[5]);
-            packed.w = pack_bf16(v[6], v[7]);
-            *reinterpret_cast<uint4 *>(buffer_smem + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
-                packed;
-        }
+        stage_row64(task, acc, row, cbase, lane, buffer_smem);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -663,11 +812,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                     mbar_arrive(&tmem_empty[buffer]);
             };
-            if (Mode == kStoreRows && u.slot >= 0) {
-                float *slot = task.sk_partial +
-                              (static_cast<long long>(u.slot) * kBlockR + quarter * 32 + lane) * BN;
-                epilogue_partial<BN>(slot, taddr, release);
-            } else if constexpr (Mode == kStoreRows) {
+            if constexpr (Mode == kStoreRows) {
+              if (u.slot >= 0) {
+                float *slot = task.sk_partial + static_cast<long long>(u.slot) * kBlockR * BN;
+                epilogue_partial<BN>(slot, taddr, quarter, lane, slab, slab_use, false, release);
+              } else {
                 const CUtensorMap *map_d = &map_d0;
                 int col_shift = 0;
                 if (col0 >= task.cut0) {
@@ -676,7 +825,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                     col_shift = third ? task.cut1 : task.cut0;
                 }
                 epilogue_rows<BN>(task, map_d, taddr, row, rb * kBlockR + quarter * 32, col0,
-                                  col_shift, lane, slab, slab_use, release);
+                                  col_shift, lane, slab, slab_use, false, release);
+              }
             } else if constexpr (Mode == kStoreFloat) {
                 /* FP32 plane of a batched product: this thread owns one row and
                  * writes 32 consecutive floats per piece (128 bytes). */
@@ -810,27 +960,9 @@ __global__ void __launch_bounds__(256)
     if (row >= task.rows || col >= task.cols)
         return;
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const int teams = grid / task.r_blocks;
-    const long long total = 1ll * task.sk_cols * task.k_blocks;
-    const long long tile_begin = 1ll * blockIdx.x * task.k_blocks, tile_end = tile_begin + task.k_blocks;
-    int team = static_cast<int>(tile_begin * teams / total);
-    team = team > 0 ? team - 1 : 0;
-    for (; team < teams; ++team) {
-        const long long begin = team * total / teams, end = (team + 1) * total / teams;
-        if (begin >= tile_end)
-            break;
-        if (end <= tile_begin || begin >= end)
-            continue;
-        /* a team's first piece lies in the column block its range starts in */
-        const int piece = begin < tile_begin ? 1 : 0;
-        const int cta = team * task.r_blocks + rb;
-        const float *source =
-            task.sk_partial + ((static_cast<long long>(2 * cta + piece)) * kBlockR + r) * BN + c8;
-        const float4 low = *reinterpret_cast<const float4 *>(source);
-        const float4 high = *reinterpret_cast<const float4 *>(source + 4);
-        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
-        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
-    }
+    sum_pieces<BN>(
+        task, grid / task.r_blocks, blockIdx.x, r, c8,
+        [&](int team, int piece) { return 2ll * (team * task.r_blocks + rb) + piece; }, sum);
     __nv_bfloat16 *out = task.out;
     long long ld = task.ld_out;
     int shift = 0, limit = min(task.cols, task.cut0);

@@ -29,6 +29,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     return now;
 }
 
+#ifdef CAMBLAS_TRACE_PHASES
+/* Development aid, compiled only on request: per-CTA timestamps (ns) of the
+ * phases of the last two-SM GEMM launch. */
+__device__ unsigned long long phase_trace[148 * 16];
+#define CAMBLAS_TRACE(slot) (phase_trace[blockIdx.x * 16 + (slot)] = global_timer_ns())
+#else
+#define CAMBLAS_TRACE(slot) ((void)0)
+#endif
+
 /* Status codes written to the context status word when a bounded wait gives up. */
 enum StatusRole : unsigned {
     kRoleProducer = 1,
@@ -170,6 +179,16 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void 
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
                      "l"(map),
                  "r"(smem_u32(smem)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+/* Untiled bulk copy shared -> global of `bytes` contiguous bytes (both addresses
+ * 16-byte aligned, bytes a multiple of 16); joins the same bulk groups as the
+ * tensor stores. */
+__device__ __forceinline__ void bulk_store(void *global, const void *smem, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(global),
+                 "r"(smem_u32(smem)), "r"(bytes)
                  : "memory");
 }
 
@@ -362,6 +381,15 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t format, uint32_t m, u
 {
     return (1u << 4) | (format << 7) | (format << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
            ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+/* 16-byte store to shared memory through its 32-bit shared-window address. */
+__device__ __forceinline__ void st_shared_v4(uint32_t address, uint32_t x, uint32_t y, uint32_t z,
+                                             uint32_t w)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(x), "r"(y), "r"(z),
+                 "r"(w)
+                 : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float low, float high)

@@ -114,21 +114,37 @@ class PeerRegions:
         size = _native.library().camblas_cuda_peer_bytes(world, capacity)
         if size == 0:
             raise ValueError("peer regions support 1 to 8 ranks and a non-zero capacity")
-        own, handle = ct.c_void_p(), ct.create_string_buffer(64)
-        native.call("peer_alloc", size, ct.byref(own), handle)
+        # Failures are collected and agreed on by all ranks, so that no rank is
+        # left alone in a collective when another could not map a region.
+        own, handle, failure = ct.c_void_p(), ct.create_string_buffer(64), None
+        try:
+            native.call("peer_alloc", size, ct.byref(own), handle)
+        except RuntimeError as error:
+            failure = str(error)
         handles = [None] * world
-        dist.all_gather_object(handles, handle.raw, group=group)
+        dist.all_gather_object(handles, None if failure else handle.raw, group=group)
         memory, opened = [], []
         for r in range(world):
             if r == rank:
                 memory.append(own.value)
                 continue
             mapped = ct.c_void_p()
-            native.call("peer_open", ct.create_string_buffer(handles[r], 64), ct.byref(mapped))
+            if failure is None and handles[r] is not None:
+                try:
+                    native.call("peer_open", ct.create_string_buffer(handles[r], 64),
+                                ct.byref(mapped))
+                    opened.append(mapped.value)
+                except RuntimeError as error:
+                    failure = str(error)
             memory.append(mapped.value)
-            opened.append(mapped.value)
-        dist.barrier(group=group)
-        return cls(device, rank, world, capacity, memory, own.value, opened)
+        failures = [None] * world
+        dist.all_gather_object(failures, failure, group=group)
+        regions = cls(device, rank, world, capacity, memory, own.value, opened)
+        if any(handle_bytes is None for handle_bytes in handles) or any(failures):
+            regions.close()
+            reasons = [text for text in failures if text] or ["a rank could not allocate its region"]
+            raise RuntimeError("peer regions could not be set up: " + reasons[0])
+        return regions
 
     @classmethod
     def emulate(cls, capacity, world, device):

@@ -51,9 +51,11 @@ def main():
     for other in gathered:
         assert torch.equal(other, results[0]), "ranks hold different results"
 
-    dist.barrier()
     torch.cuda.synchronize()
-    peers.close()
+    dist.barrier()
+    peers.close(free=False)  # unmap the others' regions before anyone frees its own
+    dist.barrier()
+    peers.close(free=True)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} OK", flush=True)
