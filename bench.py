@@ -284,7 +284,7 @@ class Block:
         if os.environ.get("CAMBLAS_B200_BENCH_EXCHANGE", "peer") == "nccl":
             return nccl + " (forced)"
         try:
-            peers = tp.PeerRegions.create(TOKENS * HIDDEN, device.index)
+            peers = tp.PeerRegions.create(tp.PeerRegions.capacity_for(TOKENS, HIDDEN), device.index)
         except RuntimeError as error:
             return nccl + f" (peer regions unavailable: {error})"
         reason = None

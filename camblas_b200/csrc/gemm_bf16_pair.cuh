@@ -162,6 +162,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t *abort = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (Push) {
+        /* The kernel that sums the pushed tiles is launched as a programmatic
+         * dependent: it may become resident as soon as every CTA here has run
+         * this, and then waits on flags, not on this kernel's completion. */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -355,8 +361,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 /* partial sums of a K range split over GPUs: to the tile's owner */
                 const int unit = ((u.rb * task.c_blocks + u.cb) * 2 + static_cast<int>(rank)) * 4 +
                                  quarter;
-                epilogue_push<kLayoutWidth>(task, taddr, row0, col0, u.cb % task.push_world, unit,
-                                            lane, own_slab, release);
+                epilogue_push<kLayoutWidth>(task, taddr, u.cb % task.push_world, unit, lane, slab,
+                                            slab_use, roomy, release);
             } else if constexpr (kDynamic) {
                 epilogue_rows_dynamic(task, &map_d0, &map_d1, &map_d2, taddr, row0 + lane, row0, col0,
                                       BN, lane, own_slab, slab_use, release);

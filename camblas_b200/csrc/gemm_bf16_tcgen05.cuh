@@ -76,11 +76,11 @@ struct GemmTask {
      * the two-SM kernel, push_world >= 1). The epilogue scales the tile by alpha
      * and, instead of storing it to `out`, writes it as BF16 into the staging
      * area of the GPU that owns the tile's column block (owner = column block
-     * mod push_world): push_staging[owner] is the [rows][cols] slot that GPU
-     * keeps for this rank, in this process's address space. An epilogue warp
-     * covers a 32-row slab of the tile; when its rows are written it adds one to
-     * word `unit` of push_arrive[owner], unit = (row block * c_blocks + column
-     * block) * 8 + slab. */
+     * mod push_world): push_staging[owner] is the slot that GPU keeps for this
+     * rank, in this process's address space, laid out slab by slab (see
+     * epilogue_push). An epilogue warp covers a 32-row slab of the tile; when
+     * its copies are complete it adds one to word `unit` of push_arrive[owner],
+     * unit = (row block * c_blocks + column block) * 8 + slab. */
     int push_world;
     __nv_bfloat16 *push_staging[8];
     unsigned *push_arrive[8];
@@ -434,60 +434,75 @@ __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtens
 
 /* Push variant of the row epilogue for a product whose K range is split over
  * GPUs: alpha*acc rounded to BF16 (bias and addend are applied once, by the GPU
- * that sums the partials), written to the owner's staging slot with ordinary
- * stores. The warp's 32 rows x 64 columns go through one of its two swizzled
- * 4 KB buffers so that eight lanes write one 128-byte row segment, then a
- * system-scope release add tells the owner that this 32-row slab is complete.
- * `unit` is the slab's flag index (see GemmTask::push_arrive). */
+ * that sums the partials) and sent to the owner's staging slot. The slot is
+ * laid out by slab, not by matrix row: slab `unit` (32 rows x BN columns) is
+ * BN/64 consecutive 4 KB chunks, each [32 rows][128 bytes] with the 16-byte
+ * pieces of a row XOR-swizzled by (row & 7) - exactly the warp's staging buffer.
+ * A chunk therefore leaves as ONE 4 KB bulk copy from shared memory to the
+ * owner's memory: large NVLink writes issued by one thread, instead of 128-byte
+ * row segments stored by all lanes. When the warp's copies are complete a
+ * system-scope release add tells the owner that the slab is there. Rows and
+ * columns beyond the matrix carry zeros (their operands were zero-filled).
+ * `slab`/`roomy` as in epilogue_rows. */
 template <int BN, typename Release>
-__device__ __forceinline__ void epilogue_push(const GemmTask &task, uint32_t taddr, int store_row,
-                                              int col0, int owner, int unit, int lane,
-                                              uint8_t *slab, Release release)
+__device__ __forceinline__ void epilogue_push(const GemmTask &task, uint32_t taddr, int owner,
+                                              int unit, int lane, uint8_t *slab,
+                                              uint32_t &slab_use, bool roomy, Release release)
 {
-    __nv_bfloat16 *destination = task.push_staging[owner];
-#pragma unroll 1
-    for (int chunk = 0; chunk < BN / 64; ++chunk) {
-        uint32_t acc[2][32];
+    constexpr int kChunks = BN / 64;
+    static_assert(kChunks % 2 == 0, "slabs are processed in pairs");
+    __nv_bfloat16 *destination =
+        task.push_staging[owner] + static_cast<long long>(unit) * (32 * BN);
+    const float alpha = task.alpha;
+    auto send = [&](int chunk, const uint32_t (&acc)[2][32]) {
+        uint8_t *buffer_smem = slab + (roomy ? chunk : (slab_use & 1)) * 4096;
+        if (!roomy) {
+            if (lane == 0)
+                tma_store_wait_read<1>();
+            __syncwarp();
+        }
+        const uint32_t base = smem_u32(buffer_smem) + lane * 128;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            const uint32_t *a = &acc[piece >> 2][(piece & 3) * 8];
+            st_shared_v4(base + ((piece ^ (lane & 7)) << 4),
+                         pack_bf16(alpha * __uint_as_float(a[0]), alpha * __uint_as_float(a[1])),
+                         pack_bf16(alpha * __uint_as_float(a[2]), alpha * __uint_as_float(a[3])),
+                         pack_bf16(alpha * __uint_as_float(a[4]), alpha * __uint_as_float(a[5])),
+                         pack_bf16(alpha * __uint_as_float(a[6]), alpha * __uint_as_float(a[7])));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            bulk_store(destination + chunk * 2048, buffer_smem, 4096);
+            tma_store_commit();
+        }
+        ++slab_use;
+    };
+    auto load = [&](int chunk, uint32_t (&acc)[2][32]) {
         tmem_ld_32x32(taddr + chunk * 64, acc[0]);
         tmem_ld_32x32(taddr + chunk * 64 + 32, acc[1]);
+    };
+    uint32_t even[2][32], odd[2][32];
+    load(0, even);
+#pragma unroll 1
+    for (int chunk = 0; chunk < kChunks; chunk += 2) {
         tmem_ld_wait();
-        if (chunk == BN / 64 - 1)
+        load(chunk + 1, odd);
+        send(chunk, even);
+        tmem_ld_wait();
+        if (chunk + 2 < kChunks)
+            load(chunk + 2, even);
+        else
             release();
-        uint8_t *buffer_smem = slab + (chunk & 1) * 4096;
-        {
-            const float alpha = task.alpha;
-            const uint32_t base = smem_u32(buffer_smem) + lane * 128;
-#pragma unroll
-            for (int piece = 0; piece < 8; ++piece) {
-                const uint32_t *a = &acc[piece >> 2][(piece & 3) * 8];
-                st_shared_v4(
-                    base + ((piece ^ (lane & 7)) << 4),
-                    pack_bf16(alpha * __uint_as_float(a[0]), alpha * __uint_as_float(a[1])),
-                    pack_bf16(alpha * __uint_as_float(a[2]), alpha * __uint_as_float(a[3])),
-                    pack_bf16(alpha * __uint_as_float(a[4]), alpha * __uint_as_float(a[5])),
-                    pack_bf16(alpha * __uint_as_float(a[6]), alpha * __uint_as_float(a[7])));
-            }
-        }
-        /* Orders this chunk's buffer writes before the reads below, and the
-         * reads of the chunk before last (same buffer) before these writes. */
-        __syncwarp();
-        const int piece = lane & 7;
-        const int c = col0 + chunk * 64 + piece * 8;
-#pragma unroll
-        for (int step = 0; step < 8; ++step) {
-            const int r = step * 4 + (lane >> 3);
-            const uint4 value =
-                *reinterpret_cast<const uint4 *>(buffer_smem + r * 128 + ((piece ^ (r & 7)) << 4));
-            const int row = store_row + r;
-            if (row < task.rows && c < task.cols)
-                *reinterpret_cast<uint4 *>(destination + static_cast<long long>(row) * task.cols +
-                                           c) = value;
-        }
+        send(chunk + 1, odd);
     }
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0)
+    if (lane == 0) {
+        tma_store_wait_all<0>(); /* the copies have been written, not only read */
+        __threadfence_system();
         flag_add_release_system(task.push_arrive[owner] + unit, 1u);
+    }
+    __syncwarp();
 }
 
 /* alpha*acc + bias + beta*addend for eight consecutive columns of one row. */

@@ -10,19 +10,22 @@
  *
  *   1. gemm_bf16_pair<.., Push>: the two-SM tcgen05 product of this GPU's K
  *      range. Its epilogue does not store a local result: every 256 x BN tile
- *      is written, rounded to BF16, straight into the staging slot that the
- *      OWNER of the tile's column block keeps for this GPU (owner = column
- *      block mod world), with ordinary stores over NVLink, 32-row slab by
- *      slab, each followed by a system-scope release add on the owner's
- *      arrival word for that slab. Tiles leave as they finish, so the transfer
- *      of early tiles overlaps the multiplication of later ones.
- *   2. peer_reduce_broadcast: on the owner, one CTA per slab waits (bounded)
- *      until all `world` partial slabs are there, clears the word, adds the
- *      partials in rank order in FP32, adds bias and residual, rounds once and
- *      writes the finished slab into the result buffer of EVERY GPU, then adds
- *      one to each GPU's delivery counter.
- *   3. peer_wait_delivered: waits (bounded) until this GPU's delivery counter
- *      has reached the number of slabs of the whole matrix, and clears it.
+ *      is sent, rounded to BF16, straight into the staging slot that the OWNER
+ *      of the tile's column block keeps for this GPU (owner = column block mod
+ *      world) as 4 KB bulk copies from shared memory over NVLink, 32-row slab
+ *      by slab, each slab followed by a system-scope release add on the
+ *      owner's arrival word for it. Tiles leave as they finish, so the
+ *      transfer of early tiles overlaps the multiplication of later ones.
+ *   2. peer_reduce_broadcast, launched as a programmatic dependent so that it
+ *      is resident before the product ends: on the owner, one CTA per slab
+ *      waits (bounded) until all `world` partial slabs are there, clears the
+ *      word, adds the partials in rank order in FP32, adds bias and residual,
+ *      rounds once and writes the finished slab into the result buffer of
+ *      EVERY GPU, then adds one to each GPU's delivery counter.
+ *   3. the wait (bounded) until this GPU's delivery counter has reached the
+ *      number of slabs of the whole matrix: done by the CTA of launch 2 that
+ *      finishes last, or by the small kernel peer_wait_delivered when the
+ *      phases are issued separately or this GPU owns no tile.
  *
  * Because every slab is summed by exactly one GPU in a fixed order, all GPUs
  * hold bit-identical results and repeated calls give identical bits.
@@ -31,7 +34,8 @@
  *   [result: capacity BF16][staging: world slots of capacity BF16][flag words]
  * obtained from camblas_cuda_peer_alloc and made visible to the other
  * processes with CUDA IPC handles (camblas_cuda_peer_open). `capacity` bounds
- * rows * outputs of a call. Flag words are cleared by their consumer, so the
+ * rows * outputs of a call, both rounded up to multiples of 256 (staging holds
+ * whole tiles). Flag words are cleared by their consumer, so the
  * region is ready for the next call when phase 3 has run; nothing depends on
  * a call count.
  *
@@ -62,7 +66,8 @@ namespace peer
 {
 
 constexpr int kMaxWorld = 8;
-constexpr int kFlagWords = 65536; /* word 0: delivery counter; words 64..: arrival words */
+constexpr int kFlagWords = 65536; /* word 0: delivery counter; word 1: CTAs of the reduction
+                                     done; words 64..: arrival words */
 constexpr int kFlagHeader = 64;
 constexpr int kMaxUnits = kFlagWords - kFlagHeader;
 
@@ -119,9 +124,25 @@ __device__ __forceinline__ void accumulate8(float (&sum)[8], const uint4 &packed
     }
 }
 
+/* Waits until `expected` slabs have been delivered to this GPU, then clears the counter. */
+__device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned expected,
+                                               unsigned *status)
+{
+    if (sm100::flag_wait_system(delivered, expected))
+        sm100::flag_store_relaxed_system(delivered, 0u);
+    else
+        atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
+}
+
 /* grid = (column blocks this GPU owns, 8 * r_blocks); 256 threads. Each CTA
- * finishes one 32-row slab of one owned tile. */
-__global__ void __launch_bounds__(256) peer_reduce_broadcast(const ReduceTask task)
+ * finishes one 32-row slab of one owned tile: it waits for the slab's `world`
+ * partial copies (staging layout: see sm100::epilogue_push), adds them in rank
+ * order, applies bias and residual, rounds once and writes the slab, now as
+ * ordinary matrix rows (a warp stores 512 contiguous bytes of one row), into
+ * every GPU's result. With `wait_inline` the CTA that finishes last also waits
+ * for the deliveries to this GPU, which saves the launch of peer_wait_delivered. */
+__global__ void __launch_bounds__(256)
+    peer_reduce_broadcast(const ReduceTask task, unsigned expected, int wait_inline)
 {
     __shared__ int failed;
     const int cb = task.rank + blockIdx.x * task.world;
@@ -137,66 +158,81 @@ __global__ void __launch_bounds__(256) peer_reduce_broadcast(const ReduceTask ta
         failed = ok ? 0 : 1;
     }
     __syncthreads();
-    if (failed)
-        return;
-    const int row0 = rb * 256 + slab * 32;
-    const int pieces_per_row = task.width >> 3;
-    const int pieces = 32 * pieces_per_row;
-    for (int p = threadIdx.x; p < pieces; p += 256) {
-        const int r = p / pieces_per_row;
-        const int row = row0 + r;
-        const int c = cb * task.width + (p - r * pieces_per_row) * 8;
-        if (row >= task.rows || c >= task.cols)
-            continue;
-        const long long offset = static_cast<long long>(row) * task.cols + c;
-        uint4 part[kMaxWorld];
+    if (!failed) {
+        const int row0 = rb * 256 + slab * 32;
+        const int pieces_per_row = task.width >> 3; /* 16-byte pieces in a slab row: 32 or 16 */
+        const int rows_per_step = 256 / pieces_per_row;
+        const int steps = 32 / rows_per_step;
+        const int piece = threadIdx.x % pieces_per_row;
+        const long long unit_offset = static_cast<long long>(unit) * (32 * task.width);
+        /* two steps at a time: up to sixteen 16-byte loads in flight per thread */
+#pragma unroll 1
+        for (int step = 0; step < steps; step += 2) {
+            uint4 part[2][kMaxWorld];
 #pragma unroll
-        for (int s = 0; s < kMaxWorld; ++s)
-            if (s < task.world)
-                part[s] = __ldcg(reinterpret_cast<const uint4 *>(task.staging +
-                                                                 s * task.slot_elements + offset));
-        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int half = 0; half < 2; ++half) {
+                const int r = (step + half) * rows_per_step + threadIdx.x / pieces_per_row;
+                const long long offset =
+                    unit_offset + (piece >> 3) * 2048 + r * 64 + (((piece & 7) ^ (r & 7)) << 3);
 #pragma unroll
-        for (int s = 0; s < kMaxWorld; ++s)
-            if (s < task.world)
-                accumulate8(sum, part[s]);
-        if (task.bias != nullptr) {
-            const uint4 b = *reinterpret_cast<const uint4 *>(task.bias + c);
-            accumulate8(sum, b);
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world)
+                        part[half][s] = __ldcg(reinterpret_cast<const uint4 *>(
+                            task.staging + s * task.slot_elements + offset));
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = (step + half) * rows_per_step + threadIdx.x / pieces_per_row;
+                const int row = row0 + r, c = cb * task.width + piece * 8;
+                if (row >= task.rows || c >= task.cols)
+                    continue;
+                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world)
+                        accumulate8(sum, part[half][s]);
+                if (task.bias != nullptr)
+                    accumulate8(sum, *reinterpret_cast<const uint4 *>(task.bias + c));
+                if (task.residual != nullptr)
+                    accumulate8(sum, *reinterpret_cast<const uint4 *>(
+                                         task.residual +
+                                         static_cast<long long>(row) * task.ld_residual + c));
+                uint4 packed;
+                packed.x = sm100::pack_bf16(sum[0], sum[1]);
+                packed.y = sm100::pack_bf16(sum[2], sum[3]);
+                packed.z = sm100::pack_bf16(sum[4], sum[5]);
+                packed.w = sm100::pack_bf16(sum[6], sum[7]);
+                const long long target_offset = static_cast<long long>(row) * task.cols + c;
+                /* start with the next GPU so that the owners do not all write to the same one */
+                for (int hop = 1; hop <= task.world; ++hop) {
+                    int target = task.rank + hop;
+                    if (target >= task.world)
+                        target -= task.world;
+                    *reinterpret_cast<uint4 *>(task.result[target] + target_offset) = packed;
+                }
+            }
         }
-        if (task.residual != nullptr) {
-            const uint4 b = *reinterpret_cast<const uint4 *>(
-                task.residual + static_cast<long long>(row) * task.ld_residual + c);
-            accumulate8(sum, b);
-        }
-        uint4 packed;
-        packed.x = sm100::pack_bf16(sum[0], sum[1]);
-        packed.y = sm100::pack_bf16(sum[2], sum[3]);
-        packed.z = sm100::pack_bf16(sum[4], sum[5]);
-        packed.w = sm100::pack_bf16(sum[6], sum[7]);
-        /* start with the next GPU so that the owners do not all write to the same one first */
-        for (int step = 1; step <= task.world; ++step) {
-            int target = task.rank + step;
-            if (target >= task.world)
-                target -= task.world;
-            *reinterpret_cast<uint4 *>(task.result[target] + offset) = packed;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (!failed && threadIdx.x < task.world)
+        sm100::flag_add_release_system(task.delivered[threadIdx.x], 1u);
+    if (wait_inline && threadIdx.x == 0) {
+        /* word 1 of this GPU's flags counts the CTAs of this launch that are done */
+        unsigned *ticket = task.delivered[task.rank] + 1;
+        const unsigned done = atomicAdd(ticket, 1u);
+        if (done == gridDim.x * gridDim.y - 1) {
+            *ticket = 0;
+            wait_delivered(task.delivered[task.rank], expected, task.status);
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < task.world)
-        sm100::flag_add_release_system(task.delivered[threadIdx.x], 1u);
 }
 
 /* One thread: wait until `expected` slabs have been delivered to this GPU. */
 __global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsigned *status)
 {
-    if (threadIdx.x != 0)
-        return;
-    if (sm100::flag_wait_system(delivered, expected))
-        sm100::flag_store_relaxed_system(delivered, 0u);
-    else
-        atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
+    if (threadIdx.x == 0)
+        wait_delivered(delivered, expected, status);
 }
 
 struct Call {
@@ -226,6 +262,12 @@ inline int run(camblas_cuda_context *context, const Call &call)
     const long long units = 1ll * r_blocks * c_blocks * 8;
     if (units > kMaxUnits)
         return fail(context, "row-parallel product has more slabs than the region has flag words", 1);
+    /* staging holds whole tiles */
+    if (size_t(r_blocks) * 256 * size_t(c_blocks) * bn > own.slot_elements)
+        return fail(context,
+                    "row-parallel result exceeds the peer region capacity (rows and outputs count "
+                    "rounded up to multiples of 256)",
+                    1);
 
     if (call.phases & 1) {
         sm100::GemmTask task{};
@@ -265,6 +307,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
             return fail(context, "two-SM tcgen05 BF16 GEMM with peer push", error);
         context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
     }
+    bool wait_inline = false;
     if (call.phases & 2) {
         const int owned = (c_blocks - call.rank + call.world - 1) / call.world;
         if (owned > 0) {
@@ -282,14 +325,27 @@ inline int run(camblas_cuda_context *context, const Call &call)
                 task.delivered[r] = regions[r].flags;
             }
             task.status = context->status;
-            dim3 grid(owned, 8 * r_blocks);
-            peer_reduce_broadcast<<<grid, 256, 0, context->stream>>>(task);
-            int status = launched(context, "peer reduction and broadcast");
-            if (status != 0)
-                return status;
+            /* Launched as a programmatic dependent of the product kernel: its CTAs
+             * may become resident while that kernel still runs (it says so at its
+             * start) and wait on the arrival words, not on the kernel boundary. */
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(owned, 8 * r_blocks);
+            config.blockDim = dim3(256);
+            config.stream = context->stream;
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attribute[0].val.programmaticStreamSerializationAllowed = 1;
+            config.attrs = attribute;
+            config.numAttrs = 1;
+            wait_inline = (call.phases & 4) != 0;
+            cudaError_t error = cudaLaunchKernelEx(&config, peer_reduce_broadcast, task,
+                                                   unsigned(units), int(wait_inline));
+            if (error != cudaSuccess)
+                return fail(context, "peer reduction and broadcast", error);
+            context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
         }
     }
-    if (call.phases & 4) {
+    if ((call.phases & 4) && !wait_inline) {
         peer_wait_delivered<<<1, 32, 0, context->stream>>>(own.flags, unsigned(units),
                                                            context->status);
         return launched(context, "peer delivery wait");

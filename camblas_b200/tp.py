@@ -83,13 +83,20 @@ class PeerRegions:
 
     Every rank owns a region that holds the result, one staging slot per rank
     and flag words (``include/camblas_cuda.h``); ``memory[r]`` is rank ``r``'s
-    region as mapped here. ``capacity`` bounds ``rows * outputs`` of a call.
+    region as mapped here. ``capacity`` bounds ``rows * outputs`` of a call, both
+    rounded up to multiples of 256 (``capacity_for``).
 
     Use ``PeerRegions.create`` with one process per GPU (regions are exchanged
     as CUDA IPC handles through ``all_gather_object``), or
     ``PeerRegions.emulate`` to get all ranks' views in one process on one GPU,
     which is how the single-GPU tests drive the kernels.
     """
+
+    @staticmethod
+    def capacity_for(rows, outputs):
+        """Capacity that fits calls of up to ``rows`` x ``outputs``: staging holds whole
+        256 x 256 tiles, so both extents count rounded up to multiples of 256."""
+        return (-(-rows // 256) * 256) * (-(-outputs // 256) * 256)
 
     def __init__(self, device, rank, world, capacity, memory, owned, opened):
         self.device, self.rank, self.world, self.capacity = device, rank, world, capacity

@@ -142,7 +142,7 @@ int camblas_cuda_linear_bf16_static(void *stream, int rows, int inner, int outpu
  * One process per GPU. Every GPU owns one *peer region*,
  *   [result: capacity BF16][staging: world slots of capacity BF16][flag words],
  * of camblas_cuda_peer_bytes(world, capacity) bytes, where capacity bounds
- * rows * outputs of any later call. camblas_cuda_peer_alloc allocates and
+ * rows * outputs of any later call, each rounded up to a multiple of 256. camblas_cuda_peer_alloc allocates and
  * clears it and, when `handle` is not NULL, writes a 64-byte CUDA IPC handle
  * that another process on the same machine passes to camblas_cuda_peer_open to
  * map the region into its own address space (the caller carries the bytes
@@ -172,22 +172,23 @@ int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memory, int wor
  * its own copies (they must be equal); they are added once, in FP32, before the
  * single rounding of the sum of the BF16-rounded partial products.
  *
- * Three launches on the context's stream, asynchronous: (1) the two-SM tcgen05
- * product whose epilogue writes each tile straight into the staging slot of
+ * Launches on the context's stream, asynchronous: (1) the two-SM tcgen05
+ * product whose epilogue sends each tile straight into the staging slot of
  * the GPU that owns the tile (owner = column block mod world) over NVLink and
  * raises that GPU's arrival word, tile by tile while later tiles are still
  * being multiplied; (2) on the owner, a kernel that waits for the `world`
  * partials of each 32-row slab, adds them in rank order, applies bias and
  * residual and writes the finished slab into every GPU's result; (3) a wait
- * until every slab has been delivered to this GPU. `phases` is a bit mask of
- * the launches to issue, 7 in production; the parts exist so that a single
+ * until every slab has been delivered to this GPU (part of launch 2 when both
+ * are requested together). `phases` is a bit mask of the steps to issue, 7 in
+ * production; the parts exist so that a single
  * process can drive several ranks on one GPU in turn (all of 1, then all of 2,
  * then all of 4), where no kernel may wait for one that has not been launched.
  * Waits inside the kernels give up after five seconds and record a device
  * status (camblas_cuda_device_status), after which camblas_cuda_peer_reset is
  * needed. The result may be overwritten by the next call: consume it with work
- * enqueued on the same stream before that call. rows * outputs <= capacity;
- * outputs, ldx, ldw and ldr multiples of 8; x, w, bias, residual 16-byte
+ * enqueued on the same stream before that call. rows * outputs, each rounded up
+ * to a multiple of 256, <= capacity; outputs, ldx, ldw and ldr multiples of 8; x, w, bias, residual 16-byte
  * aligned; world <= 8. */
 int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, int world,
                                        size_t capacity, void *const *memory, int phases, int rows,

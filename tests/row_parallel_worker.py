@@ -26,7 +26,7 @@ def main():
     w = (torch.randn((outputs, inner), generator=generator) * 0.05).bfloat16().cuda()
     bias = torch.randn((outputs,), generator=generator).bfloat16().cuda()
 
-    peers = PeerRegions.create(rows * outputs, device)
+    peers = PeerRegions.create(PeerRegions.capacity_for(rows, outputs), device)
     fused = RowParallelLinear(w, rank, world, bias=bias, peers=peers)
     plain = RowParallelLinear(w, rank, world, bias=bias)
     x_local = fused.slice_input(x)

@@ -64,7 +64,7 @@ def close_all(views):
 def test_matches_oracle_and_ranks_agree(world, rows, inner, outputs):
     rng = np.random.default_rng(20261004 + world * 1000 + rows)
     x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
-    views = PeerRegions.emulate(rows * outputs, world, 0)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
     try:
         first = run_emulated(views, xs, ws)
         second = run_emulated(views, xs, ws)
@@ -85,7 +85,7 @@ def test_bias_and_residual_enter_once():
     x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
     bias = normal_bits(rng, (outputs,))
     residual = normal_bits(rng, (rows, outputs))
-    views = PeerRegions.emulate(rows * outputs, world, 0)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
     try:
         got = run_emulated(views, xs, ws, bits_to_tensor(bias), bits_to_tensor(residual))
     finally:
@@ -106,7 +106,7 @@ def test_exact_integers_are_bit_exact():
     residual = oracle.bf16_bits(rng.integers(-8, 9, (rows, outputs)).astype(np.float32))
     xs = [bits_to_tensor(x[:, r * inner:(r + 1) * inner]) for r in range(world)]
     ws = [bits_to_tensor(w[:, r * inner:(r + 1) * inner]) for r in range(world)]
-    views = PeerRegions.emulate(rows * outputs, world, 0)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
     try:
         got = run_emulated(views, xs, ws, bits_to_tensor(bias), bits_to_tensor(residual))
     finally:
@@ -121,7 +121,7 @@ def test_narrow_tiles_give_the_same_sum(monkeypatch):
     world, rows, inner, outputs = 2, 512, 320, 1536
     rng = np.random.default_rng(99)
     x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
-    views = PeerRegions.emulate(rows * outputs, world, 0)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
     try:
         wide = run_emulated(views, xs, ws)
         monkeypatch.setenv("CAMBLAS_B200_PUSH_WIDTH", "128")
