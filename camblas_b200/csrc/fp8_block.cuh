@@ -12,12 +12,9 @@
  *    being multiplied: acc = fma(block, a_scale*w_scale, acc), blocks in
  *    ascending K order - the recurrence of the reference's block-128 decode
  *    kernel (camblas/_hopper.py:118-126, 168-182), applied to every row.
- *    The rate of this kernel for many rows is set by draining the accumulator:
- *    128 x BN FP32 values leave tensor memory once per 128-deep K block, and on
- *    B200 that read shares the TMEM port with the MMA's own accumulation. A
- *    two-SM variant with 256-column tiles and eight promotion warps was built
- *    and measured at half the speed of this kernel (it doubles the values
- *    drained per SM and K block), so it is not kept.
+ *    For more than 64 token rows fp8_block_rows (eight promotion warps, four
+ *    accumulator buffers) replaces the row mode of this kernel; what bounds
+ *    it is written there.
  *    Store modes as in the BF16 kernel: token rows on TMEM lanes with a TMA
  *    store, or operands swapped for up to 64 tokens, optionally with a K split
  *    through FP32 scratch and an ordered reduction.
@@ -386,6 +383,249 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
     }
 }
 
+/* ---- 2b. many token rows: eight promotion warps, four accumulator buffers ------ */
+
+/* Row mode for more than 64 token rows. Two warps share each quarter of the
+ * tensor-memory lanes and take 64 columns each (64 accumulator registers, one
+ * 64-column load, 64 FMAs per K block), so every scheduler has two promotion
+ * warps to interleave, and the accumulator ring has four 128-column buffers
+ * (all 512 tensor-memory columns) so that the MMA issuer can run up to three K
+ * blocks ahead. Bit-identical to the four-warp kernel above and 4-5 % faster.
+ * The arithmetic: acc = fma(block sum, a_scale * w_scale, acc) in ascending K
+ * order, one rounding at the end.
+ *
+ * What bounds it (measured on B200, M=4096): not the promotion. With the
+ * tensor-memory loads taken out the kernel takes the same time, and the tensor
+ * pipe is busy 29 % of the cycles at exactly the FP8 rate when it is. A 128 x
+ * 128 tile needs 32 KB of operands per 128-deep K block, i.e. per 256 MMA
+ * cycles, and an SM takes in 40-50 bytes per cycle from L2 with the 192 KB of
+ * stages it can keep in flight - the same feed that the BF16 two-SM kernel
+ * spends on four times the multiplications. Wider tiles would fix the feed but
+ * need 256 accumulator columns per row in registers next to the loaded block,
+ * which ten warps cannot hold (168 registers per thread) and more warps even
+ * less. A two-SM variant (256 x 128 tiles, 24 KB of operands per K block and
+ * SM, same promotion) was built twice, gave the same bits and ran at half the
+ * speed: with one accumulator hand-over per K block instead of per tile, the
+ * round trip between the leader's MMA issuer and the other CTA's promotion
+ * warps (remote barrier arrivals) is paid every 256 MMA cycles and the four
+ * buffers cannot cover it. */
+constexpr int kRowsThreads = 320; /* producer, MMA issuer, eight promotion warps */
+constexpr int kRowsBuffers = 4;
+
+template <int Stages> struct RowsSmem {
+    static constexpr int kStageBytes = 2 * 128 * 128; /* 128 rows x 128 B of each operand */
+    static constexpr int kStaging = 8 * 4096;         /* one 32 x 128 B slab per promotion warp */
+    static constexpr int kTotal = Stages * kStageBytes + kStaging + 256 + 1024;
+};
+
+template <int Stages>
+__global__ void __launch_bounds__(kRowsThreads, 1)
+    fp8_block_rows(const __grid_constant__ CUtensorMap map_p,
+                   const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_d, const BlockTask task)
+{
+    using namespace sm100;
+    using Layout = RowsSmem<Stages>;
+    constexpr int BN = 128;
+    constexpr uint32_t kTmemColumns = kRowsBuffers * BN;
+
+    extern __shared__ uint8_t raw_smem[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *staging = smem + Stages * Layout::kStageBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(staging + Layout::kStaging);
+    uint64_t *empty = full + Stages;
+    uint64_t *tmem_full = empty + Stages;
+    uint64_t *tmem_empty = tmem_full + kRowsBuffers;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + kRowsBuffers);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int units = task.r_blocks * task.c_blocks;
+    const int groups = task.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < kRowsBuffers; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 8);
+        }
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_d);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto decode = [&](int tile, int &rb, int &cb) {
+        int per_panel = task.panel * task.c_blocks;
+        int panel = tile / per_panel;
+        int local = tile - panel * per_panel;
+        int height = min(task.panel, task.r_blocks - panel * task.panel);
+        cb = local / height;
+        rb = panel * task.panel + local - cb * height;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            /* activations are re-read by every column tile, weights by the row
+             * tiles of one panel: keep both in L2 */
+            const uint64_t keep = policy_evict_last();
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+                int rb, cb;
+                decode(unit, rb, cb);
+                for (int kb = 0; kb < groups; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                        report(task.status, abort, kRoleProducer);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *p_tile = smem + stage * Layout::kStageBytes;
+                    mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
+                    tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockDepth, rb * kBlockR,
+                                     keep);
+                    tma_load_2d_hint(p_tile + 128 * 128, &map_q, &full[stage], kb * kBlockDepth,
+                                     cb * BN, keep);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok)
+                for (uint32_t s = 0; s < Stages; ++s)
+                    if (armed & (1u << s))
+                        for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                            if (mbar_try_wait(&full[s], (armed_parity >> s) & 1))
+                                break;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(0, kBlockR, BN, 0, 0); /* E4M3 x E4M3 */
+            uint32_t stage = 0, phase = 0, block = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+                for (int kb = 0; kb < groups; ++kb, ++block) {
+                    const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
+                    if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                        report(task.status, abort, kRoleMmaTmemEmpty);
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&full[stage], phase, abort)) {
+                        report(task.status, abort, kRoleMma);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                    const uint64_t desc_p = desc_kmajor_sw128(p_address);
+                    const uint64_t desc_q = desc_kmajor_sw128(p_address + 128 * 128);
+                    const uint32_t tmem_d = tmem_base + buffer * BN;
+#pragma unroll
+                    for (int k = 0; k < kBlockDepth / 32; ++k) /* 32 E4M3 = 32 bytes per MMA */
+                        umma_f8(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, k > 0 ? 1u : 0u);
+                    umma_commit(&empty[stage]);
+                    umma_commit(&tmem_full[buffer]);
+                    if (++stage == Stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;       /* tensor-memory lanes 32*quarter .. +31 */
+        const int half = (warp - 2) >> 2;   /* columns 64*half .. +63 of the tile */
+        uint8_t *slab = staging + (warp - 2) * 4096;
+        uint32_t block = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+            int rb, cb;
+            decode(unit, rb, cb);
+            const int row = rb * kBlockR + quarter * 32 + lane;
+            float acc[64];
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+                acc[i] = 0.f;
+            const float *lane_scale =
+                task.p_scale + static_cast<long long>(min(row, task.rows - 1)) * groups;
+            const float *band_scale = task.q_scale + static_cast<long long>(cb) * groups;
+            float own = lane_scale[0], band = band_scale[0];
+            bool ok = true;
+            for (int kb = 0; kb < groups; ++kb, ++block) {
+                const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
+                const float s = __fmul_rn(own, band);
+                if (kb + 1 < groups) { /* next block's scales travel while this one is added */
+                    own = lane_scale[kb + 1];
+                    band = band_scale[kb + 1];
+                }
+                if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
+                    report(task.status, abort, kRoleEpilogueFull);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                uint32_t piece[64];
+                tmem_ld_32x64(tmem_base + buffer * BN + half * 64 +
+                                  (static_cast<uint32_t>(quarter * 32) << 16),
+                              piece);
+                tmem_ld_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&tmem_empty[buffer]);
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    acc[i] = fmaf(__uint_as_float(piece[i]), s, acc[i]);
+            }
+            if (!ok)
+                break;
+            /* this warp's 32 rows x 64 columns: one swizzled 4 KB slab, one TMA store */
+            if (lane == 0)
+                tma_store_wait_read<0>();
+            __syncwarp();
+            const uint32_t base = smem_u32(slab) + lane * 128;
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+                const float *v = acc + piece * 8;
+                st_shared_v4(base + ((piece ^ (lane & 7)) << 4), pack_bf16(v[0], v[1]),
+                             pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&map_d, slab, cb * BN + half * 64, rb * kBlockR + quarter * 32);
+                tma_store_commit();
+            }
+        }
+        if (lane == 0)
+            tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
 /* ---- 3. single token, block-32 scales (reference ABI) ------------------------- */
 
 __device__ __forceinline__ float e4m3_to_float(uint32_t byte)
@@ -494,6 +734,9 @@ template <int BN, int Stages, int Mode> int prepare_kernel()
 inline int prepare_kernels()
 {
     int status = prepare_kernel<128, 6, kStoreRows>();
+    status |= int(cudaFuncSetAttribute(fp8_block_rows<6>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       RowsSmem<6>::kTotal));
+
     status |= prepare_kernel<16, 8, kStoreColumns>();
     status |= prepare_kernel<32, 8, kStoreColumns>();
     status |= prepare_kernel<64, 8, kStoreColumns>();
@@ -543,7 +786,15 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
                             size_t(ldo) * 2, 64, 32);
         if (!ok)
             return host::fail(context, "tensor map encoding", 1);
-        launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
+        const char *variant = std::getenv("CAMBLAS_B200_FP8_ROWS"); /* tuning aid: "four" */
+        if (variant != nullptr && std::strcmp(variant, "four") == 0) {
+            launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
+        } else {
+            const int units = task.r_blocks * task.c_blocks;
+            const int grid = units < context->sm_count ? units : context->sm_count;
+            fp8_block_rows<6><<<grid, kRowsThreads, RowsSmem<6>::kTotal, context->stream>>>(p, qm, d,
+                                                                                           task);
+        }
         return host::launched(context, "tcgen05 FP8 block GEMM");
     }
     /* few tokens: weights on the 128-row side, tokens on the narrow side */
