@@ -232,6 +232,58 @@ def silu_multiply(gate, up):
     return out
 
 
+def interleave_gate_up(weight, block=128):
+    """Permute a packed ``[gate; up]`` weight for ``gate_up_swiglu`` (done once, at load time).
+
+    ``weight`` is ``[2 * intermediate, inner]`` with the gate rows first. The
+    result holds, for every block ``j`` of 128 features, the gate rows of the
+    block followed by its up rows, so that one 256-column tile of the GEMM
+    carries both halves of 128 outputs.
+    """
+    _require(weight.dim() == 2 and weight.shape[0] % (2 * block) == 0,
+             "gate_up weight rows must be a multiple of 256")
+    intermediate = weight.shape[0] // 2
+    gate = weight[:intermediate].reshape(intermediate // block, block, weight.shape[1])
+    up = weight[intermediate:].reshape(intermediate // block, block, weight.shape[1])
+    return torch.stack((gate, up), dim=1).reshape(2 * intermediate, weight.shape[1]).contiguous()
+
+
+def gate_up_swiglu(x, weight_interleaved):
+    """Return ``silu_multiply(x @ Wg.T, x @ Wu.T)`` from one GEMM pass.
+
+    ``weight_interleaved`` comes from ``interleave_gate_up``. The roundings are
+    those of the two-step path (BF16 GEMM outputs, then
+    ``inference_fusion.cuh:19-29``), so the result equals
+    ``silu_multiply(*linear(x, W).chunk(2, -1))`` whenever the GEMM sums agree.
+    """
+    _check_tensor(x, x)
+    _check_tensor(weight_interleaved, x, "weight")
+    _require(x.dtype == torch.bfloat16, "gate_up_swiglu takes BF16 operands")
+    _require(x.dim() >= 1 and weight_interleaved.dim() == 2
+             and x.shape[-1] == weight_interleaved.shape[1]
+             and weight_interleaved.shape[0] % 256 == 0,
+             "gate_up_swiglu requires x [..., inner] and an interleaved [2*intermediate, inner] weight")
+    inner, intermediate = weight_interleaved.shape[1], weight_interleaved.shape[0] // 2
+    rows = 1
+    for size in x.shape[:-1]:
+        rows *= size
+    _require(rows <= _INT_MAX, "LP64 flattened row overflow")
+    x2 = x.reshape(rows, inner)
+    if x2.stride(-1) != 1 or (rows > 1 and x2.stride(0) < inner) or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    w2 = weight_interleaved
+    if w2.stride(1) != 1 or w2.stride(0) < inner or w2.stride(0) % 8:
+        w2 = w2.contiguous()
+    out = torch.empty((rows, intermediate), dtype=x.dtype, device=x.device)
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("gate_up_swiglu_bf16", rows, inner, intermediate, _pointer(x2),
+                        x2.stride(0) if rows > 1 else inner, _pointer(w2), w2.stride(0),
+                        _pointer(out), intermediate)
+    return out.reshape(tuple(x.shape[:-1]) + (intermediate,))
+
+
 def swiglu(gate, up, limit=0.0, routing=None):
     """Return ``rnd(silu(gate) * up [* routing[row]])`` with optional clipping."""
     _require(gate.is_cuda and gate.shape == up.shape and gate.dtype == up.dtype

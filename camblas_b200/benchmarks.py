@@ -140,6 +140,24 @@ def config2(results):
         2 * (10240 * hidden + tokens * hidden + tokens * 10240), "tensor_bf16")
     del weight
     linear_case(results, "C2 gate_up 512x8192 -> 57344", tokens, 57344, hidden)
+    # the same projection with SwiGLU in the epilogue, against GEMM + silu_multiply
+    weights = bf16_weight(57344, hidden, 0.02, 2)
+    mixed = [_kernels.interleave_gate_up(w) for w in weights]
+    flops = 2 * tokens * 57344 * hidden
+    fused_bytes = 2 * (57344 * hidden + tokens * hidden + tokens * 28672)
+    microseconds = graph_time_us(lambda i: _kernels.gate_up_swiglu(x, mixed[i % 2]), 2)
+    row(results, "C2 gate_up + SwiGLU in the epilogue -> 28672", microseconds, flops, fused_bytes,
+        "tensor_bf16")
+    del mixed
+
+    def two_step(i):
+        both = _kernels.linear(x, weights[i % 2]).view(tokens, 2, 28672)
+        return _kernels.silu_multiply(both[:, 0], both[:, 1])
+
+    microseconds = graph_time_us(two_step, 2)
+    row(results, "C2 gate_up GEMM, then silu_multiply (two kernels + copies)", microseconds, flops,
+        fused_bytes + 3 * tokens * 57344 * 2, "tensor_bf16", "comparator")
+    del weights
     linear_case(results, "C2 down 512x28672 -> 8192", tokens, 8192, 28672)
 
 

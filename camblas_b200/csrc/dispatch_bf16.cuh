@@ -98,12 +98,15 @@ inline int prepare_kernels()
     status |= prepare_pair_kernels<kMajorK, kMajorMN>();
     status |= prepare_pair_kernels<kMajorMN, kMajorK>();
     status |= prepare_pair_kernels<kMajorMN, kMajorMN>();
-    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, true>,
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, kEpiPush>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        PairSmem<256, 3, 2>::kTotal));
-    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<128, 4, kMajorK, kMajorK, 2, true>,
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<128, 4, kMajorK, kMajorK, 2, kEpiPush>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        PairSmem<128, 4, 2>::kTotal));
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwiglu>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       PairSmem<256, 3, 2>::kTotal));
     status |= prepare_row_kernels<kMajorK, kMajorMN>();
     status |= prepare_row_kernels<kMajorMN, kMajorK>();
     status |= prepare_row_kernels<kMajorMN, kMajorMN>();
@@ -279,7 +282,7 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     return launched(context, "stream-K fix-up");
 }
 
-template <int BN, int Stages, int PMajor, int QMajor, int Sub = 1, bool Push = false>
+template <int BN, int Stages, int PMajor, int QMajor, int Sub = 1, int Epi = sm100::kEpiStore>
 cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensorMap &p,
                         const CUtensorMap &q, const CUtensorMap &d0, const CUtensorMap &d1,
                         const CUtensorMap &d2, const sm100::GemmTask &task)
@@ -296,7 +299,7 @@ cudaError_t launch_pair(camblas_cuda_context *context, int pairs, const CUtensor
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, sm100::gemm_bf16_pair<BN, Stages, PMajor, QMajor, Sub, Push>,
+    return cudaLaunchKernelEx(&config, sm100::gemm_bf16_pair<BN, Stages, PMajor, QMajor, Sub, Epi>,
                               p, q, d0, d1, d2, task);
 }
 
@@ -458,6 +461,68 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
         sm100::sk_fixup_pair<128><<<grid, 256, 0, context->stream>>>(task, pairs, x.c1, x.ldc1,
                                                                      x.c2, x.ldc2);
     return launched(context, "stream-K fix-up");
+}
+
+/* out[rows, intermediate] = SiLU(x . Wg^T) * (x . Wu^T) in one pass over a weight
+ * whose gate and up rows are interleaved in blocks of 128 (rows [256j, 256j+128)
+ * gate features 128j.., rows [256j+128, 256j+256) the matching up features), so
+ * that every 256-column tile of the two-SM kernel holds both halves of 128
+ * outputs. Whole tiles apply SwiGLU in the epilogue; a stream-K tail does it in
+ * its second pass. */
+inline int run_gate_up_swiglu(camblas_cuda_context *context, int rows, int inner, int intermediate,
+                              const __nv_bfloat16 *x, long long ldx, const __nv_bfloat16 *w,
+                              long long ldw, __nv_bfloat16 *out, long long ldo)
+{
+    sm100::GemmTask task{};
+    const int packed = 2 * intermediate;
+    task.rows = rows, task.cols = packed, task.depth = inner;
+    task.r_blocks = (rows + 255) / 256;
+    task.c_blocks = packed / 256;
+    task.k_blocks = (inner + 63) / 64;
+    task.split = 1, task.k_blocks_per_split = task.k_blocks;
+    task.alpha = 1.f, task.beta = 0.f;
+    task.out = out, task.ld_out = ldo;
+    task.status = context->status;
+    task.cut0 = task.cut1 = packed;
+    task.batch = 1;
+    task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    const int pairs_max = context->sm_count / 2;
+    if (task.r_blocks <= 8 && pairs_max / task.r_blocks >= 2 && task.k_blocks >= 16) {
+        /* the policy of run_tensor_pair for 256-column tiles */
+        const int teams = pairs_max / task.r_blocks;
+        const int rest = task.c_blocks % teams;
+        const double tile = 2.0 * 256 * 256 * inner / (2 * 1.45e15 / 148.0 / 1e6);
+        const double second_pass = 6.0 + double(rest + teams) * task.r_blocks * 256 * 256 * 8 / 5.0e6;
+        if (rest != 0 && 2 * rest <= teams &&
+            (double(task.c_blocks) / teams) * tile + second_pass <
+                double((task.c_blocks + teams - 1) / teams) * tile) {
+            task.dp_cols = task.c_blocks - rest, task.sk_cols = rest;
+            int status = reserve_scratch(context, size_t(4) * pairs_max * 128 * 256 * sizeof(float));
+            if (status != 0)
+                return status;
+            task.sk_partial = static_cast<float *>(context->scratch);
+        }
+    }
+    const long long units = 1ll * task.r_blocks * task.c_blocks;
+    const int pairs = (units < pairs_max && task.sk_cols == 0) ? int(units) : pairs_max;
+    CUtensorMap p, q, d;
+    const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    bool ok = encode_2d(context, &p, bf16, 2, x, inner, rows, uint64_t(ldx) * 2, 64, 128) &&
+              encode_2d(context, &q, bf16, 2, w, inner, packed, uint64_t(ldw) * 2, 64, 128) &&
+              encode_2d(context, &d, bf16, 2, out, intermediate, rows, uint64_t(ldo) * 2, 64, 32);
+    if (!ok)
+        return fail(context, "tensor map encoding", 1);
+    using namespace sm100;
+    cudaError_t error =
+        launch_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwiglu>(context, pairs, p, q, d, d, d, task);
+    if (error != cudaSuccess)
+        return fail(context, "two-SM tcgen05 gate_up GEMM with SwiGLU", error);
+    context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    if (task.sk_cols == 0)
+        return 0;
+    dim3 grid(task.sk_cols, 16, task.r_blocks);
+    sm100::sk_fixup_pair_swiglu<<<grid, 256, 0, context->stream>>>(task, pairs);
+    return launched(context, "stream-K fix-up with SwiGLU");
 }
 
 inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)

@@ -117,6 +117,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t barrier_cluster_addres
 }
 
 constexpr int kPairRows = 256;
+/* What the epilogue of the two-SM kernel does with a finished tile. */
+constexpr int kEpiStore = 0;  /* alpha, bias, addend, one rounding, TMA store */
+constexpr int kEpiPush = 1;   /* BF16 partial tile to the GPU that owns it (row_parallel.cuh) */
+constexpr int kEpiSwiglu = 2; /* tile = 128 gate + 128 up columns: SiLU(gate) * up */
 
 
 template <int BN, int Stages, int Sub = 1> struct PairSmem {
@@ -132,7 +136,7 @@ template <int BN, int Stages, int Sub = 1> struct PairSmem {
  * (any multiple of 16 from 64 to 256; Q must then be K-major and the stage
  * layout and TMEM buffers are those of the 256-column tile). */
 template <int BNT, int Stages, int PMajor = kMajorK, int QMajor = kMajorK, int Sub = 1,
-          bool Push = false>
+          int Epi = kEpiStore>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_d0,
@@ -145,7 +149,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr uint32_t kTmemColumns = kLayoutWidth * 2;
     static_assert(BNT == 256 || BNT == 128 || BNT == 0, "pair tiles: 256, 128 or run-time width");
     static_assert(!kDynamic || QMajor == kMajorK, "run-time width needs a K-major Q operand");
-    static_assert(!Push || !kDynamic, "the push epilogue works on fixed-width tiles");
+    constexpr bool Push = Epi == kEpiPush;
+    static_assert(Epi == kEpiStore || !kDynamic, "the special epilogues work on fixed-width tiles");
+    static_assert(Epi != kEpiSwiglu || (BNT == 256 && QMajor == kMajorK),
+                  "the SwiGLU epilogue pairs 128 gate with 128 up columns of a K-major weight");
     const int BN = kDynamic ? task.width : BNT;
     const int kHalf = BN / 2;
     const uint32_t stage_bytes = Layout::kPBytes + kHalf * kBlockK * 2; /* bytes one CTA loads */
@@ -357,7 +364,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                     mbar_arrive_cluster(map_to_rank(smem_u32(&tmem_empty[buffer]), 0));
             };
-            if constexpr (Push) {
+            if constexpr (Epi == kEpiSwiglu) {
+                if (u.slot >= 0) {
+                    float *slot = task.sk_partial +
+                                  (static_cast<long long>(u.slot) * 2 + rank) * kBlockR * BNT;
+                    epilogue_partial<kLayoutWidth>(slot, taddr, quarter, lane, slab, slab_use, roomy,
+                                                   release);
+                } else {
+                    epilogue_swiglu(task, &map_d0, taddr, row0, u.cb * 128, lane, slab, slab_use,
+                                    roomy, release);
+                }
+            } else if constexpr (Push) {
                 /* partial sums of a K range split over GPUs: to the tile's owner */
                 const int unit = ((u.rb * task.c_blocks + u.cb) * 2 + static_cast<int>(rank)) * 4 +
                                  quarter;
@@ -460,6 +477,37 @@ __global__ void __launch_bounds__(256)
         for (int i = 0; i < 8 && col + i < limit; ++i)
             target[i] = __float2bfloat16_rn(v[i]);
     }
+}
+
+/* Second pass of the stream-K tail for SwiGLU tiles (256 packed columns = 128
+ * gate + 128 up): one thread per eight output columns adds the pieces of its
+ * gate columns and of the matching up columns in ascending K order and stores
+ * SiLU(gate) * up. grid = (stream-K column blocks, 16, 256-row blocks). */
+__global__ void __launch_bounds__(256) sk_fixup_pair_swiglu(const GemmTask task, int pairs)
+{
+    const int vector = blockIdx.y * 256 + threadIdx.x;
+    const int r = vector >> 4, c8 = (vector & 15) * 8; /* r in [0, 256), c8 in [0, 128) */
+    const int rb = blockIdx.z, cb = task.dp_cols + blockIdx.x;
+    const int row = rb * kPairRows + r, col = cb * 128 + c8; /* output column */
+    if (row >= task.rows || cb * 256 + c8 >= task.cols)
+        return;
+    float gate[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float up[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto slot_of = [&](int team, int piece) {
+        return (2ll * (team * task.r_blocks + rb) + piece) * 2 + (r >> 7);
+    };
+    sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, c8, slot_of, gate);
+    sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, 128 + c8, slot_of, up);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        v[i] = swiglu_value(task.alpha * gate[i], task.alpha * up[i]);
+    uint4 packed;
+    packed.x = pack_bf16(v[0], v[1]);
+    packed.y = pack_bf16(v[2], v[3]);
+    packed.z = pack_bf16(v[4], v[5]);
+    packed.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4 *>(task.out + static_cast<long long>(row) * task.ld_out + col) = packed;
 }
 
 } // namespace sm100

@@ -432,6 +432,68 @@ __device__ __forceinline__ void epilogue_rows(const GemmTask &task, const CUtens
     }
 }
 
+/* SiLU(gate) * up with the roundings of the two-step path it replaces (a BF16
+ * GEMM output followed by the reference's silu_multiply,
+ * inference_fusion.cuh:19-29): gate and up are first rounded to BF16 as the
+ * GEMM would have stored them, SiLU(gate) is rounded, the product is rounded. */
+__device__ __forceinline__ float swiglu_value(float gate_sum, float up_sum)
+{
+    const float g = __bfloat162float(__float2bfloat16_rn(gate_sum));
+    const float u = __bfloat162float(__float2bfloat16_rn(up_sum));
+    const float activated = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
+    return activated * u;
+}
+
+/* Epilogue of a 256-column tile whose first 128 columns are gate features and
+ * whose last 128 the matching up features (the weight was interleaved that
+ * way): writes the 128 columns SiLU(gate) * up of the tile to `map_out` at
+ * column out_col0. Two 64-column slabs, each needing the gate and the up
+ * accumulators of its columns; staging and TMA store as in epilogue_rows. */
+template <typename Release>
+__device__ __forceinline__ void epilogue_swiglu(const GemmTask &task, const CUtensorMap *map_out,
+                                                uint32_t taddr, int store_row, int out_col0, int lane,
+                                                uint8_t *slab, uint32_t &slab_use, bool roomy,
+                                                Release release)
+{
+    const float alpha = task.alpha;
+#pragma unroll 1
+    for (int chunk = 0; chunk < 2; ++chunk) {
+        uint32_t gate[2][32], up[2][32];
+        tmem_ld_32x32(taddr + chunk * 64, gate[0]);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, gate[1]);
+        tmem_ld_32x32(taddr + 128 + chunk * 64, up[0]);
+        tmem_ld_32x32(taddr + 128 + chunk * 64 + 32, up[1]);
+        tmem_ld_wait();
+        if (chunk == 1)
+            release();
+        uint8_t *buffer_smem = slab + (roomy ? chunk : (slab_use & 1)) * 4096;
+        if (!roomy) {
+            if (lane == 0)
+                tma_store_wait_read<1>();
+            __syncwarp();
+        }
+        const uint32_t base = smem_u32(buffer_smem) + lane * 128;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+            const uint32_t *g = &gate[piece >> 2][(piece & 3) * 8];
+            const uint32_t *u = &up[piece >> 2][(piece & 3) * 8];
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = swiglu_value(alpha * __uint_as_float(g[i]), alpha * __uint_as_float(u[i]));
+            st_shared_v4(base + ((piece ^ (lane & 7)) << 4), pack_bf16(v[0], v[1]),
+                         pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_out, buffer_smem, out_col0 + chunk * 64, store_row);
+            tma_store_commit();
+        }
+        ++slab_use;
+    }
+}
+
 /* Push variant of the row epilogue for a product whose K range is split over
  * GPUs: alpha*acc rounded to BF16 (bias and addend are applied once, by the GPU
  * that sums the partials) and sent to the owner's staging slot. The slot is

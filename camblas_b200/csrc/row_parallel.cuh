@@ -299,9 +299,9 @@ inline int run(camblas_cuda_context *context, const Call &call)
         using namespace sm100;
         /* the kernel only prefetches its output maps in this mode; any valid map will do */
         cudaError_t error =
-            bn == 256 ? launch_pair<256, 3, kMajorK, kMajorK, 2, true>(context, pairs, p, q, q, q, q,
+            bn == 256 ? launch_pair<256, 3, kMajorK, kMajorK, 2, kEpiPush>(context, pairs, p, q, q, q, q,
                                                                        task)
-                      : launch_pair<128, 4, kMajorK, kMajorK, 2, true>(context, pairs, p, q, q, q, q,
+                      : launch_pair<128, 4, kMajorK, kMajorK, 2, kEpiPush>(context, pairs, p, q, q, q, q,
                                                                        task);
         if (error != cudaSuccess)
             return fail(context, "two-SM tcgen05 BF16 GEMM with peer push", error);

@@ -133,6 +133,22 @@ int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int in
 int camblas_cuda_linear_bf16_static(void *stream, int rows, int inner, int outputs, const void *x,
                                     int ldx, const void *w, int ldw, void *out, int ldo);
 
+/* No counterpart in the reference ABI: there the MLP's first half is a GEMM that
+ * writes [rows, 2*intermediate] and camblas_cuda_silu_multiply
+ * (camblas_cuda.h:115-121; inference_fusion.cuh:19-29) that reads it back.
+ * This entry point does both in one pass: out[rows, intermediate] =
+ * rnd(rnd(SiLU(rnd(x . Wg^T))) * rnd(x . Wu^T)), the roundings of the two-step
+ * path, so the result equals silu_multiply applied to the BF16 GEMM outputs.
+ * `w` is [2*intermediate, inner] with gate and up rows interleaved in blocks of
+ * 128: rows [256j, 256j+128) are gate features [128j, 128j+128), rows
+ * [256j+128, 256j+256) the up features of the same indices (a one-time
+ * permutation of the packed [gate; up] weight). intermediate must be a
+ * multiple of 128; x, w, out 16-byte aligned, ldx, ldw, ldo multiples of 8.
+ * May grow the context's scratch on first use (not during stream capture). */
+int camblas_cuda_gate_up_swiglu_bf16(camblas_cuda_context *context, int rows, int inner,
+                                     int intermediate, const void *x, int ldx, const void *w,
+                                     int ldw, void *out, int ldo);
+
 /* ---- row-parallel linear layer over several GPUs ------------------------ */
 
 /* None of the following has a counterpart in the reference, which has no
