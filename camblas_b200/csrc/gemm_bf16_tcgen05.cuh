@@ -757,12 +757,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             /* The operand that is re-read by many tiles stays in L2; the one
              * that is read once per panel is streamed. With few row blocks the
              * column operand (weights) is the streamed one. */
-#ifdef CAMBLAS_EXPERIMENT_NOHINT
-            const uint64_t policy_p = keep, policy_q = keep;
-#else
             const uint64_t policy_p = task.r_blocks <= task.panel ? keep : stream;
             const uint64_t policy_q = task.r_blocks <= task.panel ? stream : keep;
-#endif
             uint32_t stage = 0, phase = 0;
             uint32_t armed = 0, armed_parity = 0;
             bool ok = true;
