@@ -7,9 +7,10 @@
  * shape M=256, N=BN, K=16 that reads both CTAs' shared memory, and each CTA
  * receives its 128 accumulator rows in its own tensor memory. Compared with the
  * one-SM kernel this halves the Q bytes every SM pulls from L2 and keeps in
- * shared memory per multiply (32 KB instead of 48 KB per 64-deep stage at
- * BN=256), which is what that kernel is short of, and lets the ring hold six
- * stages instead of four.
+ * shared memory per multiply (32 KB instead of 48 KB per 64-deep K block at
+ * BN=256), which is what that kernel is short of. The ring holds six K blocks
+ * (192 KB); with Sub=2 a stage is two of them, so that every barrier round
+ * trip, expect_tx and pair of commits covers eight MMAs instead of four.
  *
  * Roles per CTA (192 threads): warp 0 = TMA producer for this CTA's halves
  * (every CTA fetches its own bytes; no load is shared between CTAs), warp 1 =
