@@ -63,3 +63,12 @@ def test_column_and_row_parallel_layers_with_two_gloo_ranks():
     mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
     assert results["column"] and results["row"]
     assert results["bounds"] == ((0, 128), (0, 64))
+
+
+def test_peer_region_capacity_counts_whole_tiles():
+    """Staging holds whole 256 x 256 tiles: both extents round up to multiples of 256."""
+    from camblas_b200.tp import PeerRegions
+
+    assert PeerRegions.capacity_for(512, 8192) == 512 * 8192
+    assert PeerRegions.capacity_for(300, 1000) == 512 * 1024
+    assert PeerRegions.capacity_for(1, 8) == 256 * 256
