@@ -403,10 +403,18 @@ def run_ours(args):
     # result back; the copies run on their own streams with two buffer sets, so the
     # transfer of step i+1 overlaps the kernels of step i (a serving loop would do
     # the same). The timed region ends when the last result has reached the host.
+    # With N ranks every rank needs the whole activations, but only 1/N of them crosses
+    # its own host link: rank r uploads its block of token rows and the ranks exchange the
+    # blocks over NVLink (NCCL all-gather on the upload stream); likewise rank r downloads
+    # only its block of the (replicated) result. Whole-job bytes per step stay the same.
     host_x = block.x.cpu().pin_memory()
     host_residual = block.residual.cpu().pin_memory()
     host_out = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     device_in = [(torch.empty_like(block.x), torch.empty_like(block.residual)) for _ in range(2)]
+    # its own communicator, so that the all-gather does not queue behind the step's collectives
+    transfer_group = dist.new_group() if world > 1 else None
+    share = TOKENS // world if TOKENS % world == 0 else TOKENS
+    mine = slice(rank * share, (rank + 1) * share) if share != TOKENS else slice(0, TOKENS)
     compute = torch.cuda.current_stream()
     upload, download = torch.cuda.Stream(), torch.cuda.Stream()
     e2e_steps = min(steps, 200)
@@ -422,8 +430,10 @@ def run_ours(args):
             with torch.cuda.stream(upload):
                 if index >= 2:
                     upload.wait_event(consumed[slot])
-                device_in[slot][0].copy_(host_x, non_blocking=True)
-                device_in[slot][1].copy_(host_residual, non_blocking=True)
+                for target, source in zip(device_in[slot], (host_x, host_residual)):
+                    target[mine].copy_(source[mine], non_blocking=True)
+                    if share != TOKENS:
+                        dist.all_gather_into_tensor(target, target[mine], group=transfer_group)
                 loaded[slot].record(upload)
             compute.wait_event(loaded[slot])
             out = block.step(*device_in[slot])
@@ -434,7 +444,7 @@ def run_ours(args):
                 download.wait_event(consumed[slot])
                 if index >= 2:
                     download.wait_event(stored[slot])
-                host_out[slot].copy_(out, non_blocking=True)
+                host_out[slot][mine].copy_(out[mine], non_blocking=True)
                 out.record_stream(download)
                 stored[slot].record(download)
         compute.wait_stream(download)
