@@ -562,7 +562,7 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     if (task.split > 1) {
         /* the warp that writes a tile's last split adds them up: no second launch */
         const bool fused = 4ll * task.r_blocks * task.c_blocks <= camblas_cuda_context::kCounterWords &&
-                           std::getenv("CAMBLAS_B200_SPLIT_REDUCE") == nullptr;
+                           std::getenv("CAMBLAS_B200_SPLIT_REDUCE") != nullptr;
         if (fused)
             task.split_counters = context->status + camblas_cuda_context::kCounterOffset;
         if (bn == 16)

@@ -348,11 +348,11 @@ def test_split_k_summed_by_the_last_warp_equals_the_second_pass(rng, monkeypatch
     bias = bits_to_tensor(normal_bits(rng, (outputs,)))
     residual = bits_to_tensor(normal_bits(rng, (tokens, outputs)))
     with _native.kernel_family("tensor_swapped"):
-        monkeypatch.setenv("CAMBLAS_B200_SPLIT_REDUCE", "1")
+        monkeypatch.delenv("CAMBLAS_B200_SPLIT_REDUCE", raising=False)
         launches = _native.context(0).kernel_launches()
         two_pass = _kernels.linear(x, w, bias, residual)
         two_pass_launches = _native.context(0).kernel_launches() - launches
-        monkeypatch.delenv("CAMBLAS_B200_SPLIT_REDUCE")
+        monkeypatch.setenv("CAMBLAS_B200_SPLIT_REDUCE", "fused")
         launches = _native.context(0).kernel_launches()
         first = _kernels.linear(x, w, bias, residual)
         fused_launches = _native.context(0).kernel_launches() - launches
