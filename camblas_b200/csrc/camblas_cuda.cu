@@ -177,11 +177,7 @@ extern "C" int camblas_cuda_device_status(camblas_cuda_context *context, unsigne
             error = cudaMemsetAsync(context->status, 0, sizeof(unsigned), context->stream);
         if (error == cudaSuccess)
             error = cudaStreamSynchronize(context->stream);
-        if (error == cudaSuccess && *status != 0)
-            /* a kernel gave up half-way: its split-K arrival counters may be left non-zero */
-            error = cudaMemsetAsync(context->status + camblas_cuda_context::kCounterOffset, 0,
-                                    camblas_cuda_context::kCounterWords * sizeof(unsigned),
-                                    context->stream);
+
         return error == cudaSuccess ? 0 : fail(context, "device status read", error);
     });
 }

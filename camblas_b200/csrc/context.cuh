@@ -35,11 +35,7 @@ struct camblas_cuda_context {
     bool scratch_captured = false;
     std::vector<void *> retired;
     unsigned *status = nullptr; /* device words: [0] written by bounded waits that gave up,
-                                   [1] Strassen range-guard flag of the call in flight,
-                                   [kCounterOffset..] arrival counters of split-K tiles, zero
-                                   between launches (see GemmTask::split_counters) */
-    static constexpr int kCounterOffset = 64, kCounterWords = 8192;
-    static constexpr int kStatusWords = kCounterOffset + kCounterWords;
+                                   [1] Strassen range-guard flag of the call in flight */
     unsigned long long *guard_hits = nullptr;        /* pinned host counter of guard fall-backs */
     unsigned long long *guard_hits_device = nullptr; /* the same word as the device sees it */
     EncodeTiledFn encode = nullptr;

@@ -560,11 +560,6 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     if (!ok)
         return fail(context, "tensor map encoding", 1);
     if (task.split > 1) {
-        /* the warp that writes a tile's last split adds them up: no second launch */
-        const bool fused = 4ll * task.r_blocks * task.c_blocks <= camblas_cuda_context::kCounterWords &&
-                           std::getenv("CAMBLAS_B200_SPLIT_REDUCE") != nullptr;
-        if (fused)
-            task.split_counters = context->status + camblas_cuda_context::kCounterOffset;
         if (bn == 16)
             launch_tensor<16, 8, sm100::kStorePartial>(context, p, q, p, p, p, task);
         else if (bn == 32)
@@ -572,7 +567,7 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
         else
             launch_tensor<64, 8, sm100::kStorePartial>(context, p, q, p, p, p, task);
         int status = launched(context, "tcgen05 split-K BF16 GEMM");
-        if (status != 0 || fused)
+        if (status != 0)
             return status;
         dim3 grid((x.m + 255) / 256, x.n);
         sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(

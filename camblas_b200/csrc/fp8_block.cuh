@@ -90,7 +90,6 @@ struct BlockTask {
     __nv_bfloat16 *out;
     long long ld_out;
     float *partial; /* kStorePartial: [split][cols][r_blocks*128] */
-    unsigned *split_counters; /* kStorePartial: as GemmTask::split_counters, or NULL */
     unsigned *status;
 };
 
@@ -359,11 +358,6 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                 for (int i = 0; i < BN; ++i)
                     if (col0 + i < task.cols)
                         target[i * plane] = acc[i];
-                if (task.split_counters != nullptr)
-                    sm100::split_finish(task.split_counters + (rb * task.c_blocks + cb) * 4 + quarter,
-                                        task.split, task.partial, plane, task.cols, task.rows, row,
-                                        col0, BN, 1.f, 0.f, nullptr, nullptr, 0, task.out, task.ld_out,
-                                        lane);
             } else {
                 if (row < task.rows) {
 #pragma unroll
@@ -847,11 +841,6 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
     if (!ok)
         return host::fail(context, "tensor map encoding", 1);
     if (task.split > 1) {
-        /* the warp that writes a tile's last split adds them up: no second launch */
-        const bool fused = 4ll * task.r_blocks * task.c_blocks <= camblas_cuda_context::kCounterWords &&
-                           std::getenv("CAMBLAS_B200_SPLIT_REDUCE") != nullptr;
-        if (fused)
-            task.split_counters = context->status + camblas_cuda_context::kCounterOffset;
         if (bn == 16)
             launch_block<16, 8, kStorePartial>(context, p, qm, p, task);
         else if (bn == 32)
@@ -859,7 +848,7 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
         else
             launch_block<64, 8, kStorePartial>(context, p, qm, p, task);
         int status = host::launched(context, "tcgen05 FP8 split-K block GEMM");
-        if (status != 0 || fused)
+        if (status != 0)
             return status;
         dim3 grid((outputs + 255) / 256, rows);
         sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(

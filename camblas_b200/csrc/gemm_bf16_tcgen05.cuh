@@ -45,11 +45,6 @@ struct GemmTask {
     long long ld_add;
     const __nv_bfloat16 *bias; /* per column (kStoreRows) or per row (kStoreColumns) */
     float *partial;            /* kStorePartial: [split][cols][r_blocks*128] */
-    /* kStorePartial: when non-NULL, word (tile * 4 + warp quarter) counts the K
-     * splits whose partial sums for those 32 rows are written; the warp that
-     * writes the last one adds all splits in order and stores the result, so no
-     * second launch is needed. Zero between launches (the last warp clears it). */
-    unsigned *split_counters;
     unsigned *status;
     /* Optional second and third outputs for a packed projection: columns
      * [0,cut0) go to out, [cut0,cut1) to out1, [cut1,cols) to out2. cut0 and
@@ -696,45 +691,6 @@ epilogue_rows_dynamic(const GemmTask &task, const CUtensorMap *map0, const CUten
     }
 }
 
-/* Swapped modes with a K split: called by every epilogue warp after its 32 rows
- * (output features) x `width` columns (tokens col0..) of split `part` are in
- * scratch. The warp that finds all other splits already there adds them in
- * ascending split order (its own included, from memory, so the order never
- * depends on who is last), applies alpha, bias and beta*addend and stores BF16;
- * lanes read and write consecutive features, i.e. consecutive addresses.
- * Returns nothing to wait for: no warp ever waits for another. */
-__device__ __forceinline__ void split_finish(unsigned *counter, int split, const float *partial,
-                                             long long plane, int cols, int rows, int row,
-                                             int col0, int width, float alpha, float beta,
-                                             const __nv_bfloat16 *bias,
-                                             const __nv_bfloat16 *addend, long long ld_add,
-                                             __nv_bfloat16 *out, long long ld_out, int lane)
-{
-    __threadfence(); /* this lane's partial sums before the count */
-    __syncwarp();
-    unsigned ticket = 0;
-    if (lane == 0)
-        ticket = atomicAdd(counter, 1u);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != static_cast<unsigned>(split - 1))
-        return;
-    __threadfence(); /* the other splits' sums after the count */
-    if (lane == 0)
-        *counter = 0; /* ready for the next launch */
-    if (row >= rows)
-        return;
-    const float own_bias = bias != nullptr ? __bfloat162float(bias[row]) : 0.f;
-    for (int c = col0; c < min(col0 + width, cols); ++c) {
-        float sum = 0.f;
-        for (int s = 0; s < split; ++s)
-            sum += __ldcg(partial + (static_cast<long long>(s) * cols + c) * plane + row);
-        float v = alpha * sum + own_bias;
-        if (beta != 0.f)
-            v = fmaf(beta, __bfloat162float(addend[c * ld_add + row]), v);
-        out[c * ld_out + row] = __float2bfloat16_rn(v);
-    }
-}
-
 template <int BN, int Stages, int Mode, int PMajor = kMajorK, int QMajor = kMajorK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap map_p,
@@ -1000,11 +956,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                         for (int i = 0; i < kPiece; ++i)
                             if (cbase + i < task.cols)
                                 target[i * plane] = __uint_as_float(acc[i]);
-                        if (chunk == BN / kPiece - 1 && task.split_counters != nullptr)
-                            split_finish(task.split_counters + (rb * task.c_blocks + cb) * 4 + quarter,
-                                         task.split, task.partial, plane, task.cols, task.rows, row,
-                                         col0, BN, task.alpha, task.beta, task.bias, task.addend,
-                                         task.ld_add, task.out, task.ld_out, lane);
                     } else {
                         if (row < task.rows) {
                             float bias =

@@ -334,31 +334,3 @@ def test_two_sm_kernel_with_a_run_time_tile_width(rng, monkeypatch, width):
         q, k, v = _kernels.qkv_linear(bits_to_tensor(x), bits_to_tensor(w), *widths)
     packed = torch.cat([q, k, v], dim=1).float().cpu().numpy()
     assert oracle.rel_l2(packed, expected) <= BF16_TOLERANCE
-
-
-@pytest.mark.parametrize("tokens,outputs,inner", [(2, 4096, 2048), (16, 8192, 4096), (64, 1000, 3072),
-                                                  (33, 520, 8192)])
-def test_split_k_summed_by_the_last_warp_equals_the_second_pass(rng, monkeypatch, tokens, outputs,
-                                                                inner):
-    """Few tokens with a K split: the warp that writes a tile's last split adds the splits in
-    order itself. The bits must equal those of the separate reduction kernel (same order), on
-    repeated calls too (the arrival counters are cleared by the warp that used them)."""
-    x = bits_to_tensor(normal_bits(rng, (tokens, inner)))
-    w = bits_to_tensor(normal_bits(rng, (outputs, inner), 0.05))
-    bias = bits_to_tensor(normal_bits(rng, (outputs,)))
-    residual = bits_to_tensor(normal_bits(rng, (tokens, outputs)))
-    with _native.kernel_family("tensor_swapped"):
-        monkeypatch.delenv("CAMBLAS_B200_SPLIT_REDUCE", raising=False)
-        launches = _native.context(0).kernel_launches()
-        two_pass = _kernels.linear(x, w, bias, residual)
-        two_pass_launches = _native.context(0).kernel_launches() - launches
-        monkeypatch.setenv("CAMBLAS_B200_SPLIT_REDUCE", "fused")
-        launches = _native.context(0).kernel_launches()
-        first = _kernels.linear(x, w, bias, residual)
-        fused_launches = _native.context(0).kernel_launches() - launches
-        second = _kernels.linear(x, w, bias, residual)
-    assert _native.context(0).device_status() == 0
-    assert torch.equal(first, two_pass)
-    assert torch.equal(second, first)
-    if two_pass_launches == 2:  # the shape was split: the fused path saves the second launch
-        assert fused_launches == 1
