@@ -199,6 +199,8 @@ def run_reference(args):
     steps, warmup = max(1, args.steps), max(0, args.warmup)
     sample = CpuSample()
     per_step = min(20.0, 150.0 / (steps + warmup))
+    if "CAMBLAS_BENCH_STEP_SECONDS" in os.environ:  # tests shorten the sample
+        per_step = float(os.environ["CAMBLAS_BENCH_STEP_SECONDS"])
     rows = sample.rows_for(per_step)
     passes = 1
     if rows == TOKENS:  # the whole slab is quicker than the step budget: repeat it
