@@ -255,8 +255,14 @@ class RowParallelLinear:
         """Return the rank's columns of a replicated activation tensor."""
         return x[..., self.bounds[0]:self.bounds[1]].contiguous()
 
+    # Below this many token rows the product is a weight-streaming kernel (GEMV or
+    # swapped tcgen05) and the payload of the sum is at most 1 MB: the NCCL path is used.
+    # The peer-memory path multiplies with 256-row tiles, which is what prefill needs.
+    PEER_ROWS = 65
+
     def __call__(self, x_local):
-        if self.peers is not None:
+        rows = x_local.numel() // x_local.shape[-1]
+        if self.peers is not None and rows >= self.PEER_ROWS:
             # product and sum in one sequence of kernels over peer memory; the
             # bias enters once, on the rank that sums each tile
             return self.peers.linear(x_local.reshape(-1, x_local.shape[-1]), self.weight,

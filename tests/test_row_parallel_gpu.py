@@ -132,6 +132,38 @@ def test_narrow_tiles_give_the_same_sum(monkeypatch):
     assert np.array_equal(narrow[1], narrow[0])
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_benchmark_shape_against_partial_products(world):
+    """The down projection of the benchmark (512 x 28672 -> 8192) split over `world` ranks:
+    the exchanged result equals the sum of the ranks' BF16 partial products (each rounded
+    once, summed in FP32 in rank order, rounded once) bit for bit - the partial products
+    come from the same two-SM kernel without a stream-K split - and is within the BF16
+    tolerance of the unsharded product."""
+    from camblas_b200 import _kernels
+
+    torch.manual_seed(705537 + world)
+    rows, inner, outputs = 512, 28672, 8192
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(outputs, inner, device="cuda") * 0.02).bfloat16()
+    step = inner // world
+    xs = [x[:, r * step:(r + 1) * step].contiguous() for r in range(world)]
+    ws = [w[:, r * step:(r + 1) * step].contiguous() for r in range(world)]
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
+    try:
+        got = run_emulated(views, xs, ws)
+    finally:
+        close_all(views)
+    total = torch.zeros((rows, outputs), dtype=torch.float32, device="cuda")
+    for x_r, w_r in zip(xs, ws):
+        total += _kernels.linear(x_r, w_r).float()
+    expected = tensor_to_bits(total.bfloat16())
+    assert np.array_equal(got[0], expected)
+    for r in range(1, world):
+        assert np.array_equal(got[r], got[0])
+    full = _kernels.linear(x, w).float().cpu().numpy()
+    assert oracle.rel_l2(oracle.bf16_values(got[0]), full) <= BF16_TOLERANCE
+
+
 def test_rejects_what_it_cannot_do():
     views = PeerRegions.emulate(64 * 64, 2, 0)
     try:
