@@ -256,7 +256,19 @@ def single(kind, tokens, outputs, inner, launches=20):
     print(json.dumps(result), flush=True)
 
 
-CONFIGS = {1: config1, 2: config2, 3: config3, 4: config4, 5: config5}
+def config6(results):
+    """What one rank multiplies when the M=512 block is sharded over 2, 4 and 8 GPUs:
+    column-parallel QKV and gate_up (outputs / tp), row-parallel down (inner / tp)."""
+    tokens = 512
+    for tp in (2, 4, 8):
+        linear_case(results, f"C2/tp{tp} QKV shard 512x8192 -> {10240 // tp}", tokens, 10240 // tp, 8192)
+        linear_case(results, f"C2/tp{tp} gate_up shard 512x8192 -> {57344 // tp}", tokens,
+                    57344 // tp, 8192)
+        linear_case(results, f"C2/tp{tp} down shard 512x{28672 // tp} -> 8192", tokens, 8192,
+                    28672 // tp)
+
+
+CONFIGS = {1: config1, 2: config2, 3: config3, 4: config4, 5: config5, 6: config6}
 
 
 def main():
