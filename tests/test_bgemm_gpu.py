@@ -334,3 +334,29 @@ def test_two_sm_kernel_with_a_run_time_tile_width(rng, monkeypatch, width):
         q, k, v = _kernels.qkv_linear(bits_to_tensor(x), bits_to_tensor(w), *widths)
     packed = torch.cat([q, k, v], dim=1).float().cpu().numpy()
     assert oracle.rel_l2(packed, expected) <= BF16_TOLERANCE
+
+
+@pytest.mark.parametrize("widths", [(8192, 1024, 1024), (4096, 512, 512), (2048, 256, 256),
+                                    (1024, 128, 128)])
+def test_packed_projection_at_the_sharded_widths(widths):
+    """QKV of the M=512 block on 1, 2, 4 and 8 ranks (whole heads per rank): one launch
+    with three outputs must give what three separate linear layers give. The narrower
+    shards have few tiles and take the one-SM route; K is split differently there, so the
+    comparison is by tolerance, plus sampled FP64 dot products."""
+    torch.manual_seed(705537 + widths[0])
+    rows, inner = 512, 8192
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(sum(widths), inner, device="cuda") * 0.02).bfloat16()
+    q, k, v = _kernels.qkv_linear(x, w, *widths)
+    assert _native.context(0).device_status() == 0
+    assert q.shape == (rows, widths[0]) and k.shape == (rows, widths[1]) and v.shape == (rows, widths[2])
+    packed = torch.cat([q, k, v], dim=1).float()
+    separate = torch.cat([_kernels.linear(x, part) for part in torch.split(w, list(widths))],
+                         dim=1).float()
+    assert ((packed - separate).norm() / separate.norm()).item() <= 2e-3
+    generator = torch.Generator().manual_seed(11)
+    picks_r = torch.randint(0, rows, (64,), generator=generator)
+    picks_c = torch.randint(0, sum(widths), (64,), generator=generator)
+    expected = (x[picks_r].double().cpu() * w[picks_c].double().cpu()).sum(1)
+    got = packed[picks_r, picks_c].double().cpu()
+    assert ((got - expected).norm() / expected.norm()).item() <= BF16_TOLERANCE
