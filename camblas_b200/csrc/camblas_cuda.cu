@@ -14,10 +14,33 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 using host::fail;
 using host::guarded;
 using host::launched;
+
+namespace
+{
+/* The environment is consulted here, once per context, and nowhere else. */
+void options_from_environment(ContextOptions &options)
+{
+    if (const char *text = std::getenv("CAMBLAS_B200_PAIR_MODE")) {
+        if (std::strcmp(text, "plain") == 0)
+            options.pair_tail = 1;
+        else if (std::strcmp(text, "sk") == 0)
+            options.pair_tail = 2;
+        else if (std::strncmp(text, "width=", 6) == 0)
+            options.pair_width = std::atoi(text + 6);
+    }
+    if (const char *text = std::getenv("CAMBLAS_B200_PUSH_WIDTH"))
+        options.push_width = std::atoi(text);
+    if (const char *text = std::getenv("CAMBLAS_B200_FP8_ROWS"))
+        options.fp8_rows = std::strcmp(text, "four") == 0 ? 1 : (std::strcmp(text, "single") == 0 ? 2 : 0);
+    if (const char *text = std::getenv("CAMBLAS_B200_BF16_STRASSEN"))
+        options.bf16_strassen = std::atoi(text) != 0;
+}
+} // namespace
 
 extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_context **out)
 {
@@ -32,6 +55,7 @@ extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_contex
         return fail(nullptr, "context allocation", 2);
     context->device = device;
     context->stream = static_cast<cudaStream_t>(stream);
+    options_from_environment(context->options);
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
     int status = int(cudaStreamIsCapturing(context->stream, &capture));
     const char *what = "stream capture status";
@@ -135,6 +159,35 @@ extern "C" int camblas_cuda_force_kernel(camblas_cuda_context *context, int fami
     return 0;
 }
 
+extern "C" int camblas_cuda_set_option(camblas_cuda_context *context, const char *name, int value)
+{
+    if (!context || !name)
+        return fail(context, "missing context or option name", 1);
+    ContextOptions &options = context->options;
+    struct Known {
+        const char *name;
+        int *slot;
+        int low, high;
+    } const known[] = {
+        {"pair_tail", &options.pair_tail, 0, 2},
+        {"pair_width", &options.pair_width, 0, 256},
+        {"push_width", &options.push_width, 0, 256},
+        {"fp8_rows", &options.fp8_rows, 0, 2},
+        {"bf16_strassen", &options.bf16_strassen, 0, 1},
+        {"peer_wait_ms", &options.peer_wait_ms, 1, 60000},
+    };
+    for (const Known &entry : known)
+        if (std::strcmp(name, entry.name) == 0) {
+            if (value < entry.low || value > entry.high ||
+                (entry.slot == &options.pair_width && value % 16 != 0) ||
+                (entry.slot == &options.push_width && value != 0 && value != 128 && value != 256))
+                return fail(context, "option value out of range", 1);
+            *entry.slot = value;
+            return 0;
+        }
+    return fail(context, "unknown option", 1);
+}
+
 extern "C" int camblas_cuda_stats(const camblas_cuda_context *context, uint64_t *counts, int length)
 {
     if (!context || !counts || (length != 6 && length != 8))
@@ -216,7 +269,8 @@ extern "C" int camblas_cuda_bgemm(camblas_cuda_context *context, char trans_a, c
         x.c = out, x.ldc = ldc;
         x.addend = out, x.ld_add = ldc;
         x.cut0 = x.cut1 = m;
-        if (context->algorithm == CAMBLAS_CUDA_STRASSEN && strassen::eligible(context, x))
+        if (context->algorithm == CAMBLAS_CUDA_STRASSEN && context->options.bf16_strassen &&
+            strassen::eligible(context, x))
             return strassen::run(context, x);
         return host::run_product(context, x);
     });
@@ -596,15 +650,3 @@ extern "C" int camblas_cuda_reduce_groups(camblas_cuda_context *context, int, in
 {
     return host::unavailable(context, "camblas_cuda_reduce_groups");
 }
-
-#ifdef CAMBLAS_TRACE_PHASES
-/* Development aid, compiled only on request: copies the per-CTA phase timestamps
- * of the last two-SM GEMM launch (148 x 16 words) to host memory. */
-extern "C" int camblas_cuda_debug_phase_trace(unsigned long long *host)
-{
-    cudaError_t error = cudaDeviceSynchronize();
-    if (error == cudaSuccess)
-        error = cudaMemcpyFromSymbol(host, sm100::phase_trace, sizeof(sm100::phase_trace));
-    return error == cudaSuccess ? 0 : -int(error);
-}
-#endif

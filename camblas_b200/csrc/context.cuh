@@ -24,6 +24,33 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+/* Tuning and test switches of a context. They are read from the environment
+ * once, when the context is created (names in parentheses), and changed
+ * afterwards only through camblas_cuda_set_option; no entry point on the call
+ * path looks at the environment. */
+struct ContextOptions {
+    int pair_tail = 0;     /* "pair_tail" (CAMBLAS_B200_PAIR_MODE=plain|sk): 0 cost model, 1 whole
+                              tiles only, 2 always split the last wave by K */
+    int pair_width = 0;    /* "pair_width" (CAMBLAS_B200_PAIR_MODE=width=<n>): forced tile width of
+                              the two-SM kernel, 0 = fixed 256/128-column tiles */
+    int push_width = 0;    /* "push_width" (CAMBLAS_B200_PUSH_WIDTH): tile width of the peer-memory
+                              row-parallel product, 0 = by shape */
+    int fp8_rows = 0;      /* "fp8_rows" (CAMBLAS_B200_FP8_ROWS=four|single): 1, 2 select the older
+                              many-row FP8 kernels, which give the same bits */
+    int bf16_strassen = 0; /* "bf16_strassen" (CAMBLAS_B200_BF16_STRASSEN=1): let policy STRASSEN
+                              run one Strassen level on BF16 squares */
+    int peer_wait_ms = 5000; /* "peer_wait_ms": how long a kernel waits for another GPU's flag */
+};
+
+/* One cached tensor map: the arguments it was encoded from and the result. */
+struct TensorMapEntry {
+    const void *base = nullptr;
+    uint64_t extent0 = 0, extent1 = 0, pitch = 0;
+    uint32_t box0 = 0, box1 = 0;
+    int type = -1;
+    CUtensorMap map;
+};
+
 struct camblas_cuda_context {
     int device = 0;
     int algorithm = CAMBLAS_CUDA_AUTO;
@@ -39,6 +66,13 @@ struct camblas_cuda_context {
     unsigned long long *guard_hits = nullptr;        /* pinned host counter of guard fall-backs */
     unsigned long long *guard_hits_device = nullptr; /* the same word as the device sees it */
     EncodeTiledFn encode = nullptr;
+    ContextOptions options;
+    /* Direct-mapped cache of encoded tensor maps: a serving loop presents the
+     * same (pointer, shape) pairs call after call, and a hit costs a 128-byte
+     * copy instead of a driver call. */
+    static constexpr int kMapSlots = 128;
+    TensorMapEntry maps[kMapSlots];
+    uint64_t map_hits = 0, map_misses = 0;
     std::atomic<uint64_t> counts[8] = {};
     std::atomic<uint64_t> kernel_launches{0}; /* every kernel this context put on its stream */
     char error[256] = "";
@@ -163,15 +197,32 @@ inline bool encode_2d(camblas_cuda_context *context, CUtensorMap *map, CUtensorM
     /* A single row never uses the pitch; keep it legal (multiple of 16). */
     if (extent1 == 1)
         pitch_bytes = (extent0 * element_bytes + 15) & ~uint64_t(15);
+    uint64_t hash = reinterpret_cast<uintptr_t>(base) >> 4;
+    hash = (hash ^ (extent0 * 0x9e3779b97f4a7c15ull) ^ (extent1 * 0xc2b2ae3d27d4eb4full) ^
+            (pitch_bytes << 7) ^ (uint64_t(box0) << 20) ^ (uint64_t(box1) << 40) ^ uint64_t(type)) *
+           0xff51afd7ed558ccdull;
+    TensorMapEntry &entry = context->maps[(hash >> 40) % camblas_cuda_context::kMapSlots];
+    if (entry.base == base && entry.extent0 == extent0 && entry.extent1 == extent1 &&
+        entry.pitch == pitch_bytes && entry.box0 == box0 && entry.box1 == box1 &&
+        entry.type == int(type)) {
+        *map = entry.map;
+        ++context->map_hits;
+        return true;
+    }
     cuuint64_t strides[1] = {pitch_bytes};
     cuuint32_t box[2] = {box0, box1};
     cuuint32_t element_strides[2] = {1, 1};
-    (void)element_bytes;
     CUresult result = context->encode(map, type, 2, const_cast<void *>(base), dims, strides, box,
                                       element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return result == CUDA_SUCCESS;
+    if (result != CUDA_SUCCESS)
+        return false;
+    ++context->map_misses;
+    entry.base = base, entry.extent0 = extent0, entry.extent1 = extent1, entry.pitch = pitch_bytes;
+    entry.box0 = box0, entry.box1 = box1, entry.type = int(type);
+    entry.map = *map;
+    return true;
 }
 
 inline bool aligned16(const void *pointer)

@@ -354,13 +354,12 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
         const double cycles = std::max(2.0 * width, (16384.0 + 64.0 * width) / 65.0);
         return 2.0 * 256 * 256 * x.k / pair_flops_per_us * cycles / 512.0;
     };
-    const char *mode = std::getenv("CAMBLAS_B200_PAIR_MODE"); /* tuning aid: sk, width=<n>, plain */
+    /* tuning aids of the context: whole tiles only, always split the tail, forced width */
+    const bool tail_plain = context->options.pair_tail == 1, tail_split = context->options.pair_tail == 2;
     int bn = x.m <= 128 ? 128 : 256;
     double best = 1e30;
     int best_width = 0;
-    int forced_width = 0;
-    if (mode != nullptr && std::strncmp(mode, "width=", 6) == 0)
-        forced_width = std::atoi(mode + 6);
+    const int forced_width = context->options.pair_width;
     /* Measured on B200, tiles narrower than 256 columns are bound by operand
      * loads and never beat 256-column tiles with or without the stream-K tail on
      * the Llama shapes, so a run-time width is used only on request. */
@@ -387,14 +386,12 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
         const int teams = pairs_max / task.r_blocks;
         const int rest = columns % teams;
         /* a long tail (most teams busy anyway) gains less than the second pass costs */
-        if (rest != 0 && (2 * rest <= teams || (mode != nullptr && std::strcmp(mode, "sk") == 0))) {
+        if (rest != 0 && (2 * rest <= teams || tail_split)) {
             const double second_pass =
                 6.0 + double(rest + teams) * task.r_blocks * 256 * bn * 8 / 5.0e6;
             const double cost = (double(columns) / teams) * tile_us(bn) + second_pass;
             const double plain = double((columns + teams - 1) / teams) * tile_us(bn);
-            const bool forced = mode != nullptr && std::strcmp(mode, "sk") == 0;
-            if ((cost < plain && cost < best && forced_width == 0 &&
-                 !(mode != nullptr && std::strcmp(mode, "plain") == 0)) || forced) {
+            if ((cost < plain && cost < best && forced_width == 0 && !tail_plain) || tail_split) {
                 stream_k = true;
                 best_width = 0;
             }
@@ -698,7 +695,16 @@ inline int run_product(camblas_cuda_context *context, const Product &x)
         if (!possible)
             return fail(context, "forced kernel family cannot take these operands", 1);
     }
-    if (packed && family != kTensor && family != kTensorPair) {
+    /* One launch serves a packed projection only on the tensor-core row kernels and
+     * only when the three outputs start on tile boundaries (multiples of 128
+     * columns; of 16 with a forced run-time width); any other packed projection is
+     * three independent products, each dispatched on its own, which is what the
+     * reference computes (torch_bindings.cpp:725-736). */
+    const bool cuts_on_tiles =
+        (x.cut0 % 128 == 0 && x.cut1 % 128 == 0) ||
+        (family == kTensorPair && context->options.pair_width != 0 && x.ta && x.m > 128 &&
+         x.cut0 % 16 == 0 && x.cut1 % 16 == 0);
+    if (packed && ((family != kTensor && family != kTensorPair) || !cuts_on_tiles)) {
         Product part = x;
         part.cut0 = part.cut1 = 0;
         const int starts[4] = {0, x.cut0, x.cut1, x.m};

@@ -802,14 +802,14 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
                             size_t(ldo) * 2, 64, 32);
         if (!ok)
             return host::fail(context, "tensor map encoding", 1);
-        const char *variant = std::getenv("CAMBLAS_B200_FP8_ROWS"); /* tuning aid: four, single */
-        if (variant != nullptr && std::strcmp(variant, "four") == 0) {
+        const int variant = context->options.fp8_rows; /* tuning aid: 1 four warps, 2 one block per stage */
+        if (variant == 1) {
             launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
         } else {
             const int units = task.r_blocks * task.c_blocks;
             const int grid = units < context->sm_count ? units : context->sm_count;
             /* two K blocks per stage: 5 % faster than one (fewer barrier round trips) */
-            if (variant != nullptr && std::strcmp(variant, "single") == 0)
+            if (variant == 2)
                 fp8_block_rows<6><<<grid, kRowsThreads, RowsSmem<6>::kTotal, context->stream>>>(
                     p, qm, d, task);
             else

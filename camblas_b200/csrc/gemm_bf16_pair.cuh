@@ -181,7 +181,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        CAMBLAS_TRACE(0);
         for (int s = 0; s < Stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -205,8 +204,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     cluster_sync();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0)
-        CAMBLAS_TRACE(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -257,15 +254,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                                                  k0, policy_q);
                         }
                     }
-                    if (item == 0 && kb == u.kb0)
-                        CAMBLAS_TRACE(9);
                     if (++stage == Stages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
             }
-            CAMBLAS_TRACE(10);
             if (!ok) {
                 /* let copies already in flight land before the pair retires */
                 for (int wait = 0; wait < 64; ++wait)
@@ -294,8 +288,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tcgen05_fence_after();
-                    if (item == 0 && kb == u.kb0)
-                        CAMBLAS_TRACE(2);
                     const int blocks = min(Sub, u.kb1 - kb);
                     for (int sub = 0; sub < blocks; ++sub) {
                     const uint32_t p_address =
@@ -327,7 +319,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     umma_commit_pair(local_full);
                     umma_commit_pair(map_to_rank(local_full, 1));
                 }
-                CAMBLAS_TRACE(item == 0 ? 3 : 4);
             }
         }
     } else {
@@ -353,8 +344,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tcgen05_fence_after();
-            if (warp == 2 && lane == 0)
-                CAMBLAS_TRACE(item == 0 ? 5 : 11);
             const uint32_t taddr =
                 tmem_base + buffer * kLayoutWidth + (static_cast<uint32_t>(quarter * 32) << 16);
             const int row0 = u.rb * kPairRows + rank * kBlockR + quarter * 32;
@@ -401,13 +390,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                                             lane, slab, slab_use, roomy, release);
             }
         }
-        if (warp == 2 && lane == 0)
-            CAMBLAS_TRACE(6);
         if (lane == 0)
             tma_store_wait_all<0>();
         __syncwarp();
-        if (warp == 2 && lane == 0)
-            CAMBLAS_TRACE(7);
     }
 
     tcgen05_fence_before();
@@ -417,8 +402,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         tcgen05_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemColumns);
     }
-    if (threadIdx.x == 0)
-        CAMBLAS_TRACE(8);
 }
 
 /* Second pass of the stream-K tail of the pair kernel: like sk_fixup, with

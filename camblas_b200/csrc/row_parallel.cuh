@@ -112,6 +112,7 @@ struct ReduceTask {
     __nv_bfloat16 *result[kMaxWorld]; /* every GPU's result buffer */
     unsigned *delivered[kMaxWorld];   /* every GPU's delivery counter */
     unsigned *status;
+    unsigned long long wait_ns; /* how long a wait on another GPU's flag may last */
 };
 
 __device__ __forceinline__ void accumulate8(float (&sum)[8], const uint4 &packed)
@@ -126,9 +127,9 @@ __device__ __forceinline__ void accumulate8(float (&sum)[8], const uint4 &packed
 
 /* Waits until `expected` slabs have been delivered to this GPU, then clears the counter. */
 __device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned expected,
-                                               unsigned *status)
+                                               unsigned *status, unsigned long long wait_ns)
 {
-    if (sm100::flag_wait_system(delivered, expected))
+    if (sm100::flag_wait_system(delivered, expected, wait_ns))
         sm100::flag_store_relaxed_system(delivered, 0u);
     else
         atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(256)
     const int unit = (rb * task.c_blocks + cb) * 8 + slab;
     if (threadIdx.x == 0) {
         unsigned *word = task.arrive + unit;
-        const bool ok = sm100::flag_wait_system(word, unsigned(task.world));
+        const bool ok = sm100::flag_wait_system(word, unsigned(task.world), task.wait_ns);
         if (ok)
             sm100::flag_store_relaxed_system(word, 0u);
         else
@@ -223,16 +224,28 @@ __global__ void __launch_bounds__(256)
         const unsigned done = atomicAdd(ticket, 1u);
         if (done == gridDim.x * gridDim.y - 1) {
             *ticket = 0;
-            wait_delivered(task.delivered[task.rank], expected, task.status);
+            wait_delivered(task.delivered[task.rank], expected, task.status, task.wait_ns);
         }
     }
+    /* This kernel is launched as a programmatic dependent of the product kernel
+     * and may otherwise finish before it: on the success path every push of the
+     * product has landed by now (the arrivals say so), but after an expired wait
+     * the product could still be writing into other GPUs' staging while the
+     * stream moves on to camblas_cuda_peer_reset or the next call. Waiting for the
+     * preceding grid here makes "this launch is complete" imply "the product is
+     * complete" in every case; it is free when the product has already ended and
+     * does nothing when the launch had no programmatic dependency. The product
+     * kernel waits on nothing that this kernel provides, so no cycle can form. */
+    if (threadIdx.x == 0)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 /* One thread: wait until `expected` slabs have been delivered to this GPU. */
-__global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsigned *status)
+__global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsigned *status,
+                                    unsigned long long wait_ns)
 {
     if (threadIdx.x == 0)
-        wait_delivered(delivered, expected, status);
+        wait_delivered(delivered, expected, status, wait_ns);
 }
 
 struct Call {
@@ -253,9 +266,8 @@ inline int run(camblas_cuda_context *context, const Call &call)
         regions[r] = carve(call.memory[r], call.world, call.capacity);
     const Region &own = regions[call.rank];
 
-    const char *width_text = std::getenv("CAMBLAS_B200_PUSH_WIDTH"); /* tuning aid: 128 or 256 */
     int bn = call.outputs <= 128 ? 128 : 256;
-    if (width_text != nullptr && std::atoi(width_text) == 128)
+    if (context->options.push_width == 128)
         bn = 128;
     const int r_blocks = (call.rows + 255) / 256;
     const int c_blocks = (call.outputs + bn - 1) / bn;
@@ -325,6 +337,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
                 task.delivered[r] = regions[r].flags;
             }
             task.status = context->status;
+            task.wait_ns = 1000000ull * unsigned(context->options.peer_wait_ms);
             /* Launched as a programmatic dependent of the product kernel: its CTAs
              * may become resident while that kernel still runs (it says so at its
              * start) and wait on the arrival words, not on the kernel boundary. */
@@ -346,8 +359,9 @@ inline int run(camblas_cuda_context *context, const Call &call)
         }
     }
     if ((call.phases & 4) && !wait_inline) {
-        peer_wait_delivered<<<1, 32, 0, context->stream>>>(own.flags, unsigned(units),
-                                                           context->status);
+        peer_wait_delivered<<<1, 32, 0, context->stream>>>(
+            own.flags, unsigned(units), context->status,
+            1000000ull * unsigned(context->options.peer_wait_ms));
         return launched(context, "peer delivery wait");
     }
     return 0;

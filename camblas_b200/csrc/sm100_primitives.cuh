@@ -19,7 +19,9 @@ namespace sm100
  * limit of two seconds. A healthy pipeline needs microseconds. */
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-/* Waits on another GPU allow for the skew between processes: five seconds. */
+/* Waits on another GPU allow for the skew between processes: five seconds unless
+ * the context's "peer_wait_ms" option says otherwise (the limit travels as a
+ * kernel argument). */
 constexpr unsigned long long kPeerWaitLimitNs = 5000000000ull;
 
 __device__ __forceinline__ unsigned long long global_timer_ns()
@@ -28,15 +30,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
     return now;
 }
-
-#ifdef CAMBLAS_TRACE_PHASES
-/* Development aid, compiled only on request: per-CTA timestamps (ns) of the
- * phases of the last two-SM GEMM launch. */
-__device__ unsigned long long phase_trace[148 * 16];
-#define CAMBLAS_TRACE(slot) (phase_trace[blockIdx.x * 16 + (slot)] = global_timer_ns())
-#else
-#define CAMBLAS_TRACE(slot) ((void)0)
-#endif
 
 /* Status codes written to the context status word when a bounded wait gives up. */
 enum StatusRole : unsigned {
@@ -67,8 +60,9 @@ __device__ __forceinline__ void flag_store_relaxed_system(unsigned *word, unsign
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
 }
 
-/* Poll a flag word until it reaches `target`; gives up after kPeerWaitLimitNs. */
-__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target);
+/* Poll a flag word until it reaches `target`; gives up after `limit_ns`. */
+__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target,
+                                                 unsigned long long limit_ns = kPeerWaitLimitNs);
 
 __device__ __forceinline__ uint32_t smem_u32(const void *pointer)
 {
@@ -137,9 +131,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
-__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target)
+__device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target,
+                                                 unsigned long long limit_ns)
 {
     unsigned long long started = 0;
+    /* the poll count alone bounds the loop even if the timer misbehaves */
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (flag_load_acquire_system(word) >= target)
             return true;
@@ -147,7 +143,7 @@ __device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned 
             const unsigned long long now = global_timer_ns();
             if (started == 0)
                 started = now;
-            else if (now - started > kPeerWaitLimitNs)
+            else if (now - started > limit_ns)
                 return false;
         }
     }

@@ -18,7 +18,9 @@
  * stand-in for the device symbol, not a device address. The first call on each
  * device, with that device current, asks the runtime for the real address with
  * cudaGetSymbolAddress and caches it per device; later calls reuse it. That
- * first call should therefore be made before any stream capture begins.
+ * first call should therefore be made before any stream capture begins. The
+ * look-up is guarded by a once-flag per device, so host threads may make their
+ * first calls concurrently; each of them sees a complete entry.
  *
  * Sharing. All calls on a device share the one array and it keeps whatever
  * the previous call left. Nothing in it has to start at zero: every partial
@@ -31,6 +33,8 @@
 #include "context.cuh"
 #include "gemv_skinny.cuh"
 
+#include <mutex>
+
 namespace static_scratch
 {
 
@@ -40,30 +44,35 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) float partial_sums[kScratchBytes / sizeof(float)];
 
 struct DeviceSetup {
+    std::once_flag once;
     float *scratch = nullptr; /* device address of partial_sums on this device */
     int sm_count = 0;
-    bool ready = false;
+    int lookup = 0; /* cudaError_t of the look-up, 0 when it succeeded */
 };
 static DeviceSetup device_setup[kMaxDevices];
 
-/* Look up the device address of the array once per device (current device). */
+/* Look up the device address of the array once per device (current device).
+ * std::call_once orders the writes of the first caller before every other
+ * caller's reads, so no thread can see a half-filled entry. A failed look-up
+ * is remembered and reported by every later call on that device. */
 inline int setup(int device, DeviceSetup **out)
 {
     if (device < 0 || device >= kMaxDevices)
         return host::fail(nullptr, "static scratch device index", 1);
     DeviceSetup &entry = device_setup[device];
-    if (!entry.ready) {
+    std::call_once(entry.once, [&entry, device] {
         float *address = nullptr;
         cudaError_t error =
             cudaGetSymbolAddress(reinterpret_cast<void **>(&address), partial_sums);
-        if (error != cudaSuccess || address == nullptr)
-            return host::fail(nullptr, "static scratch address lookup", int(error ? error : 1));
-        error = cudaDeviceGetAttribute(&entry.sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (error != cudaSuccess)
-            return host::fail(nullptr, "device attribute query", int(error));
+        if (error == cudaSuccess && address == nullptr)
+            error = cudaErrorInvalidSymbol;
+        if (error == cudaSuccess)
+            error = cudaDeviceGetAttribute(&entry.sm_count, cudaDevAttrMultiProcessorCount, device);
         entry.scratch = address;
-        entry.ready = true;
-    }
+        entry.lookup = int(error);
+    });
+    if (entry.lookup != 0 || entry.scratch == nullptr || entry.sm_count < 1)
+        return host::fail(nullptr, "static scratch address lookup", entry.lookup ? entry.lookup : 1);
     *out = &entry;
     return 0;
 }

@@ -40,9 +40,16 @@ typedef struct camblas_cuda_context camblas_cuda_context;
 
 /* Multiplication policies; values match reference include/camblas_cuda.h:14-23.
  * AUTO, CLASSICAL and LT all select the tcgen05 GEMM (LT has no separate
- * library route here). STRASSEN applies one Strassen level to eligible BF16
- * squares; the multi-level and SYMMETRIC values are accepted and treated as
- * CLASSICAL for BF16, as the reference does (camblas_cuda.h:64-66). */
+ * library route here). For BF16 the reference runs the classical library GEMM
+ * under every policy, the Strassen ones included (camblas_cuda.h:64-66;
+ * bfloat16.cuh has no Strassen branch), and so does this library by default:
+ * STRASSEN, the multi-level values and SYMMETRIC are accepted and computed
+ * classically. A one-level BF16 Strassen exists as a deliberate extension
+ * behind the context option "bf16_strassen" (camblas_cuda_set_option): with it
+ * set, STRASSEN on 'N','N' squares whose order is a multiple of 512 multiplies
+ * seven half-size products of BF16-rounded operand sums, which costs accuracy
+ * (measured rel-L2 against FP64 2-5 times the classical kernel's on uniform
+ * [-1,1] inputs) and gives different bits than the classical kernel. */
 enum camblas_cuda_algorithm {
     CAMBLAS_CUDA_AUTO = 0,
     CAMBLAS_CUDA_CLASSICAL = 1,
@@ -128,7 +135,10 @@ int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int in
  * each device looks up the array's device address; make that call before any
  * stream capture. All calls on a device share the array: it needs no clearing
  * (every partial is written before it is read), but two calls that overlap on
- * the GPU race on it - keep them ordered. Failure text is read with
+ * the GPU race on it - keep them ordered. Host threads may call it
+ * concurrently (the per-device look-up runs once, under a once-flag; the
+ * failure text is per thread), but each thread is responsible for ordering its
+ * GPU work against the others' as above. Failure text is read with
  * camblas_cuda_error(NULL). */
 int camblas_cuda_linear_bf16_static(void *stream, int rows, int inner, int outputs, const void *x,
                                     int ldx, const void *w, int ldw, void *out, int ldo);
@@ -200,7 +210,8 @@ int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memory, int wor
  * production; the parts exist so that a single
  * process can drive several ranks on one GPU in turn (all of 1, then all of 2,
  * then all of 4), where no kernel may wait for one that has not been launched.
- * Waits inside the kernels give up after five seconds and record a device
+ * Waits inside the kernels give up after five seconds (option "peer_wait_ms"
+ * of camblas_cuda_set_option) and record a device
  * status (camblas_cuda_device_status), after which camblas_cuda_peer_reset is
  * needed. The result may be overwritten by the next call: consume it with work
  * enqueued on the same stream before that call. rows * outputs, each rounded up
@@ -304,6 +315,25 @@ int camblas_cuda_device_status(camblas_cuda_context *context, unsigned *status);
  * enqueued since it was created (every launch, including reduction and fix-up
  * passes; graph replays are not counted). */
 int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *count);
+/* No counterpart in the reference ABI. Sets one tuning or test switch of the
+ * context by name; returns -1 for an unknown name or a value out of range.
+ * Every switch starts from the environment variable in parentheses, which is
+ * read once when the context is created; no call on the hot path reads the
+ * environment.
+ *   "pair_tail"      0 cost model, 1 whole tiles only, 2 always split the last
+ *                    wave of the two-SM BF16 kernel by K
+ *                    (CAMBLAS_B200_PAIR_MODE=plain|sk)
+ *   "pair_width"     forced tile width of the two-SM kernel, a multiple of 16 up
+ *                    to 256, 0 = off (CAMBLAS_B200_PAIR_MODE=width=<n>)
+ *   "push_width"     0, 128 or 256: tile width of the peer-memory row-parallel
+ *                    product (CAMBLAS_B200_PUSH_WIDTH)
+ *   "fp8_rows"       0 current, 1 four-warp, 2 one-block-per-stage FP8 row
+ *                    kernel; same bits (CAMBLAS_B200_FP8_ROWS=four|single)
+ *   "bf16_strassen"  1 lets policy STRASSEN run one Strassen level on BF16
+ *                    squares (CAMBLAS_B200_BF16_STRASSEN)
+ *   "peer_wait_ms"   1..60000, how long a kernel of the row-parallel layer waits
+ *                    for another GPU's flag before it gives up (default 5000) */
+int camblas_cuda_set_option(camblas_cuda_context *context, const char *name, int value);
 /* No counterpart in the reference ABI. Chooses the BF16 kernel family for the
  * next calls on this context: 0 automatic, 1 generic CUDA-core kernel,
  * 2 skinny weight-streaming kernel, 3 tcgen05 kernel, 4 tcgen05 with swapped

@@ -315,11 +315,15 @@ def test_tensor_family_takes_every_transpose_pair(rng, ta, tb, m, n, k):
 
 
 @pytest.mark.parametrize("width", [128, 144, 208, 240])
-def test_two_sm_kernel_with_a_run_time_tile_width(rng, monkeypatch, width):
-    """CAMBLAS_B200_PAIR_MODE=width=<n> makes the two-SM kernel use tiles of n
+def test_two_sm_kernel_with_a_run_time_tile_width(rng, width):
+    """The context option pair_width=<n> makes the two-SM kernel use tiles of n
     columns (any multiple of 16): ragged last tiles, slabs beyond the matrix and a
     packed projection whose outputs meet inside a tile all have to come out right."""
-    monkeypatch.setenv("CAMBLAS_B200_PAIR_MODE", f"width={width}")
+    with _native.options(pair_width=width):
+        _run_time_width_cases(rng, width)
+
+
+def _run_time_width_cases(rng, width):
     for m, n, k in [(264, 130, 136), (1000, 300, 520), (592, 512, 2048)]:
         w, x, c = normal_bits(rng, (m, k)), normal_bits(rng, (n, k)), normal_bits(rng, (n, m))
         expected = c.copy()
@@ -334,6 +338,27 @@ def test_two_sm_kernel_with_a_run_time_tile_width(rng, monkeypatch, width):
         q, k, v = _kernels.qkv_linear(bits_to_tensor(x), bits_to_tensor(w), *widths)
     packed = torch.cat([q, k, v], dim=1).float().cpu().numpy()
     assert oracle.rel_l2(packed, expected) <= BF16_TOLERANCE
+
+
+@pytest.mark.parametrize("rows", [65, 200, 600])
+@pytest.mark.parametrize("widths", [(400, 112, 112), (320, 64, 64), (256, 128, 72)])
+def test_packed_projection_of_any_widths_in_automatic_mode(rng, rows, widths):
+    """The reference's qkv_linear is three independent linears and takes any widths
+    (torch_bindings.cpp:725-736). With more than 64 token rows the automatic choice
+    is a tensor-core row kernel, which serves a packed projection in one launch only
+    when the outputs start on 128-column boundaries; other widths must be split into
+    three products, not refused. Compared bit for bit with three linear() calls."""
+    inner = 512
+    x = bits_to_tensor(normal_bits(rng, (rows, inner)))
+    w = bits_to_tensor(normal_bits(rng, (sum(widths), inner), 0.05))
+    q, k, v = _kernels.qkv_linear(x, w, *widths)
+    assert _native.context(0).device_status() == 0
+    parts = [_kernels.linear(x, part.contiguous()) for part in torch.split(w, list(widths))]
+    for got, expected in zip((q, k, v), parts):
+        assert got.shape == expected.shape and torch.equal(got, expected)
+    reference = oracle.bf16_values(oracle.linear_bf16(tensor_to_bits(x[:8]), tensor_to_bits(w)))
+    packed = torch.cat([q, k, v], dim=1)[:8].float().cpu().numpy()
+    assert oracle.rel_l2(packed, reference) <= BF16_TOLERANCE
 
 
 @pytest.mark.parametrize("widths", [(8192, 1024, 1024), (4096, 512, 512), (2048, 256, 256),

@@ -116,7 +116,7 @@ def test_exact_integers_are_bit_exact():
         assert np.array_equal(got[r], expected)
 
 
-def test_narrow_tiles_give_the_same_sum(monkeypatch):
+def test_narrow_tiles_give_the_same_sum():
     """The 128-column tile variant (tuning aid) is the same arithmetic."""
     world, rows, inner, outputs = 2, 512, 320, 1536
     rng = np.random.default_rng(99)
@@ -124,8 +124,8 @@ def test_narrow_tiles_give_the_same_sum(monkeypatch):
     views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
     try:
         wide = run_emulated(views, xs, ws)
-        monkeypatch.setenv("CAMBLAS_B200_PUSH_WIDTH", "128")
-        narrow = run_emulated(views, xs, ws)
+        with _native.options(push_width=128):
+            narrow = run_emulated(views, xs, ws)
     finally:
         close_all(views)
     assert np.array_equal(wide[0], narrow[0])
@@ -180,3 +180,38 @@ def test_rejects_what_it_cannot_do():
         close_all(views)
     with pytest.raises(ValueError):
         PeerRegions.emulate(16, 9, 0)
+
+
+def test_expired_wait_reports_and_reset_recovers():
+    """A rank whose peer never sends: the bounded wait runs out, the kernel returns, the
+    status word names the wait, and after camblas_cuda_peer_reset the regions work again.
+
+    Rank 0 of two emulated ranks issues its product (one arrival per slab at the owner,
+    which is rank 0 itself) and then its reduction, which needs two arrivals per slab and
+    never gets the second because rank 1 launches nothing. The wait limit is lowered to
+    50 ms through the context option so that the test is quick; nothing traps or faults,
+    the kernel simply gives up. The stale arrival words (one instead of zero) would let
+    the next call start on incomplete data, which is what the reset is for.
+    """
+    world, rows, inner, outputs = 2, 256, 128, 256
+    rng = np.random.default_rng(20261127)
+    x, w, xs, ws = make_case(rng, world, rows, inner, outputs)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(rows, outputs), world, 0)
+    native = _native.context(0)
+    try:
+        good = run_emulated(views, xs, ws)
+        with _native.options(peer_wait_ms=50):
+            views[0].linear(xs[0], ws[0], phases=1)
+            views[0].linear(xs[0], ws[0], phases=6)
+            torch.cuda.synchronize()  # returns: the waits were bounded
+            status = _native.context(0).device_status()
+        assert status & 15 in (6, 7), hex(status)  # kRolePeerArrive / kRolePeerDelivered
+        assert native.device_status() == 0  # reading cleared it
+        for view in views:
+            view.reset()
+        torch.cuda.synchronize()
+        again = run_emulated(views, xs, ws)
+    finally:
+        close_all(views)
+    for r in range(world):
+        assert np.array_equal(again[r], good[r])

@@ -25,10 +25,11 @@ from tests.helpers import BF16_TOLERANCE, bits_to_tensor, normal_bits, pointer
 pytestmark = pytest.mark.gpu
 
 
-def static_linear(x, w):
+def static_linear(x, w, out=None):
     rows, inner = x.shape
     outputs = w.shape[0]
-    out = torch.empty((rows, outputs), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((rows, outputs), dtype=torch.bfloat16, device=x.device)
     stream = ct.c_void_p(torch.cuda.current_stream().cuda_stream)
     library = _native.library()
     status = library.camblas_cuda_linear_bf16_static(stream, rows, inner, outputs, pointer(x), inner,
@@ -55,6 +56,37 @@ def test_static_scratch_linear_matches_context_linear_twice():
             x[:1].cpu().view(torch.int16).numpy().view(np.uint16),
             w[:64].cpu().view(torch.int16).numpy().view(np.uint16)))
         assert oracle.rel_l2(actual[:1, :64].float().cpu().numpy(), reference) <= BF16_TOLERANCE
+
+
+def test_static_scratch_linear_leaves_device_memory_alone():
+    """Free device memory, as the driver reports it, is the same before and after.
+
+    The buffers are made first and the entry point is called once beforehand,
+    so the per-device look-up and the loading of the kernels are not counted.
+    `cudaMemGetInfo` sees every allocation on the device whichever allocator
+    made it; torch's own counters show that the caching allocator did not
+    serve one either. Another process on the same GPU could move the driver's
+    figure, so a mismatch is retried before it counts.
+    """
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(20261126)
+    x = bits_to_tensor(normal_bits(rng, (4, 16384)))
+    w = bits_to_tensor(normal_bits(rng, (1536, 16384), 0.02))
+    out = torch.empty((4, 1536), dtype=torch.bfloat16, device="cuda")
+    static_linear(x, w, out)
+    torch.cuda.synchronize()
+    for attempt in range(3):
+        free_before, _ = torch.cuda.mem_get_info()
+        torch_before = torch.cuda.memory_stats().get("allocation.all.allocated", 0)
+        for _ in range(8):
+            static_linear(x, w, out)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        torch_after = torch.cuda.memory_stats().get("allocation.all.allocated", 0)
+        assert torch_after == torch_before
+        if free_after == free_before:
+            break
+    assert free_after == free_before, (free_before, free_after)
 
 
 def test_static_scratch_linear_rejects_what_it_cannot_hold():
