@@ -22,6 +22,8 @@ using host::launched;
 
 namespace
 {
+int prepare_rms_kernels(); /* defined with the RMS wrappers below */
+
 /* The environment is consulted here, once per context, and nowhere else. */
 void options_from_environment(ContextOptions &options)
 {
@@ -103,7 +105,7 @@ extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_contex
     }
     if (status == 0) {
         what = "kernel attributes";
-        status = host::prepare_kernels() | fp8::prepare_kernels();
+        status = host::prepare_kernels() | fp8::prepare_kernels() | prepare_rms_kernels();
     }
     if (status != 0) {
         cudaGetLastError();
@@ -360,32 +362,113 @@ extern "C" int camblas_cuda_gate_up_swiglu_bf16(camblas_cuda_context *context, i
 
 namespace
 {
+constexpr int kStagedLimitBytes = 160 * 1024; /* widest row rows_staged keeps in shared memory */
+
+int prepare_rms_kernels()
+{
+    return int(cudaFuncSetAttribute(rms::rows_staged<float, true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kStagedLimitBytes)) |
+           int(cudaFuncSetAttribute(rms::rows_staged<__nv_bfloat16, true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kStagedLimitBytes));
+}
+
+template <typename T, typename W, bool Add, int Sweeps>
+void launch_in_registers(camblas_cuda_context *context, int rows, int width, float epsilon,
+                         const T *in, const T *res, const W *gamma, T *sum, T *out,
+                         bool round_before_weight, bool descending)
+{
+    rms::rows_in_registers<T, W, Add, Sweeps><<<rows, rms::kRowThreads, 0, context->stream>>>(
+        width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+}
+
+/* Single-row order for `rows` rows, one CTA each. Rows of up to 16384 columns
+ * with vector-aligned pointers stay in registers between the two passes. */
 template <typename T, typename W, bool Add>
 int launch_rms_rows(camblas_cuda_context *context, int rows, int width, float epsilon,
                     const void *input, const void *residual, const void *weight, void *added,
-                    void *output, bool round_before_weight, bool descending)
+                    void *output, bool round_before_weight, bool descending, bool in_place = false)
 {
     constexpr uintptr_t mask = sizeof(T) * 4 - 1, weight_mask = sizeof(W) * 4 - 1;
-    bool vector = width % 4 == 0 && !(uintptr_t(input) & mask) && !(uintptr_t(output) & mask) &&
-                  !(uintptr_t(weight) & weight_mask) &&
-                  (!Add || (!(uintptr_t(residual) & mask) && !(uintptr_t(added) & mask)));
+    const bool vector = width % 4 == 0 && !(uintptr_t(input) & mask) &&
+                        !(uintptr_t(output) & mask) && !(uintptr_t(weight) & weight_mask) &&
+                        (!Add || (!(uintptr_t(residual) & mask) && !(uintptr_t(added) & mask)));
     auto *in = static_cast<const T *>(input);
     auto *res = static_cast<const T *>(residual);
     auto *gamma = static_cast<const W *>(weight);
     auto *sum = static_cast<T *>(added);
     auto *out = static_cast<T *>(output);
-    if (vector)
-        rms::rms_row_kernel<T, W, Add, true><<<rows, rms::kRowThreads, 0, context->stream>>>(
+    /* the register kernel declares its pointers restrict: not for in-place calls */
+    const int sweeps = in_place ? 9 : (width + rms::kRowSpan - 1) / rms::kRowSpan;
+    if (vector && sweeps <= 1)
+        launch_in_registers<T, W, Add, 1>(context, rows, width, epsilon, in, res, gamma, sum, out,
+                                          round_before_weight, descending);
+    else if (vector && sweeps <= 2)
+        launch_in_registers<T, W, Add, 2>(context, rows, width, epsilon, in, res, gamma, sum, out,
+                                          round_before_weight, descending);
+    else if (vector && sweeps <= 4)
+        launch_in_registers<T, W, Add, 4>(context, rows, width, epsilon, in, res, gamma, sum, out,
+                                          round_before_weight, descending);
+    else if (vector && sweeps <= 8)
+        launch_in_registers<T, W, Add, 8>(context, rows, width, epsilon, in, res, gamma, sum, out,
+                                          round_before_weight, descending);
+    else if (vector)
+        rms::rows_two_sweeps<T, W, Add, true><<<rows, rms::kRowThreads, 0, context->stream>>>(
             width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
     else
-        rms::rms_row_kernel<T, W, Add, false><<<rows, rms::kRowThreads, 0, context->stream>>>(
+        rms::rows_two_sweeps<T, W, Add, false><<<rows, rms::kRowThreads, 0, context->stream>>>(
             width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
     return launched(context, Add ? "residual RMS normalisation" : "RMS normalisation");
+}
+
+/* Multi-row order for rows of any width. */
+template <typename T>
+int launch_rms_any(camblas_cuda_context *context, int rows, int width, float epsilon,
+                   const void *input, const void *weight, void *output)
+{
+    constexpr int lanes = rms::Storage<T>::kLanes;
+    const size_t row_bytes = size_t(width) * sizeof(T);
+    const bool staged = width % lanes == 0 && host::aligned16(input) && host::aligned16(weight) &&
+                        host::aligned16(output) && row_bytes <= size_t(kStagedLimitBytes);
+    const int grid = std::min(rows, context->sm_count * 8);
+    auto *in = static_cast<const T *>(input);
+    auto *gamma = static_cast<const T *>(weight);
+    auto *out = static_cast<T *>(output);
+    if (staged)
+        rms::rows_staged<T, true><<<grid, rms::kStagedThreads, row_bytes, context->stream>>>(
+            rows, width, epsilon, in, gamma, out);
+    else
+        rms::rows_staged<T, false><<<grid, rms::kStagedThreads, 0, context->stream>>>(
+            rows, width, epsilon, in, gamma, out);
+    return launched(context, "RMS normalisation");
 }
 
 bool decode_width(int width)
 {
     return width >= 2048 && width <= 65536 && width % 4 == 0;
+}
+
+/* Launch geometry of the elementwise kernels: how many leading 16-byte vectors
+ * the kernel may take (none unless every pointer is 16-byte aligned and, for
+ * row-structured operands, rows are whole vectors) and a grid that gives every
+ * SM a few CTAs without exceeding the work. */
+struct Elementwise {
+    size_t vectors;
+    unsigned blocks;
+};
+
+Elementwise elementwise_plan(const camblas_cuda_context *context, uint64_t count, int lanes,
+                             bool aligned, int width = 0)
+{
+    Elementwise plan{};
+    if (aligned && (width == 0 || width % lanes == 0))
+        plan.vectors = size_t(count / uint64_t(lanes));
+    const uint64_t items = std::max<uint64_t>(plan.vectors, count - plan.vectors * lanes);
+    plan.blocks = unsigned(std::min<uint64_t>((items + 255) / 256, uint64_t(context->sm_count) * 16));
+    if (plan.blocks == 0)
+        plan.blocks = 1;
+    return plan;
 }
 } // namespace
 
@@ -401,24 +484,21 @@ extern "C" int camblas_cuda_rms_norm(camblas_cuda_context *context, int dtype, i
             return 0;
         if (!input || !weight || !output || output == weight)
             return fail(context, "invalid RMS normalisation operands", 1);
+        /* a single long row takes the single-row order, as in the reference
+         * (inference_fusion.cuh:194-207); the output may be the input there */
         if (rows == 1 && decode_width(width)) {
+            const bool in_place = output == input;
             if (dtype == 0)
                 return launch_rms_rows<float, float, false>(context, 1, width, epsilon, input,
                                                             nullptr, weight, nullptr, output, true,
-                                                            false);
+                                                            false, in_place);
             return launch_rms_rows<__nv_bfloat16, __nv_bfloat16, false>(
-                context, 1, width, epsilon, input, nullptr, weight, nullptr, output, true, false);
+                context, 1, width, epsilon, input, nullptr, weight, nullptr, output, true, false,
+                in_place);
         }
-        int grid = std::min(rows, 65535);
         if (dtype == 0)
-            rms::rms_rows_kernel<float><<<grid, 256, 0, context->stream>>>(
-                rows, width, epsilon, static_cast<const float *>(input),
-                static_cast<const float *>(weight), static_cast<float *>(output));
-        else
-            rms::rms_rows_kernel<__nv_bfloat16><<<grid, 256, 0, context->stream>>>(
-                rows, width, epsilon, static_cast<const __nv_bfloat16 *>(input),
-                static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(output));
-        return launched(context, "RMS normalisation");
+            return launch_rms_any<float>(context, rows, width, epsilon, input, weight, output);
+        return launch_rms_any<__nv_bfloat16>(context, rows, width, epsilon, input, weight, output);
     });
 }
 
@@ -428,14 +508,17 @@ extern "C" int camblas_cuda_rms_norm_decode(camblas_cuda_context *context, int d
                                             const void *input, const void *weight, void *output)
 {
     return guarded(context, [&] {
-        if ((dtype != 0 && dtype != 2) || (weight_dtype != 0 && weight_dtype != 2) ||
-            (dtype == 0 && weight_dtype != 0) || !decode_width(width) ||
-            (round_before_weight != 0 && round_before_weight != 1) ||
-            (descending != 0 && descending != 1) || !std::isfinite(epsilon) || epsilon < 0 ||
-            !input || !weight || !output || output == input || output == weight ||
-            (uintptr_t(input) % (dtype == 0 ? 4 : 2)) ||
-            (uintptr_t(weight) % (weight_dtype == 0 ? 4 : 2)) ||
-            (uintptr_t(output) % (dtype == 0 ? 4 : 2)))
+        const bool types_ok = (dtype == 0 || dtype == 2) && (weight_dtype == 0 || weight_dtype == 2) &&
+                              !(dtype == 0 && weight_dtype != 0);
+        const bool flags_ok = (round_before_weight == 0 || round_before_weight == 1) &&
+                              (descending == 0 || descending == 1);
+        const bool values_ok = decode_width(width) && std::isfinite(epsilon) && epsilon >= 0;
+        const uintptr_t element = dtype == 0 ? 4 : 2, weight_element = weight_dtype == 0 ? 4 : 2;
+        const bool operands_ok = input && weight && output && output != input && output != weight &&
+                                 uintptr_t(input) % element == 0 &&
+                                 uintptr_t(output) % element == 0 &&
+                                 uintptr_t(weight) % weight_element == 0;
+        if (!types_ok || !flags_ok || !values_ok || !operands_ok)
             return fail(context, "invalid decode RMS arguments", 1);
         if (dtype == 0)
             return launch_rms_rows<float, float, false>(context, 1, width, epsilon, input, nullptr,
@@ -463,12 +546,18 @@ int add_rms(camblas_cuda_context *context, int dtype, int rows, int width, float
         context, rows, width, epsilon, input, residual, weight, added, output, true, false);
 }
 
+/* the five buffers of the residual form must all be present and pairwise distinct
+ * where one is written (reference backend.cu:1404-1408) */
 bool add_rms_operands_bad(const void *input, const void *residual, const void *weight, void *added,
                           void *output)
 {
-    return !input || !residual || !weight || !added || !output || added == output ||
-           added == input || added == residual || added == weight || output == input ||
-           output == residual || output == weight;
+    const void *read[3] = {input, residual, weight};
+    if (!added || !output || added == output)
+        return true;
+    for (const void *pointer : read)
+        if (!pointer || pointer == added || pointer == output)
+            return true;
+    return false;
 }
 } // namespace
 
@@ -510,9 +599,10 @@ extern "C" int camblas_cuda_bfloat16_square(camblas_cuda_context *context, uint6
             return 0;
         if (!input || !output || count > SIZE_MAX / sizeof(float))
             return fail(context, "invalid BF16 square operands", 1);
-        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
-        rms::square_kernel<<<blocks, 256, 0, context->stream>>>(
-            count, static_cast<const __nv_bfloat16 *>(input), output);
+        const Elementwise plan = elementwise_plan(
+            context, count, 8, host::aligned16(input) && host::aligned16(output));
+        rms::square_kernel<<<plan.blocks, 256, 0, context->stream>>>(
+            size_t(count), plan.vectors, static_cast<const __nv_bfloat16 *>(input), output);
         return launched(context, "BF16 squares");
     });
 }
@@ -529,14 +619,18 @@ extern "C" int camblas_cuda_rms_scale(camblas_cuda_context *context, int dtype, 
         if (!width || count % width || count > SIZE_MAX / sizeof(float) || !input || !weight ||
             !means || !output || output == weight)
             return fail(context, "invalid RMS scale operands", 1);
-        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        const bool aligned =
+            host::aligned16(input) && host::aligned16(weight) && host::aligned16(output);
+        const Elementwise plan =
+            elementwise_plan(context, count, dtype == 0 ? 4 : 8, aligned, width);
         if (dtype == 0)
-            rms::scale_kernel<float><<<blocks, 256, 0, context->stream>>>(
-                count, width, epsilon, static_cast<const float *>(input),
+            rms::scale_kernel<float><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, width, epsilon, static_cast<const float *>(input),
                 static_cast<const float *>(weight), means, static_cast<float *>(output));
         else
-            rms::scale_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
-                count, width, epsilon, static_cast<const __nv_bfloat16 *>(input),
+            rms::scale_kernel<__nv_bfloat16><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, width, epsilon,
+                static_cast<const __nv_bfloat16 *>(input),
                 static_cast<const __nv_bfloat16 *>(weight), means,
                 static_cast<__nv_bfloat16 *>(output));
         return launched(context, "RMS scaling");
@@ -553,14 +647,15 @@ extern "C" int camblas_cuda_silu_multiply(camblas_cuda_context *context, int dty
             return 0;
         if (!gate || !up || !output)
             return fail(context, "missing SiLU multiply operand", 1);
-        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        const bool aligned = host::aligned16(gate) && host::aligned16(up) && host::aligned16(output);
+        const Elementwise plan = elementwise_plan(context, count, dtype == 0 ? 4 : 8, aligned);
         if (dtype == 0)
-            rms::silu_multiply_kernel<float><<<blocks, 256, 0, context->stream>>>(
-                count, static_cast<const float *>(gate), static_cast<const float *>(up),
-                static_cast<float *>(output));
+            rms::silu_multiply_kernel<float><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, static_cast<const float *>(gate),
+                static_cast<const float *>(up), static_cast<float *>(output));
         else
-            rms::silu_multiply_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
-                count, static_cast<const __nv_bfloat16 *>(gate),
+            rms::silu_multiply_kernel<__nv_bfloat16><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, static_cast<const __nv_bfloat16 *>(gate),
                 static_cast<const __nv_bfloat16 *>(up), static_cast<__nv_bfloat16 *>(output));
         return launched(context, "SiLU multiply");
     });
@@ -578,14 +673,16 @@ extern "C" int camblas_cuda_swiglu(camblas_cuda_context *context, int dtype, uin
             return 0;
         if (!gate || !up || !output || static_cast<const void *>(routing) == output)
             return fail(context, "invalid SwiGLU operands", 1);
-        unsigned blocks = unsigned(std::min<uint64_t>((count + 255) / 256, 65535));
+        const bool aligned = host::aligned16(gate) && host::aligned16(up) && host::aligned16(output);
+        const Elementwise plan =
+            elementwise_plan(context, count, dtype == 0 ? 4 : 8, aligned, routing ? width : 0);
         if (dtype == 0)
-            rms::swiglu_kernel<float><<<blocks, 256, 0, context->stream>>>(
-                count, width, limit, static_cast<const float *>(gate),
+            rms::swiglu_kernel<float><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, width, limit, static_cast<const float *>(gate),
                 static_cast<const float *>(up), routing, static_cast<float *>(output));
         else
-            rms::swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, context->stream>>>(
-                count, width, limit, static_cast<const __nv_bfloat16 *>(gate),
+            rms::swiglu_kernel<__nv_bfloat16><<<plan.blocks, 256, 0, context->stream>>>(
+                size_t(count), plan.vectors, width, limit, static_cast<const __nv_bfloat16 *>(gate),
                 static_cast<const __nv_bfloat16 *>(up), routing,
                 static_cast<__nv_bfloat16 *>(output));
         return launched(context, "SwiGLU");

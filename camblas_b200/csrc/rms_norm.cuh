@@ -1,15 +1,24 @@
 /*
- * Residual add + RMS normalisation and the small elementwise kernels beside
- * it. These are bound by HBM traffic: every row is read once (twice from L2 for
- * the second pass) and every result written once.
+ * Residual add + RMS normalisation and the elementwise kernels beside it. All
+ * of them are bound by HBM traffic, so they are built around three rules: every
+ * byte is read from global memory once, accesses are 8- or 16-byte vectors that
+ * a warp issues as whole 128-byte lines, and a thread has all the loads of its
+ * row in flight before it uses the first of them.
  *
- * Arithmetic order. The reference normalises a row with 512 threads, four
- * running sums per thread over columns 4t+o+2048i, a shared-memory halving tree
- * down to one warp and a shuffle tree whose direction is selectable
- * (inference_fusion.cuh:136-191). rms_row_kernel below performs exactly that
- * sequence of FP32 roundings - products and sums are rounded separately, never
- * fused - for one row per CTA, so a batch of rows gives, row by row, the bits
- * the reference's single-row kernel gives. Loads are 8- or 16-byte vectors.
+ * Arithmetic order. Results are meant to agree with the reference bit for bit
+ * wherever the device functions involved (rsqrtf, expf) agree, so the order of
+ * the FP32 roundings is the reference's and products and sums are rounded
+ * separately (__fmul_rn/__fadd_rn, never contracted):
+ *   - single-row normalisation (inference_fusion.cuh:136-191): 512 threads, four
+ *     running sums per thread over columns 4t+o+2048i, a shared-memory halving
+ *     tree down to one warp, a shuffle tree whose direction is selectable;
+ *   - multi-row normalisation (inference_fusion.cuh:53-86): 256 threads, thread
+ *     t adds columns t+256i in sequence, a descending shuffle tree per warp, then
+ *     the eight warp sums through the same tree.
+ * How the data reaches the threads is this library's own: rows_in_registers
+ * keeps a row's values in registers between the sum and the scaling pass,
+ * rows_staged brings a row into shared memory with 16-byte loads and lets the
+ * threads pick their strided columns from there.
  */
 #pragma once
 
@@ -20,8 +29,11 @@
 namespace rms
 {
 
+/* Storage type <-> FP32, scalar and as the widest vector a thread moves:
+ * kLanes elements in 16 bytes. */
 template <typename T> struct Storage;
 template <> struct Storage<float> {
+    static constexpr int kLanes = 4;
     static __device__ __forceinline__ float load(const float *p, long long i) { return p[i]; }
     static __device__ __forceinline__ float round(float v) { return v; }
     static __device__ __forceinline__ void store(float *p, long long i, float v) { p[i] = v; }
@@ -34,8 +46,17 @@ template <> struct Storage<float> {
     {
         *reinterpret_cast<float4 *>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
     }
+    static __device__ __forceinline__ void load16(const float *p, long long i, float (&v)[4])
+    {
+        load4(p, i, v);
+    }
+    static __device__ __forceinline__ void store16(float *p, long long i, const float (&v)[4])
+    {
+        store4(p, i, v);
+    }
 };
 template <> struct Storage<__nv_bfloat16> {
+    static constexpr int kLanes = 8;
     static __device__ __forceinline__ float load(const __nv_bfloat16 *p, long long i)
     {
         return __bfloat162float(p[i]);
@@ -48,71 +69,49 @@ template <> struct Storage<__nv_bfloat16> {
     {
         p[i] = __float2bfloat16_rn(v);
     }
+    static __device__ __forceinline__ float low(uint32_t word) { return __uint_as_float(word << 16); }
+    static __device__ __forceinline__ float high(uint32_t word)
+    {
+        return __uint_as_float(word & 0xffff0000u);
+    }
+    static __device__ __forceinline__ uint32_t pack(float a, float b)
+    {
+        __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&pair);
+    }
     static __device__ __forceinline__ void load4(const __nv_bfloat16 *p, long long i, float (&v)[4])
     {
         uint2 q = *reinterpret_cast<const uint2 *>(p + i);
-        v[0] = __uint_as_float(q.x << 16), v[1] = __uint_as_float(q.x & 0xffff0000u);
-        v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xffff0000u);
+        v[0] = low(q.x), v[1] = high(q.x), v[2] = low(q.y), v[3] = high(q.y);
     }
     static __device__ __forceinline__ void store4(__nv_bfloat16 *p, long long i,
                                                   const float (&v)[4])
     {
-        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-        uint2 q;
-        q.x = *reinterpret_cast<uint32_t *>(&a), q.y = *reinterpret_cast<uint32_t *>(&b);
-        *reinterpret_cast<uint2 *>(p + i) = q;
+        *reinterpret_cast<uint2 *>(p + i) = make_uint2(pack(v[0], v[1]), pack(v[2], v[3]));
+    }
+    static __device__ __forceinline__ void load16(const __nv_bfloat16 *p, long long i,
+                                                  float (&v)[8])
+    {
+        uint4 q = *reinterpret_cast<const uint4 *>(p + i);
+        v[0] = low(q.x), v[1] = high(q.x), v[2] = low(q.y), v[3] = high(q.y);
+        v[4] = low(q.z), v[5] = high(q.z), v[6] = low(q.w), v[7] = high(q.w);
+    }
+    static __device__ __forceinline__ void store16(__nv_bfloat16 *p, long long i,
+                                                   const float (&v)[8])
+    {
+        *reinterpret_cast<uint4 *>(p + i) = make_uint4(pack(v[0], v[1]), pack(v[2], v[3]),
+                                                       pack(v[4], v[5]), pack(v[6], v[7]));
     }
 };
 
 constexpr int kRowThreads = 512;
+constexpr int kRowSpan = kRowThreads * 4; /* columns one sweep of the 512 threads covers */
 
-/* One row per CTA. Vector: every pointer is aligned for four-element vector
- * access and width % 4 == 0 (always true for the row width, checked by the
- * caller for the pointers); otherwise the scalar accessors are used. */
-template <typename T, typename W, bool Add, bool Vector>
-__global__ void __launch_bounds__(kRowThreads)
-    rms_row_kernel(int width, float epsilon, const T *input, const T *residual, const W *weight,
-                   T *added, T *output, bool round_before_weight, bool descending)
+/* Sum of the 512 per-thread values in the single-row order: halving tree in
+ * shared memory down to 32, then a shuffle tree (descending: offsets 16..1,
+ * ascending: 1..16). Returns the total in thread 0 only. */
+__device__ __forceinline__ float row_tree_sum(float sum, float *tree, int t, bool descending)
 {
-    __shared__ float tree[kRowThreads];
-    __shared__ float scale_slot;
-    const long long base = static_cast<long long>(blockIdx.x) * width;
-    input += base;
-    output += base;
-    if (Add) {
-        residual += base;
-        added += base;
-    }
-    const int t = threadIdx.x;
-    float sums[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int column = t * 4; column < width; column += kRowThreads * 4) {
-        float v[4];
-        if (Vector) {
-            Storage<T>::load4(input, column, v);
-            if (Add) {
-                float r[4];
-                Storage<T>::load4(residual, column, r);
-#pragma unroll
-                for (int o = 0; o < 4; ++o)
-                    v[o] = Storage<T>::round(__fadd_rn(v[o], r[o]));
-                Storage<T>::store4(added, column, v);
-            }
-        } else {
-#pragma unroll
-            for (int o = 0; o < 4; ++o) {
-                v[o] = Storage<T>::load(input, column + o);
-                if (Add) {
-                    v[o] = Storage<T>::round(
-                        __fadd_rn(v[o], Storage<T>::load(residual, column + o)));
-                    Storage<T>::store(added, column + o, v[o]);
-                }
-            }
-        }
-#pragma unroll
-        for (int o = 0; o < 4; ++o)
-            sums[o] = __fadd_rn(sums[o], __fmul_rn(v[o], v[o]));
-    }
-    float sum = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[1]), sums[2]), sums[3]);
     tree[t] = sum;
     for (int offset = kRowThreads / 2; offset >= 32; offset >>= 1) {
         __syncthreads();
@@ -130,34 +129,148 @@ __global__ void __launch_bounds__(kRowThreads)
             for (int offset = 1; offset < 32; offset <<= 1)
                 sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, offset));
         }
-        if (t == 0)
-            scale_slot = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.f / static_cast<float>(width)), epsilon));
     }
+    return sum;
+}
+
+/* One row per CTA, the row held in registers: Sweeps * 4 values per thread
+ * (width <= Sweeps * 2048, width % 4 == 0, all pointers aligned for four-element
+ * vectors). Every load of the row - input, residual and weight - is issued
+ * before the first value is used; the sums run over the values in the order
+ * 4t+o+2048i; the scaling pass works on the registers, so input and residual
+ * are read exactly once and nothing depends on this CTA's own stores. */
+template <typename T, typename W, bool Add, int Sweeps>
+__global__ void __launch_bounds__(kRowThreads)
+    rows_in_registers(int width, float epsilon, const T *__restrict__ input,
+                      const T *__restrict__ residual, const W *__restrict__ weight,
+                      T *__restrict__ added, T *__restrict__ output, bool round_before_weight,
+                      bool descending)
+{
+    __shared__ float tree[kRowThreads];
+    __shared__ float scale_slot;
+    const long long base = static_cast<long long>(blockIdx.x) * width;
+    const int t = threadIdx.x;
+    float v[Sweeps][4], r[Sweeps][4], g[Sweeps][4];
+#pragma unroll
+    for (int i = 0; i < Sweeps; ++i) {
+        const int column = i * kRowSpan + t * 4;
+        if (column < width) {
+            Storage<T>::load4(input + base, column, v[i]);
+            if (Add)
+                Storage<T>::load4(residual + base, column, r[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < Sweeps; ++i) {
+        const int column = i * kRowSpan + t * 4;
+        if (column < width)
+            Storage<W>::load4(weight, column, g[i]);
+    }
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < Sweeps; ++i) {
+        const int column = i * kRowSpan + t * 4;
+        if (column < width) {
+            if (Add) {
+#pragma unroll
+                for (int o = 0; o < 4; ++o)
+                    v[i][o] = Storage<T>::round(__fadd_rn(v[i][o], r[i][o]));
+                Storage<T>::store4(added + base, column, v[i]);
+            }
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+                sums[o] = __fadd_rn(sums[o], __fmul_rn(v[i][o], v[i][o]));
+        }
+    }
+    float sum = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[1]), sums[2]), sums[3]);
+    sum = row_tree_sum(sum, tree, t, descending);
+    if (t == 0)
+        scale_slot = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.f / static_cast<float>(width)), epsilon));
     __syncthreads();
     const float scale = scale_slot;
-    /* Second pass: the sum x+r is recomputed rather than re-read so that the
-     * pass does not depend on the visibility of this CTA's own stores. */
-    for (int column = t * 4; column < width; column += kRowThreads * 4) {
-        float v[4], g[4];
+#pragma unroll
+    for (int i = 0; i < Sweeps; ++i) {
+        const int column = i * kRowSpan + t * 4;
+        if (column < width) {
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                float normalised = __fmul_rn(v[i][o], scale);
+                if (round_before_weight)
+                    normalised = Storage<T>::round(normalised);
+                v[i][o] = __fmul_rn(normalised, g[i][o]);
+            }
+            Storage<T>::store4(output + base, column, v[i]);
+        }
+    }
+}
+
+/* The same arithmetic for rows that do not fit the register kernel (wider than
+ * 16384 columns), whose pointers are not aligned for vector access, or whose
+ * output is the input (in place): two sweeps over global memory, the second one
+ * re-forming x+r instead of reading back this CTA's own stores, and every
+ * element read before it is overwritten. Vector selects four-element vector
+ * access. */
+template <typename T, typename W, bool Add, bool Vector>
+__global__ void __launch_bounds__(kRowThreads)
+    rows_two_sweeps(int width, float epsilon, const T *input, const T *residual, const W *weight,
+                    T *added, T *output, bool round_before_weight, bool descending)
+{
+    __shared__ float tree[kRowThreads];
+    __shared__ float scale_slot;
+    const long long base = static_cast<long long>(blockIdx.x) * width;
+    const int t = threadIdx.x;
+    auto fetch = [&](int column, float (&v)[4]) {
         if (Vector) {
-            Storage<T>::load4(input, column, v);
+            Storage<T>::load4(input + base, column, v);
             if (Add) {
                 float r[4];
-                Storage<T>::load4(residual, column, r);
+                Storage<T>::load4(residual + base, column, r);
 #pragma unroll
                 for (int o = 0; o < 4; ++o)
                     v[o] = Storage<T>::round(__fadd_rn(v[o], r[o]));
             }
-            Storage<W>::load4(weight, column, g);
         } else {
 #pragma unroll
             for (int o = 0; o < 4; ++o) {
-                v[o] = Storage<T>::load(input, column + o);
+                v[o] = Storage<T>::load(input + base, column + o);
                 if (Add)
                     v[o] = Storage<T>::round(
-                        __fadd_rn(v[o], Storage<T>::load(residual, column + o)));
-                g[o] = Storage<W>::load(weight, column + o);
+                        __fadd_rn(v[o], Storage<T>::load(residual + base, column + o)));
             }
+        }
+    };
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int column = t * 4; column < width; column += kRowSpan) {
+        float v[4];
+        fetch(column, v);
+        if (Add) {
+            if (Vector) {
+                Storage<T>::store4(added + base, column, v);
+            } else {
+#pragma unroll
+                for (int o = 0; o < 4; ++o)
+                    Storage<T>::store(added + base, column + o, v[o]);
+            }
+        }
+#pragma unroll
+        for (int o = 0; o < 4; ++o)
+            sums[o] = __fadd_rn(sums[o], __fmul_rn(v[o], v[o]));
+    }
+    float sum = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[1]), sums[2]), sums[3]);
+    sum = row_tree_sum(sum, tree, t, descending);
+    if (t == 0)
+        scale_slot = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.f / static_cast<float>(width)), epsilon));
+    __syncthreads();
+    const float scale = scale_slot;
+    for (int column = t * 4; column < width; column += kRowSpan) {
+        float v[4], g[4];
+        fetch(column, v);
+        if (Vector) {
+            Storage<W>::load4(weight, column, g);
+        } else {
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+                g[o] = Storage<W>::load(weight, column + o);
         }
 #pragma unroll
         for (int o = 0; o < 4; ++o) {
@@ -167,106 +280,231 @@ __global__ void __launch_bounds__(kRowThreads)
             v[o] = __fmul_rn(normalised, g[o]);
         }
         if (Vector) {
-            Storage<T>::store4(output, column, v);
+            Storage<T>::store4(output + base, column, v);
         } else {
 #pragma unroll
             for (int o = 0; o < 4; ++o)
-                Storage<T>::store(output, column + o, v[o]);
+                Storage<T>::store(output + base, column + o, v[o]);
         }
     }
 }
 
-/* Rows of any width, in the order of the reference's multi-row kernel
- * (inference_fusion.cuh:53-86): 256 threads, thread t sums columns t+256i in
- * sequence, a descending shuffle tree per warp, then the eight warp sums through
- * the same tree; scale = rsqrt(sum/width + eps). */
-template <typename T>
-__global__ void __launch_bounds__(256) rms_rows_kernel(int rows, int width, float epsilon,
-                                                       const T *input, const T *weight, T *output)
+constexpr int kStagedThreads = 256;
+
+/* Sum over the 256 threads in the multi-row order: descending shuffle tree per
+ * warp, the eight warp sums through the same tree. Every thread gets the total. */
+__device__ __forceinline__ float staged_tree_sum(float sum, float *warp_sums)
 {
-    __shared__ float warp_sums[8];
+    for (int offset = 16; offset; offset >>= 1)
+        sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, offset));
+    if ((threadIdx.x & 31) == 0)
+        warp_sums[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        sum = threadIdx.x < 8 ? warp_sums[threadIdx.x] : 0.f;
+        for (int offset = 16; offset; offset >>= 1)
+            sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, offset));
+        if (threadIdx.x == 0)
+            warp_sums[8] = sum;
+    }
+    __syncthreads();
+    return warp_sums[8];
+}
+
+/* Rows of any width, multi-row order. With Staged the row is brought into
+ * dynamic shared memory by 16-byte loads (width a multiple of the vector
+ * length, pointers 16-byte aligned, row fits in `width * sizeof(T)` bytes of
+ * shared memory), each thread then takes its columns t+256i from there, and the
+ * scaling pass reads shared memory and writes 16-byte vectors: one global read
+ * of the row instead of two strided ones. Without Staged both passes read
+ * global memory element by element. The output may be the input: a row is
+ * complete in shared memory (or each element read) before it is overwritten. */
+template <typename T, bool Staged>
+__global__ void __launch_bounds__(kStagedThreads)
+    rows_staged(int rows, int width, float epsilon, const T *input,
+                const T *weight, T *output)
+{
+    extern __shared__ __align__(16) uint8_t staged_bytes[];
+    __shared__ float warp_sums[9];
+    T *row_copy = reinterpret_cast<T *>(staged_bytes);
+    constexpr int kLanes = Storage<T>::kLanes;
+    const int t = threadIdx.x;
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const T *source = input + row * width;
         float sum = 0.f;
-        for (int column = threadIdx.x; column < width; column += 256) {
-            float value = Storage<T>::load(source, column);
-            sum = __fadd_rn(sum, __fmul_rn(value, value));
+        if (Staged) {
+            for (int column = t * kLanes; column < width; column += kStagedThreads * kLanes)
+                *reinterpret_cast<uint4 *>(row_copy + column) =
+                    *reinterpret_cast<const uint4 *>(source + column);
+            __syncthreads();
+            for (int column = t; column < width; column += kStagedThreads) {
+                const float value = Storage<T>::load(row_copy, column);
+                sum = __fadd_rn(sum, __fmul_rn(value, value));
+            }
+        } else {
+            for (int column = t; column < width; column += kStagedThreads) {
+                const float value = Storage<T>::load(source, column);
+                sum = __fadd_rn(sum, __fmul_rn(value, value));
+            }
         }
-        for (int offset = 16; offset; offset >>= 1)
-            sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, offset));
-        if ((threadIdx.x & 31) == 0)
-            warp_sums[threadIdx.x >> 5] = sum;
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            sum = threadIdx.x < 8 ? warp_sums[threadIdx.x] : 0.f;
-            for (int offset = 16; offset; offset >>= 1)
-                sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, offset));
-            if (threadIdx.x == 0)
-                warp_sums[0] = rsqrtf(sum / static_cast<float>(width) + epsilon);
+        sum = staged_tree_sum(sum, warp_sums);
+        const float scale = rsqrtf(sum / static_cast<float>(width) + epsilon);
+        if (Staged) {
+            for (int column = t * kLanes; column < width; column += kStagedThreads * kLanes) {
+                float v[kLanes], g[kLanes];
+                Storage<T>::load16(row_copy, column, v);
+                Storage<T>::load16(weight, column, g);
+#pragma unroll
+                for (int o = 0; o < kLanes; ++o)
+                    v[o] = __fmul_rn(Storage<T>::round(__fmul_rn(v[o], scale)), g[o]);
+                Storage<T>::store16(output, row * width + column, v);
+            }
+        } else {
+            for (int column = t; column < width; column += kStagedThreads) {
+                const float normalised =
+                    Storage<T>::round(__fmul_rn(Storage<T>::load(source, column), scale));
+                Storage<T>::store(output, row * width + column,
+                                  __fmul_rn(normalised, Storage<T>::load(weight, column)));
+            }
         }
-        __syncthreads();
-        const float scale = warp_sums[0];
-        for (int column = threadIdx.x; column < width; column += 256) {
-            float normalised = Storage<T>::round(__fmul_rn(Storage<T>::load(source, column), scale));
-            Storage<T>::store(output, row * width + column,
-                              __fmul_rn(normalised, Storage<T>::load(weight, column)));
-        }
-        __syncthreads();
+        __syncthreads(); /* the row copy and warp_sums are reused by the next row */
     }
 }
 
-__global__ void square_kernel(size_t count, const __nv_bfloat16 *input, float *output)
+/* ---- elementwise kernels -------------------------------------------------------
+ * Each works on 16-byte vectors (eight BF16 or four FP32 per thread and step)
+ * over the leading `vectors * kLanes` elements and finishes the remaining
+ * elements one by one; the host passes vectors = 0 when a pointer is not
+ * 16-byte aligned. Outputs may be one of the inputs (each thread reads its
+ * vector before it writes it). `width`-dependent kernels are vectorised only when width is a
+ * multiple of the vector length, so that a vector never crosses a row. */
+
+/* output[i] = input[i]^2 in FP32 (the per-element squares the multi-kernel RMS
+ * path of the reference averages, backend.cu:1442-1454). */
+__global__ void __launch_bounds__(256)
+    square_kernel(size_t count, size_t vectors, const __nv_bfloat16 *input,
+                  float *output)
 {
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
-         i += size_t(gridDim.x) * blockDim.x) {
-        float value = __bfloat162float(input[i]);
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (size_t vector = first; vector < vectors; vector += stride) {
+        float v[8];
+        Storage<__nv_bfloat16>::load16(input, vector * 8, v);
+        float4 *target = reinterpret_cast<float4 *>(output + vector * 8);
+        target[0] = make_float4(__fmul_rn(v[0], v[0]), __fmul_rn(v[1], v[1]), __fmul_rn(v[2], v[2]),
+                                __fmul_rn(v[3], v[3]));
+        target[1] = make_float4(__fmul_rn(v[4], v[4]), __fmul_rn(v[5], v[5]), __fmul_rn(v[6], v[6]),
+                                __fmul_rn(v[7], v[7]));
+    }
+    for (size_t i = vectors * 8 + first; i < count; i += stride) {
+        const float value = __bfloat162float(input[i]);
         output[i] = __fmul_rn(value, value);
     }
 }
 
+/* output = rnd(rnd(input * rsqrt(means[row] + eps)) * weight[column]) with a
+ * mean of squares per row supplied by the caller (backend.cu:1456-1475). */
 template <typename T>
-__global__ void scale_kernel(size_t count, int width, float epsilon, const T *input,
-                             const T *weight, const float *means, T *output)
+__global__ void __launch_bounds__(256)
+    scale_kernel(size_t count, size_t vectors, int width, float epsilon, const T *input,
+                 const T *weight, const float *means,
+                 T *output)
 {
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
-         i += size_t(gridDim.x) * blockDim.x) {
-        float scale = rsqrtf(__fadd_rn(means[i / width], epsilon));
-        float normalised = Storage<T>::round(__fmul_rn(Storage<T>::load(input, i), scale));
+    constexpr int kLanes = Storage<T>::kLanes;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (size_t vector = first; vector < vectors; vector += stride) {
+        const size_t i = vector * kLanes;
+        const size_t row = i / width;
+        const float scale = rsqrtf(__fadd_rn(means[row], epsilon));
+        float v[kLanes], g[kLanes];
+        Storage<T>::load16(input, i, v);
+        Storage<T>::load16(weight, i - row * width, g);
+#pragma unroll
+        for (int o = 0; o < kLanes; ++o)
+            v[o] = __fmul_rn(Storage<T>::round(__fmul_rn(v[o], scale)), g[o]);
+        Storage<T>::store16(output, i, v);
+    }
+    for (size_t i = vectors * kLanes + first; i < count; i += stride) {
+        const float scale = rsqrtf(__fadd_rn(means[i / width], epsilon));
+        const float normalised = Storage<T>::round(__fmul_rn(Storage<T>::load(input, i), scale));
         Storage<T>::store(output, i, __fmul_rn(normalised, Storage<T>::load(weight, i % width)));
     }
 }
 
-/* SiLU(gate) rounded to storage, then times up (inference_fusion.cuh:19-29). */
-template <typename T>
-__global__ void silu_multiply_kernel(size_t count, const T *gate, const T *up, T *output)
+/* SiLU(g) = g / (1 + exp(-g)), the expression of inference_fusion.cuh:19-29. */
+__device__ __forceinline__ float silu(float g)
 {
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
-         i += size_t(gridDim.x) * blockDim.x) {
-        float g = Storage<T>::load(gate, i);
-        float activated = Storage<T>::round(g / (1.f + expf(-g)));
+    return g / (1.f + expf(-g));
+}
+
+/* output = rnd(rnd(SiLU(gate)) * up). */
+template <typename T>
+__global__ void __launch_bounds__(256)
+    silu_multiply_kernel(size_t count, size_t vectors, const T *gate,
+                         const T *up, T *output)
+{
+    constexpr int kLanes = Storage<T>::kLanes;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (size_t vector = first; vector < vectors; vector += stride) {
+        float g[kLanes], u[kLanes];
+        Storage<T>::load16(gate, vector * kLanes, g);
+        Storage<T>::load16(up, vector * kLanes, u);
+#pragma unroll
+        for (int o = 0; o < kLanes; ++o)
+            g[o] = Storage<T>::round(silu(g[o])) * u[o];
+        Storage<T>::store16(output, vector * kLanes, g);
+    }
+    for (size_t i = vectors * kLanes + first; i < count; i += stride) {
+        const float activated = Storage<T>::round(silu(Storage<T>::load(gate, i)));
         Storage<T>::store(output, i, activated * Storage<T>::load(up, i));
     }
 }
 
-/* SiLU(gate)*up with optional clip and per-row routing factor; one rounding
- * (inference_fusion.cuh:31-51). Comparisons, not fmin/fmax, so NaNs survive. */
-template <typename T>
-__global__ void swiglu_kernel(size_t count, int width, float limit, const T *gate, const T *up,
-                              const float *routing, T *output)
+/* One element of the clipped, routed SwiGLU (inference_fusion.cuh:31-51): gate
+ * clipped from above, up from both sides (comparisons rather than fmin/fmax, so
+ * that NaNs pass through), SiLU(gate) * up, times the row's routing factor, one
+ * rounding by the caller. */
+__device__ __forceinline__ float swiglu_element(float g, float u, float limit, bool routed,
+                                                float factor)
 {
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
-         i += size_t(gridDim.x) * blockDim.x) {
-        float g = Storage<T>::load(gate, i), u = Storage<T>::load(up, i);
-        if (limit > 0.f) {
-            g = g > limit ? limit : g;
-            u = u > limit ? limit : u;
-            u = u < -limit ? -limit : u;
-        }
-        float value = __fmul_rn(g / (1.f + expf(-g)), u);
-        if (routing != nullptr)
-            value = __fmul_rn(routing[i / width], value);
-        Storage<T>::store(output, i, value);
+    if (limit > 0.f) {
+        g = g > limit ? limit : g;
+        u = u > limit ? limit : u;
+        u = u < -limit ? -limit : u;
     }
+    float value = __fmul_rn(silu(g), u);
+    if (routed)
+        value = __fmul_rn(factor, value);
+    return value;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    swiglu_kernel(size_t count, size_t vectors, int width, float limit, const T *gate,
+                  const T *up, const float *routing,
+                  T *output)
+{
+    constexpr int kLanes = Storage<T>::kLanes;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const bool routed = routing != nullptr;
+    for (size_t vector = first; vector < vectors; vector += stride) {
+        const size_t i = vector * kLanes;
+        const float factor = routed ? routing[i / width] : 1.f;
+        float g[kLanes], u[kLanes];
+        Storage<T>::load16(gate, i, g);
+        Storage<T>::load16(up, i, u);
+#pragma unroll
+        for (int o = 0; o < kLanes; ++o)
+            g[o] = swiglu_element(g[o], u[o], limit, routed, factor);
+        Storage<T>::store16(output, i, g);
+    }
+    for (size_t i = vectors * kLanes + first; i < count; i += stride)
+        Storage<T>::store(output, i,
+                          swiglu_element(Storage<T>::load(gate, i), Storage<T>::load(up, i), limit,
+                                         routed, routed ? routing[i / width] : 1.f));
 }
 
 } // namespace rms

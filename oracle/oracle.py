@@ -11,6 +11,7 @@ in ascending k.
 """
 
 import ctypes as ct
+import os
 import subprocess
 from functools import lru_cache
 from pathlib import Path
@@ -23,9 +24,29 @@ _I = ct.c_int
 _F = ct.c_float
 
 
+def reference_tree():
+    """Where the reference's sources are, or None.
+
+    ``CAMBLAS_REFERENCE`` names the tree; without it a checkout called
+    ``reference`` beside this repository is used when it exists. On a machine
+    with neither, only the prebuilt files under ``_ref/`` are available.
+    """
+    named = os.environ.get("CAMBLAS_REFERENCE")
+    candidates = [Path(named)] if named else [HERE.parents[1] / "reference"]
+    for candidate in candidates:
+        if (candidate / "src" / "scalar.c").is_file():
+            return candidate
+    return None
+
+
 def build():
-    """Compile ``liboracle.so`` (and the reference library when its sources exist)."""
-    subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    """Compile ``liboracle.so`` and, when the reference's sources are at hand, the
+    reference's own CPU and CUDA libraries into ``_ref/`` (see the Makefile)."""
+    command = ["make", "-C", str(HERE)]
+    tree = reference_tree()
+    if tree is not None:
+        command.append(f"REFERENCE={tree}")
+    subprocess.run(command, check=True, capture_output=True)
 
 
 @lru_cache(maxsize=1)
