@@ -178,8 +178,10 @@ def add_rms_norm(x, residual, weight, epsilon):
 
     ``added`` is rounded to the storage type before the mean of squares;
     ``normalised = rnd(rnd(added * rsqrt(mean(added^2)+eps)) * weight)``
-    (``inference_fusion.cuh:136-191``). Any number of rows of a contiguous
-    ``[..., width]`` tensor is handled by one launch with one CTA per row.
+    (``inference_fusion.cuh:136-191``). Any number of rows is handled by one
+    launch with one CTA per row. Two-dimensional ``x`` and ``residual`` may be
+    views whose rows are contiguous but spaced apart (a column slice, one half
+    of an interleaved buffer): they are read where they lie.
     """
     _require(x.is_cuda and residual.is_cuda and weight.is_cuda, "operands must be CUDA tensors")
     _require(x.dtype == residual.dtype == weight.dtype and x.device == residual.device == weight.device,
@@ -189,7 +191,24 @@ def add_rms_norm(x, residual, weight, epsilon):
     code = _dtype_code(x)
     width = x.shape[-1]
     _require(4 <= width <= 65536 and width % 4 == 0, "width must be a multiple of four up to 65536")
-    x2, r2, w2 = x.contiguous(), residual.contiguous(), weight.contiguous()
+    w2 = weight.contiguous()
+
+    def rows_in_place(tensor):
+        return (tensor.dim() == 2 and tensor.stride(1) == 1 and tensor.stride(0) >= width
+                and tensor.stride(0) % 4 == 0 and tensor.stride(0) <= _INT_MAX)
+
+    if rows_in_place(x) and rows_in_place(residual) and not (x.is_contiguous()
+                                                              and residual.is_contiguous()):
+        added = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+        out = torch.empty_like(added)
+        if x.shape[0]:
+            with torch.cuda.device(x.device):
+                native = _native.context(x.device.index)
+                native.call("add_rms_norm_strided", code, x.shape[0], width, float(epsilon),
+                            _pointer(x), x.stride(0), _pointer(residual), residual.stride(0),
+                            _pointer(w2), _pointer(added), width, _pointer(out), width)
+        return added, out
+    x2, r2 = x.contiguous(), residual.contiguous()
     added, out = torch.empty_like(x2), torch.empty_like(x2)
     rows = x2.numel() // width
     if rows:

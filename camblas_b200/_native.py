@@ -92,6 +92,8 @@ _SIGNATURES = {
     "rms_norm_decode": ([_P, _I, _I, _I, _F, _I, _I, _P, _P, _P], _I),
     "add_rms_norm": ([_P, _I, _I, _F, _P, _P, _P, _P, _P], _I),
     "add_rms_norm_rows": ([_P, _I, _I, _I, _F, _P, _P, _P, _P, _P], _I),
+    "add_rms_norm_strided": ([_P, _I, _I, _I, _F, _P, ct.c_longlong, _P, ct.c_longlong, _P, _P,
+                              ct.c_longlong, _P, ct.c_longlong], _I),
     "bfloat16_square": ([_P, _U64, _P, _P], _I),
     "rms_scale": ([_P, _I, _U64, _I, _F, _P, _P, _P, _P], _I),
     "silu_multiply": ([_P, _I, _U64, _P, _P, _P], _I),

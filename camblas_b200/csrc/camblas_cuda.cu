@@ -375,12 +375,12 @@ int prepare_rms_kernels()
 }
 
 template <typename T, typename W, bool Add, int Sweeps>
-void launch_in_registers(camblas_cuda_context *context, int rows, int width, float epsilon,
-                         const T *in, const T *res, const W *gamma, T *sum, T *out,
+void launch_in_registers(camblas_cuda_context *context, int rows, int width, rms::RowPitch pitch,
+                         float epsilon, const T *in, const T *res, const W *gamma, T *sum, T *out,
                          bool round_before_weight, bool descending)
 {
     rms::rows_in_registers<T, W, Add, Sweeps><<<rows, rms::kRowThreads, 0, context->stream>>>(
-        width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+        width, pitch, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
 }
 
 /* Single-row order for `rows` rows, one CTA each. Rows of up to 16384 columns
@@ -388,10 +388,14 @@ void launch_in_registers(camblas_cuda_context *context, int rows, int width, flo
 template <typename T, typename W, bool Add>
 int launch_rms_rows(camblas_cuda_context *context, int rows, int width, float epsilon,
                     const void *input, const void *residual, const void *weight, void *added,
-                    void *output, bool round_before_weight, bool descending, bool in_place = false)
+                    void *output, bool round_before_weight, bool descending, bool in_place = false,
+                    const rms::RowPitch *pitches = nullptr)
 {
     constexpr uintptr_t mask = sizeof(T) * 4 - 1, weight_mask = sizeof(W) * 4 - 1;
-    const bool vector = width % 4 == 0 && !(uintptr_t(input) & mask) &&
+    const rms::RowPitch pitch = pitches ? *pitches : rms::RowPitch{width, width, width, width};
+    const bool pitches_ok = rows == 1 || (pitch.input % 4 == 0 && pitch.output % 4 == 0 &&
+                                          (!Add || (pitch.residual % 4 == 0 && pitch.added % 4 == 0)));
+    const bool vector = width % 4 == 0 && pitches_ok && !(uintptr_t(input) & mask) &&
                         !(uintptr_t(output) & mask) && !(uintptr_t(weight) & weight_mask) &&
                         (!Add || (!(uintptr_t(residual) & mask) && !(uintptr_t(added) & mask)));
     auto *in = static_cast<const T *>(input);
@@ -402,23 +406,23 @@ int launch_rms_rows(camblas_cuda_context *context, int rows, int width, float ep
     /* the register kernel declares its pointers restrict: not for in-place calls */
     const int sweeps = in_place ? 9 : (width + rms::kRowSpan - 1) / rms::kRowSpan;
     if (vector && sweeps <= 1)
-        launch_in_registers<T, W, Add, 1>(context, rows, width, epsilon, in, res, gamma, sum, out,
+        launch_in_registers<T, W, Add, 1>(context, rows, width, pitch, epsilon, in, res, gamma, sum, out,
                                           round_before_weight, descending);
     else if (vector && sweeps <= 2)
-        launch_in_registers<T, W, Add, 2>(context, rows, width, epsilon, in, res, gamma, sum, out,
+        launch_in_registers<T, W, Add, 2>(context, rows, width, pitch, epsilon, in, res, gamma, sum, out,
                                           round_before_weight, descending);
     else if (vector && sweeps <= 4)
-        launch_in_registers<T, W, Add, 4>(context, rows, width, epsilon, in, res, gamma, sum, out,
+        launch_in_registers<T, W, Add, 4>(context, rows, width, pitch, epsilon, in, res, gamma, sum, out,
                                           round_before_weight, descending);
     else if (vector && sweeps <= 8)
-        launch_in_registers<T, W, Add, 8>(context, rows, width, epsilon, in, res, gamma, sum, out,
+        launch_in_registers<T, W, Add, 8>(context, rows, width, pitch, epsilon, in, res, gamma, sum, out,
                                           round_before_weight, descending);
     else if (vector)
         rms::rows_two_sweeps<T, W, Add, true><<<rows, rms::kRowThreads, 0, context->stream>>>(
-            width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+            width, pitch, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
     else
         rms::rows_two_sweeps<T, W, Add, false><<<rows, rms::kRowThreads, 0, context->stream>>>(
-            width, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
+            width, pitch, epsilon, in, res, gamma, sum, out, round_before_weight, descending);
     return launched(context, Add ? "residual RMS normalisation" : "RMS normalisation");
 }
 
@@ -537,13 +541,16 @@ extern "C" int camblas_cuda_rms_norm_decode(camblas_cuda_context *context, int d
 namespace
 {
 int add_rms(camblas_cuda_context *context, int dtype, int rows, int width, float epsilon,
-            const void *input, const void *residual, const void *weight, void *added, void *output)
+            const void *input, const void *residual, const void *weight, void *added, void *output,
+            const rms::RowPitch *pitches = nullptr)
 {
     if (dtype == 0)
         return launch_rms_rows<float, float, true>(context, rows, width, epsilon, input, residual,
-                                                   weight, added, output, true, false);
+                                                   weight, added, output, true, false, false,
+                                                   pitches);
     return launch_rms_rows<__nv_bfloat16, __nv_bfloat16, true>(
-        context, rows, width, epsilon, input, residual, weight, added, output, true, false);
+        context, rows, width, epsilon, input, residual, weight, added, output, true, false, false,
+        pitches);
 }
 
 /* the five buffers of the residual form must all be present and pairwise distinct
@@ -588,6 +595,28 @@ extern "C" int camblas_cuda_add_rms_norm_rows(camblas_cuda_context *context, int
             return fail(context, "invalid residual RMS rows operands", 1);
         return add_rms(context, dtype, rows, width, epsilon, input, residual, weight, added,
                        output);
+    });
+}
+
+extern "C" int camblas_cuda_add_rms_norm_strided(camblas_cuda_context *context, int dtype, int rows,
+                                                 int width, float epsilon, const void *input,
+                                                 long long ld_input, const void *residual,
+                                                 long long ld_residual, const void *weight,
+                                                 void *added, long long ld_added, void *output,
+                                                 long long ld_output)
+{
+    return guarded(context, [&] {
+        if ((dtype != 0 && dtype != 2) || rows < 0 || width < 4 || width > 65536 || width % 4 ||
+            !std::isfinite(epsilon) || epsilon < 0 || ld_input < width || ld_residual < width ||
+            ld_added < width || ld_output < width)
+            return fail(context, "invalid residual RMS rows arguments", 1);
+        if (rows == 0)
+            return 0;
+        if (add_rms_operands_bad(input, residual, weight, added, output))
+            return fail(context, "invalid residual RMS rows operands", 1);
+        const rms::RowPitch pitch{ld_input, ld_residual, ld_added, ld_output};
+        return add_rms(context, dtype, rows, width, epsilon, input, residual, weight, added, output,
+                       &pitch);
     });
 }
 

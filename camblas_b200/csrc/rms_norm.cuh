@@ -104,6 +104,12 @@ template <> struct Storage<__nv_bfloat16> {
     }
 };
 
+/* Row pitches in elements of the four row-structured buffers of the single-row
+ * order kernels (a contiguous matrix has all four equal to the width). */
+struct RowPitch {
+    long long input, residual, added, output;
+};
+
 constexpr int kRowThreads = 512;
 constexpr int kRowSpan = kRowThreads * 4; /* columns one sweep of the 512 threads covers */
 
@@ -141,14 +147,18 @@ __device__ __forceinline__ float row_tree_sum(float sum, float *tree, int t, boo
  * are read exactly once and nothing depends on this CTA's own stores. */
 template <typename T, typename W, bool Add, int Sweeps>
 __global__ void __launch_bounds__(kRowThreads)
-    rows_in_registers(int width, float epsilon, const T *__restrict__ input,
+    rows_in_registers(int width, RowPitch pitch, float epsilon, const T *__restrict__ input,
                       const T *__restrict__ residual, const W *__restrict__ weight,
                       T *__restrict__ added, T *__restrict__ output, bool round_before_weight,
                       bool descending)
 {
     __shared__ float tree[kRowThreads];
     __shared__ float scale_slot;
-    const long long base = static_cast<long long>(blockIdx.x) * width;
+    const long long row = blockIdx.x;
+    input += row * pitch.input, output += row * pitch.output;
+    if (Add)
+        residual += row * pitch.residual, added += row * pitch.added;
+    constexpr long long base = 0;
     const int t = threadIdx.x;
     float v[Sweeps][4], r[Sweeps][4], g[Sweeps][4];
 #pragma unroll
@@ -212,12 +222,16 @@ __global__ void __launch_bounds__(kRowThreads)
  * access. */
 template <typename T, typename W, bool Add, bool Vector>
 __global__ void __launch_bounds__(kRowThreads)
-    rows_two_sweeps(int width, float epsilon, const T *input, const T *residual, const W *weight,
-                    T *added, T *output, bool round_before_weight, bool descending)
+    rows_two_sweeps(int width, RowPitch pitch, float epsilon, const T *input, const T *residual,
+                    const W *weight, T *added, T *output, bool round_before_weight, bool descending)
 {
     __shared__ float tree[kRowThreads];
     __shared__ float scale_slot;
-    const long long base = static_cast<long long>(blockIdx.x) * width;
+    const long long row = blockIdx.x;
+    input += row * pitch.input, output += row * pitch.output;
+    if (Add)
+        residual += row * pitch.residual, added += row * pitch.added;
+    constexpr long long base = 0;
     const int t = threadIdx.x;
     auto fetch = [&](int column, float (&v)[4]) {
         if (Vector) {

@@ -247,6 +247,17 @@ int camblas_cuda_add_rms_norm(camblas_cuda_context *context, int dtype, int widt
 int camblas_cuda_add_rms_norm_rows(camblas_cuda_context *context, int dtype, int rows, int width,
                                    float epsilon, const void *input, const void *residual,
                                    const void *weight, void *added, void *output);
+/* No counterpart in the reference ABI. camblas_cuda_add_rms_norm_rows for rows
+ * that are not packed back to back: row i of input, residual, added and output
+ * starts ld_input, ld_residual, ld_added and ld_output elements after row i-1
+ * (each >= width), so that column slices and interleaved buffers are
+ * normalised where they lie instead of being copied first. Same arithmetic,
+ * same bits. The rows of `added` and `output` must not overlap any row read. */
+int camblas_cuda_add_rms_norm_strided(camblas_cuda_context *context, int dtype, int rows, int width,
+                                      float epsilon, const void *input, long long ld_input,
+                                      const void *residual, long long ld_residual,
+                                      const void *weight, void *added, long long ld_added,
+                                      void *output, long long ld_output);
 /* Replace camblas_cuda_bfloat16_square / rms_scale (camblas_cuda.h:190-198;
  * backend.cu:1442-1475). */
 int camblas_cuda_bfloat16_square(camblas_cuda_context *context, uint64_t count, const void *input,

@@ -138,3 +138,20 @@ def test_silu_multiply_and_swiglu(rng):
     assert ulp_distance_bf16(tensor_to_bits(out), expected).max() <= 1
     nan = bits_to_tensor(np.full((1, 8), 0x7FC0, dtype=np.uint16))
     assert torch.isnan(_kernels.swiglu(nan, nan, 2.0)).all()
+
+
+def test_add_rms_norm_on_spaced_rows(rng):
+    """Rows that are contiguous but spaced apart (the two halves of an interleaved
+    [rows, 2, width] buffer) are normalised where they lie and give the bits of the
+    packed call."""
+    rows, width = 37, 4096
+    both = bits_to_tensor(normal_bits(rng, (rows, 2, width)))
+    g = bits_to_tensor(gamma_bits(rng, width))
+    x, r = both[:, 0], both[:, 1]
+    assert not x.is_contiguous() and x.stride(0) == 2 * width
+    added, out = _kernels.add_rms_norm(x, r, g, 1e-5)
+    expected_added, expected_out = _kernels.add_rms_norm(x.contiguous(), r.contiguous(), g, 1e-5)
+    assert torch.equal(added, expected_added) and torch.equal(out, expected_out)
+    status, context = raw("add_rms_norm_strided", 2, rows, width, 1e-5, pointer(x), width - 4,
+                          pointer(r), 2 * width, pointer(g), pointer(added), width, pointer(out), width)
+    assert status == -1 and "invalid" in error_text(context)
