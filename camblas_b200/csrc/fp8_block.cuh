@@ -12,12 +12,12 @@
  *    being multiplied: acc = fma(block, a_scale*w_scale, acc), blocks in
  *    ascending K order - the recurrence of the reference's block-128 decode
  *    kernel (camblas/_hopper.py:118-126, 168-182), applied to every row.
- *    For more than 64 token rows fp8_block_rows (eight promotion warps, four
+ *    For more than 128 token rows fp8_block_rows (eight promotion warps, four
  *    accumulator buffers) replaces the row mode of this kernel; what bounds
  *    it is written there.
  *    Store modes as in the BF16 kernel: token rows on TMEM lanes with a TMA
- *    store, or operands swapped for up to 64 tokens, optionally with a K split
- *    through FP32 scratch and an ordered reduction.
+ *    store, or operands swapped for up to 128 tokens (64 per column block),
+ *    optionally with a K split through FP32 scratch and an ordered reduction.
  * 3. fp8_token_kernel: the reference ABI's single-token block-32 product
  *    (src/cuda/fp8_decode.cuh:74-165) on CUDA cores: 16-byte weight loads,
  *    per-block FP32 dot products, then sum = fma(rnd(dot*sw), sx, sum) in
@@ -94,6 +94,7 @@ struct BlockTask {
 };
 
 constexpr int kBlockDepth = 128; /* bytes = E4M3 elements per stage row */
+constexpr int kSwappedRowLimit = 128; /* most token rows the swapped (weight-streaming) modes take */
 
 /* Dynamic shared memory of fp8_block_gemm: the BF16 kernel's layout plus, in the
  * swapped modes, BN scale products for each of the four epilogue warps. */
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
 
 /* ---- 2b. many token rows: eight promotion warps, four accumulator buffers ------ */
 
-/* Row mode for more than 64 token rows. Two warps share each quarter of the
+/* Row mode for more than 128 token rows. Two warps share each quarter of the
  * tensor-memory lanes and take 64 columns each (64 accumulator registers, one
  * 64-column load, 64 FMAs per K block), so every scheduler has two promotion
  * warps to interleave, and the accumulator ring has four 128-column buffers
@@ -790,7 +791,11 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
     task.status = context->status;
     CUtensorMap p, qm, d;
     const auto type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    if (rows > 64) {
+    /* Up to 128 token rows the product is bound by streaming the weights, and a
+     * 128 x 128 row tiling would leave most SMs idle (32 tiles for N = 4096): those
+     * shapes take the swapped kernel, one or two 64-token column blocks per weight
+     * band with the K range split over the SMs. */
+    if (rows > kSwappedRowLimit) {
         task.rows = rows, task.cols = outputs;
         task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;
         task.split = 1, task.k_blocks_per_split = task.k_blocks;
@@ -900,7 +905,7 @@ extern "C" int camblas_cuda_fp8_block_gemm(camblas_cuda_context *context, int ro
         if (!q || !q_scale || !w || !w_scale || !out || out == q || out == w)
             return host::fail(context, "missing or aliased FP8 block GEMM operand", 1);
         if (!host::aligned16(q) || !host::aligned16(w) ||
-            (rows > 64 && (!host::aligned16(out) || ldo % 8 || outputs % 8)))
+            (rows > fp8::kSwappedRowLimit && (!host::aligned16(out) || ldo % 8 || outputs % 8)))
             return host::fail(context, "FP8 block GEMM operands must be 16-byte aligned", 1);
         context->counts[0]++;
         return fp8::block_gemm(context, rows, outputs, inner, q, q_scale, w, w_scale, out, ldo);

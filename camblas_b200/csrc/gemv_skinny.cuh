@@ -60,6 +60,28 @@ __global__ void __launch_bounds__(kThreads) skinny_gemv(const Task task)
     const int vectors = span >> 3;   /* whole 16-byte pieces */
     const int span8 = (span + 7) & ~7;
 
+    const int row0 = (blockIdx.x * kWarps + warp) * RowsPerWarp;
+    const bool active = row0 < task.outputs; /* warps beyond the last row only help staging */
+    const __nv_bfloat16 *rows[RowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < RowsPerWarp; ++r)
+        rows[r] = task.w + static_cast<long long>(min(row0 + r, task.outputs - 1)) * task.ldw + k0;
+
+    /* The first batch of weight loads is issued before the tokens are staged,
+     * so that the HBM latency of a short row runs under the staging and its
+     * barrier instead of after them. */
+    constexpr int kUnroll = RowsPerWarp >= 4 ? 2 : 4;
+    uint4 wv[kUnroll][RowsPerWarp];
+    int v = lane;
+    const bool ahead = active && v + (kUnroll - 1) * 32 < vectors;
+    if (ahead) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int r = 0; r < RowsPerWarp; ++r)
+                wv[u][r] = load_stream(rows[r] + (v + u * 32) * 8);
+    }
+
     /* Stage the token slice: [Tokens][span8] BF16, zero padded. */
     __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(shared);
     for (int t = 0; t < Tokens; ++t) {
@@ -68,14 +90,8 @@ __global__ void __launch_bounds__(kThreads) skinny_gemv(const Task task)
             xs[t * span8 + i] = (t < task.tokens && i < span) ? source[i] : __float2bfloat16(0.f);
     }
     __syncthreads();
-
-    const int row0 = (blockIdx.x * kWarps + warp) * RowsPerWarp;
-    if (row0 >= task.outputs)
+    if (!active)
         return;
-    const __nv_bfloat16 *rows[RowsPerWarp];
-#pragma unroll
-    for (int r = 0; r < RowsPerWarp; ++r)
-        rows[r] = task.w + static_cast<long long>(min(row0 + r, task.outputs - 1)) * task.ldw + k0;
 
     float acc[RowsPerWarp][Tokens];
 #pragma unroll
@@ -84,20 +100,12 @@ __global__ void __launch_bounds__(kThreads) skinny_gemv(const Task task)
         for (int t = 0; t < Tokens; ++t)
             acc[r][t] = 0.f;
 
-    constexpr int kUnroll = RowsPerWarp >= 4 ? 2 : 4;
-    int v = lane;
-    for (; v + (kUnroll - 1) * 32 < vectors; v += kUnroll * 32) {
-        uint4 wv[kUnroll][RowsPerWarp];
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u)
-#pragma unroll
-            for (int r = 0; r < RowsPerWarp; ++r)
-                wv[u][r] = load_stream(rows[r] + (v + u * 32) * 8);
+    auto multiply = [&](int at) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
             for (int t = 0; t < Tokens; ++t) {
-                uint4 xv = *reinterpret_cast<const uint4 *>(xs + t * span8 + (v + u * 32) * 8);
+                uint4 xv = *reinterpret_cast<const uint4 *>(xs + t * span8 + (at + u * 32) * 8);
                 const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
                 for (int r = 0; r < RowsPerWarp; ++r) {
@@ -111,6 +119,18 @@ __global__ void __launch_bounds__(kThreads) skinny_gemv(const Task task)
                 }
             }
         }
+    };
+    if (ahead) {
+        multiply(v);
+        v += kUnroll * 32;
+    }
+    for (; v + (kUnroll - 1) * 32 < vectors; v += kUnroll * 32) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int r = 0; r < RowsPerWarp; ++r)
+                wv[u][r] = load_stream(rows[r] + (v + u * 32) * 8);
+        multiply(v);
     }
     for (; v < vectors; v += 32) {
 #pragma unroll

@@ -34,6 +34,23 @@ namespace rms
 template <typename T> struct Storage;
 template <> struct Storage<float> {
     static constexpr int kLanes = 4;
+    using Raw4 = float4; /* four elements as they are stored */
+    static __device__ __forceinline__ Raw4 load_raw4(const float *p, long long i)
+    {
+        return *reinterpret_cast<const float4 *>(p + i);
+    }
+    static __device__ __forceinline__ void store_raw4(float *p, long long i, Raw4 q)
+    {
+        *reinterpret_cast<float4 *>(p + i) = q;
+    }
+    static __device__ __forceinline__ void unpack4(Raw4 q, float (&v)[4])
+    {
+        v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+    }
+    static __device__ __forceinline__ Raw4 pack4(const float (&v)[4])
+    {
+        return make_float4(v[0], v[1], v[2], v[3]);
+    }
     static __device__ __forceinline__ float load(const float *p, long long i) { return p[i]; }
     static __device__ __forceinline__ float round(float v) { return v; }
     static __device__ __forceinline__ void store(float *p, long long i, float v) { p[i] = v; }
@@ -57,6 +74,25 @@ template <> struct Storage<float> {
 };
 template <> struct Storage<__nv_bfloat16> {
     static constexpr int kLanes = 8;
+    using Raw4 = uint2;
+    static __device__ __forceinline__ Raw4 load_raw4(const __nv_bfloat16 *p, long long i)
+    {
+        return *reinterpret_cast<const uint2 *>(p + i);
+    }
+    static __device__ __forceinline__ void store_raw4(__nv_bfloat16 *p, long long i, Raw4 q)
+    {
+        *reinterpret_cast<uint2 *>(p + i) = q;
+    }
+    static __device__ __forceinline__ void unpack4(Raw4 q, float (&v)[4])
+    {
+        v[0] = __uint_as_float(q.x << 16), v[1] = __uint_as_float(q.x & 0xffff0000u);
+        v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ Raw4 pack4(const float (&v)[4])
+    {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        return make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+    }
     static __device__ __forceinline__ float load(const __nv_bfloat16 *p, long long i)
     {
         return __bfloat162float(p[i]);
@@ -139,14 +175,25 @@ __device__ __forceinline__ float row_tree_sum(float sum, float *tree, int t, boo
     return sum;
 }
 
-/* One row per CTA, the row held in registers: Sweeps * 4 values per thread
- * (width <= Sweeps * 2048, width % 4 == 0, all pointers aligned for four-element
- * vectors). Every load of the row - input, residual and weight - is issued
- * before the first value is used; the sums run over the values in the order
- * 4t+o+2048i; the scaling pass works on the registers, so input and residual
- * are read exactly once and nothing depends on this CTA's own stores. */
+/* One row per CTA, the row held in registers in its stored form: Sweeps
+ * four-element vectors per thread (width <= Sweeps * 2048, width % 4 == 0, all
+ * pointers aligned for four-element vectors). The loads of input and residual
+ * are all issued before the first value is used, the weight loads before the
+ * reduction tree so that they arrive while it runs; the sums run over the
+ * values in the order 4t+o+2048i; the scaling pass unpacks the registers again,
+ * so input and residual are read exactly once and nothing depends on this
+ * CTA's own stores. Keeping the stored form (two registers per four BF16
+ * values; rnd(x+r) is exactly representable) is what lets four CTAs share an
+ * SM - with the row unpacked to FP32 only two fit and the kernel ran a quarter
+ * slower on rows streamed from HBM. */
+template <typename T, int Sweeps>
+constexpr int rows_in_registers_ctas()
+{
+    return (sizeof(T) == 2 && Sweeps <= 4) ? 4 : (sizeof(T) * Sweeps <= 16 ? 2 : 1);
+}
+
 template <typename T, typename W, bool Add, int Sweeps>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, rows_in_registers_ctas<T, Sweeps>())
     rows_in_registers(int width, RowPitch pitch, float epsilon, const T *__restrict__ input,
                       const T *__restrict__ residual, const W *__restrict__ weight,
                       T *__restrict__ added, T *__restrict__ output, bool round_before_weight,
@@ -158,39 +205,44 @@ __global__ void __launch_bounds__(kRowThreads)
     input += row * pitch.input, output += row * pitch.output;
     if (Add)
         residual += row * pitch.residual, added += row * pitch.added;
-    constexpr long long base = 0;
     const int t = threadIdx.x;
-    float v[Sweeps][4], r[Sweeps][4], g[Sweeps][4];
+    typename Storage<T>::Raw4 kept[Sweeps], other[Sweeps];
 #pragma unroll
     for (int i = 0; i < Sweeps; ++i) {
         const int column = i * kRowSpan + t * 4;
         if (column < width) {
-            Storage<T>::load4(input + base, column, v[i]);
+            kept[i] = Storage<T>::load_raw4(input, column);
             if (Add)
-                Storage<T>::load4(residual + base, column, r[i]);
+                other[i] = Storage<T>::load_raw4(residual, column);
         }
-    }
-#pragma unroll
-    for (int i = 0; i < Sweeps; ++i) {
-        const int column = i * kRowSpan + t * 4;
-        if (column < width)
-            Storage<W>::load4(weight, column, g[i]);
     }
     float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < Sweeps; ++i) {
         const int column = i * kRowSpan + t * 4;
         if (column < width) {
+            float v[4];
+            Storage<T>::unpack4(kept[i], v);
             if (Add) {
+                float r[4];
+                Storage<T>::unpack4(other[i], r);
 #pragma unroll
                 for (int o = 0; o < 4; ++o)
-                    v[i][o] = Storage<T>::round(__fadd_rn(v[i][o], r[i][o]));
-                Storage<T>::store4(added + base, column, v[i]);
+                    v[o] = Storage<T>::round(__fadd_rn(v[o], r[o]));
+                kept[i] = Storage<T>::pack4(v);
+                Storage<T>::store_raw4(added, column, kept[i]);
             }
 #pragma unroll
             for (int o = 0; o < 4; ++o)
-                sums[o] = __fadd_rn(sums[o], __fmul_rn(v[i][o], v[i][o]));
+                sums[o] = __fadd_rn(sums[o], __fmul_rn(v[o], v[o]));
         }
+    }
+    typename Storage<W>::Raw4 gamma[Sweeps];
+#pragma unroll
+    for (int i = 0; i < Sweeps; ++i) {
+        const int column = i * kRowSpan + t * 4;
+        if (column < width)
+            gamma[i] = Storage<W>::load_raw4(weight, column);
     }
     float sum = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[1]), sums[2]), sums[3]);
     sum = row_tree_sum(sum, tree, t, descending);
@@ -202,14 +254,17 @@ __global__ void __launch_bounds__(kRowThreads)
     for (int i = 0; i < Sweeps; ++i) {
         const int column = i * kRowSpan + t * 4;
         if (column < width) {
+            float v[4], g[4];
+            Storage<T>::unpack4(kept[i], v);
+            Storage<W>::unpack4(gamma[i], g);
 #pragma unroll
             for (int o = 0; o < 4; ++o) {
-                float normalised = __fmul_rn(v[i][o], scale);
+                float normalised = __fmul_rn(v[o], scale);
                 if (round_before_weight)
                     normalised = Storage<T>::round(normalised);
-                v[i][o] = __fmul_rn(normalised, g[i][o]);
+                v[o] = __fmul_rn(normalised, g[o]);
             }
-            Storage<T>::store4(output + base, column, v[i]);
+            Storage<T>::store_raw4(output, column, Storage<T>::pack4(v));
         }
     }
 }
@@ -330,26 +385,55 @@ __device__ __forceinline__ float staged_tree_sum(float sum, float *warp_sums)
  * length, pointers 16-byte aligned, row fits in `width * sizeof(T)` bytes of
  * shared memory), each thread then takes its columns t+256i from there, and the
  * scaling pass reads shared memory and writes 16-byte vectors: one global read
- * of the row instead of two strided ones. Without Staged both passes read
- * global memory element by element. The output may be the input: a row is
- * complete in shared memory (or each element read) before it is overwritten. */
+ * of the row instead of two strided ones. A CTA that works through several rows
+ * fetches the next row into registers (up to kPrefetch vectors per thread, i.e.
+ * rows of up to 16 KB) while it reduces and scales the current one, so that its
+ * share of the memory system does not idle during the two passes. Without
+ * Staged both passes read global memory element by element. The output may be
+ * the input: a row is complete in shared memory (or each element read) before
+ * it is overwritten, and the row fetched ahead is a different row. */
+constexpr int kPrefetch = 4;
+
 template <typename T, bool Staged>
 __global__ void __launch_bounds__(kStagedThreads)
-    rows_staged(int rows, int width, float epsilon, const T *input,
-                const T *weight, T *output)
+    rows_staged(int rows, int width, float epsilon, const T *input, const T *weight, T *output)
 {
     extern __shared__ __align__(16) uint8_t staged_bytes[];
     __shared__ float warp_sums[9];
     T *row_copy = reinterpret_cast<T *>(staged_bytes);
     constexpr int kLanes = Storage<T>::kLanes;
     const int t = threadIdx.x;
+    const bool ahead = Staged && width <= kPrefetch * kStagedThreads * kLanes;
+    uint4 next[kPrefetch];
+    auto fetch = [&](long long row) {
+        const T *source = input + row * width;
+#pragma unroll
+        for (int i = 0; i < kPrefetch; ++i) {
+            const int column = (i * kStagedThreads + t) * kLanes;
+            if (column < width)
+                next[i] = *reinterpret_cast<const uint4 *>(source + column);
+        }
+    };
+    if (ahead && blockIdx.x < rows)
+        fetch(blockIdx.x);
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const T *source = input + row * width;
         float sum = 0.f;
         if (Staged) {
-            for (int column = t * kLanes; column < width; column += kStagedThreads * kLanes)
-                *reinterpret_cast<uint4 *>(row_copy + column) =
-                    *reinterpret_cast<const uint4 *>(source + column);
+            if (ahead) {
+#pragma unroll
+                for (int i = 0; i < kPrefetch; ++i) {
+                    const int column = (i * kStagedThreads + t) * kLanes;
+                    if (column < width)
+                        *reinterpret_cast<uint4 *>(row_copy + column) = next[i];
+                }
+                if (row + gridDim.x < rows)
+                    fetch(row + gridDim.x);
+            } else {
+                for (int column = t * kLanes; column < width; column += kStagedThreads * kLanes)
+                    *reinterpret_cast<uint4 *>(row_copy + column) =
+                        *reinterpret_cast<const uint4 *>(source + column);
+            }
             __syncthreads();
             for (int column = t; column < width; column += kStagedThreads) {
                 const float value = Storage<T>::load(row_copy, column);
@@ -386,33 +470,110 @@ __global__ void __launch_bounds__(kStagedThreads)
 }
 
 /* ---- elementwise kernels -------------------------------------------------------
- * Each works on 16-byte vectors (eight BF16 or four FP32 per thread and step)
- * over the leading `vectors * kLanes` elements and finishes the remaining
- * elements one by one; the host passes vectors = 0 when a pointer is not
- * 16-byte aligned. Outputs may be one of the inputs (each thread reads its
- * vector before it writes it). `width`-dependent kernels are vectorised only when width is a
- * multiple of the vector length, so that a vector never crosses a row. */
+ * Each works on 16-byte vectors (eight BF16 or four FP32) over the leading
+ * `vectors * kLanes` elements and finishes the remaining elements one by one;
+ * the host passes vectors = 0 when a pointer is not 16-byte aligned. A thread
+ * takes kBatch vectors per step, a grid stride apart, and loads all of their
+ * operands before it computes and stores any of them, so that several memory
+ * requests per thread are in flight whatever the compiler can prove about
+ * aliasing. Outputs may be one of the inputs: a thread reads its vectors
+ * before it writes those same vectors. `width`-dependent kernels are
+ * vectorised only when width is a multiple of the vector length, so that a
+ * vector never crosses a row. SiLU costs an exponential and an IEEE division
+ * per element in the reference's expression, which is kept so that the bits
+ * agree; on B200 that arithmetic is within a factor of two of the memory time,
+ * so these kernels do not reach the copy bandwidth. */
+constexpr int kBatch = 4;
 
 /* output[i] = input[i]^2 in FP32 (the per-element squares the multi-kernel RMS
  * path of the reference averages, backend.cu:1442-1454). */
 __global__ void __launch_bounds__(256)
-    square_kernel(size_t count, size_t vectors, const __nv_bfloat16 *input,
-                  float *output)
+    square_kernel(size_t count, size_t vectors, const __nv_bfloat16 *input, float *output)
 {
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (size_t vector = first; vector < vectors; vector += stride) {
-        float v[8];
-        Storage<__nv_bfloat16>::load16(input, vector * 8, v);
-        float4 *target = reinterpret_cast<float4 *>(output + vector * 8);
-        target[0] = make_float4(__fmul_rn(v[0], v[0]), __fmul_rn(v[1], v[1]), __fmul_rn(v[2], v[2]),
-                                __fmul_rn(v[3], v[3]));
-        target[1] = make_float4(__fmul_rn(v[4], v[4]), __fmul_rn(v[5], v[5]), __fmul_rn(v[6], v[6]),
-                                __fmul_rn(v[7], v[7]));
+    for (size_t vector = first; vector < vectors; vector += kBatch * stride) {
+        uint4 raw[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+            if (vector + b * stride < vectors)
+                raw[b] = *reinterpret_cast<const uint4 *>(input + (vector + b * stride) * 8);
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+            if (vector + b * stride < vectors) {
+                const uint32_t words[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
+                float v[8];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    v[2 * w] = Storage<__nv_bfloat16>::low(words[w]);
+                    v[2 * w + 1] = Storage<__nv_bfloat16>::high(words[w]);
+                }
+                float4 *target = reinterpret_cast<float4 *>(output + (vector + b * stride) * 8);
+                target[0] = make_float4(__fmul_rn(v[0], v[0]), __fmul_rn(v[1], v[1]),
+                                        __fmul_rn(v[2], v[2]), __fmul_rn(v[3], v[3]));
+                target[1] = make_float4(__fmul_rn(v[4], v[4]), __fmul_rn(v[5], v[5]),
+                                        __fmul_rn(v[6], v[6]), __fmul_rn(v[7], v[7]));
+            }
     }
     for (size_t i = vectors * 8 + first; i < count; i += stride) {
         const float value = __bfloat162float(input[i]);
         output[i] = __fmul_rn(value, value);
+    }
+}
+
+/* Sixteen bytes of T as FP32 values and back. */
+template <typename T> __device__ __forceinline__ void unpack16(uint4 raw, float (&v)[Storage<T>::kLanes]);
+template <> __device__ __forceinline__ void unpack16<float>(uint4 raw, float (&v)[4])
+{
+    v[0] = __uint_as_float(raw.x), v[1] = __uint_as_float(raw.y);
+    v[2] = __uint_as_float(raw.z), v[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(uint4 raw, float (&v)[8])
+{
+    using S = Storage<__nv_bfloat16>;
+    v[0] = S::low(raw.x), v[1] = S::high(raw.x), v[2] = S::low(raw.y), v[3] = S::high(raw.y);
+    v[4] = S::low(raw.z), v[5] = S::high(raw.z), v[6] = S::low(raw.w), v[7] = S::high(raw.w);
+}
+template <typename T> __device__ __forceinline__ uint4 pack16(const float (&v)[Storage<T>::kLanes]);
+template <> __device__ __forceinline__ uint4 pack16<float>(const float (&v)[4])
+{
+    return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
+                      __float_as_uint(v[3]));
+}
+template <> __device__ __forceinline__ uint4 pack16<__nv_bfloat16>(const float (&v)[8])
+{
+    using S = Storage<__nv_bfloat16>;
+    return make_uint4(S::pack(v[0], v[1]), S::pack(v[2], v[3]), S::pack(v[4], v[5]),
+                      S::pack(v[6], v[7]));
+}
+
+/* The batched loop shared by the two-operand kernels: for every vector of this
+ * thread, element(a, b, index of the vector's first element) -> result values
+ * written over a. */
+template <typename T, typename Element>
+__device__ __forceinline__ void for_each_vector(size_t vectors, const T *left, const T *right,
+                                                T *output, Element element)
+{
+    constexpr int kLanes = Storage<T>::kLanes;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (size_t vector = first; vector < vectors; vector += kBatch * stride) {
+        uint4 a[kBatch], b[kBatch];
+#pragma unroll
+        for (int s = 0; s < kBatch; ++s)
+            if (vector + s * stride < vectors) {
+                a[s] = *reinterpret_cast<const uint4 *>(left + (vector + s * stride) * kLanes);
+                b[s] = *reinterpret_cast<const uint4 *>(right + (vector + s * stride) * kLanes);
+            }
+#pragma unroll
+        for (int s = 0; s < kBatch; ++s)
+            if (vector + s * stride < vectors) {
+                float x[kLanes], y[kLanes];
+                unpack16<T>(a[s], x);
+                unpack16<T>(b[s], y);
+                element(x, y, (vector + s * stride) * kLanes);
+                *reinterpret_cast<uint4 *>(output + (vector + s * stride) * kLanes) = pack16<T>(x);
+            }
     }
 }
 
@@ -421,27 +582,39 @@ __global__ void __launch_bounds__(256)
 template <typename T>
 __global__ void __launch_bounds__(256)
     scale_kernel(size_t count, size_t vectors, int width, float epsilon, const T *input,
-                 const T *weight, const float *means,
-                 T *output)
+                 const T *weight, const float *means, T *output)
 {
     constexpr int kLanes = Storage<T>::kLanes;
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (size_t vector = first; vector < vectors; vector += stride) {
-        const size_t i = vector * kLanes;
-        const size_t row = i / width;
-        const float scale = rsqrtf(__fadd_rn(means[row], epsilon));
-        float v[kLanes], g[kLanes];
-        Storage<T>::load16(input, i, v);
-        Storage<T>::load16(weight, i - row * width, g);
+    for (size_t vector = first; vector < vectors; vector += kBatch * stride) {
+        uint4 a[kBatch], b[kBatch];
+        float scale[kBatch];
 #pragma unroll
-        for (int o = 0; o < kLanes; ++o)
-            v[o] = __fmul_rn(Storage<T>::round(__fmul_rn(v[o], scale)), g[o]);
-        Storage<T>::store16(output, i, v);
+        for (int s = 0; s < kBatch; ++s)
+            if (vector + s * stride < vectors) {
+                const size_t i = (vector + s * stride) * kLanes;
+                const size_t row = i / width;
+                a[s] = *reinterpret_cast<const uint4 *>(input + i);
+                b[s] = *reinterpret_cast<const uint4 *>(weight + (i - row * width));
+                scale[s] = means[row];
+            }
+#pragma unroll
+        for (int s = 0; s < kBatch; ++s)
+            if (vector + s * stride < vectors) {
+                float v[kLanes], g[kLanes];
+                unpack16<T>(a[s], v);
+                unpack16<T>(b[s], g);
+                const float factor = rsqrtf(__fadd_rn(scale[s], epsilon));
+#pragma unroll
+                for (int o = 0; o < kLanes; ++o)
+                    v[o] = __fmul_rn(Storage<T>::round(__fmul_rn(v[o], factor)), g[o]);
+                *reinterpret_cast<uint4 *>(output + (vector + s * stride) * kLanes) = pack16<T>(v);
+            }
     }
     for (size_t i = vectors * kLanes + first; i < count; i += stride) {
-        const float scale = rsqrtf(__fadd_rn(means[i / width], epsilon));
-        const float normalised = Storage<T>::round(__fmul_rn(Storage<T>::load(input, i), scale));
+        const float factor = rsqrtf(__fadd_rn(means[i / width], epsilon));
+        const float normalised = Storage<T>::round(__fmul_rn(Storage<T>::load(input, i), factor));
         Storage<T>::store(output, i, __fmul_rn(normalised, Storage<T>::load(weight, i % width)));
     }
 }
@@ -455,21 +628,17 @@ __device__ __forceinline__ float silu(float g)
 /* output = rnd(rnd(SiLU(gate)) * up). */
 template <typename T>
 __global__ void __launch_bounds__(256)
-    silu_multiply_kernel(size_t count, size_t vectors, const T *gate,
-                         const T *up, T *output)
+    silu_multiply_kernel(size_t count, size_t vectors, const T *gate, const T *up, T *output)
 {
     constexpr int kLanes = Storage<T>::kLanes;
+    for_each_vector<T>(vectors, gate, up, output,
+                       [](float (&g)[kLanes], const float (&u)[kLanes], size_t) {
+#pragma unroll
+                           for (int o = 0; o < kLanes; ++o)
+                               g[o] = Storage<T>::round(silu(g[o])) * u[o];
+                       });
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (size_t vector = first; vector < vectors; vector += stride) {
-        float g[kLanes], u[kLanes];
-        Storage<T>::load16(gate, vector * kLanes, g);
-        Storage<T>::load16(up, vector * kLanes, u);
-#pragma unroll
-        for (int o = 0; o < kLanes; ++o)
-            g[o] = Storage<T>::round(silu(g[o])) * u[o];
-        Storage<T>::store16(output, vector * kLanes, g);
-    }
     for (size_t i = vectors * kLanes + first; i < count; i += stride) {
         const float activated = Storage<T>::round(silu(Storage<T>::load(gate, i)));
         Storage<T>::store(output, i, activated * Storage<T>::load(up, i));
@@ -496,25 +665,20 @@ __device__ __forceinline__ float swiglu_element(float g, float u, float limit, b
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-    swiglu_kernel(size_t count, size_t vectors, int width, float limit, const T *gate,
-                  const T *up, const float *routing,
-                  T *output)
+    swiglu_kernel(size_t count, size_t vectors, int width, float limit, const T *gate, const T *up,
+                  const float *routing, T *output)
 {
     constexpr int kLanes = Storage<T>::kLanes;
+    const bool routed = routing != nullptr;
+    for_each_vector<T>(vectors, gate, up, output,
+                       [&](float (&g)[kLanes], const float (&u)[kLanes], size_t index) {
+                           const float factor = routed ? routing[index / width] : 1.f;
+#pragma unroll
+                           for (int o = 0; o < kLanes; ++o)
+                               g[o] = swiglu_element(g[o], u[o], limit, routed, factor);
+                       });
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    const bool routed = routing != nullptr;
-    for (size_t vector = first; vector < vectors; vector += stride) {
-        const size_t i = vector * kLanes;
-        const float factor = routed ? routing[i / width] : 1.f;
-        float g[kLanes], u[kLanes];
-        Storage<T>::load16(gate, i, g);
-        Storage<T>::load16(up, i, u);
-#pragma unroll
-        for (int o = 0; o < kLanes; ++o)
-            g[o] = swiglu_element(g[o], u[o], limit, routed, factor);
-        Storage<T>::store16(output, i, g);
-    }
     for (size_t i = vectors * kLanes + first; i < count; i += stride)
         Storage<T>::store(output, i,
                           swiglu_element(Storage<T>::load(gate, i), Storage<T>::load(up, i), limit,
