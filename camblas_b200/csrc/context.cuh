@@ -37,6 +37,8 @@ struct ContextOptions {
                               row-parallel product, 0 = by shape */
     int fp8_rows = 0;      /* "fp8_rows" (CAMBLAS_B200_FP8_ROWS=four|single): 1, 2 select the older
                               many-row FP8 kernels, which give the same bits */
+    int fp8_swapped_rows = 128; /* "fp8_swapped_rows": most token rows the weight-streaming
+                                   (swapped, split-K) FP8 modes take, 64 or 128 */
     int bf16_strassen = 0; /* "bf16_strassen" (CAMBLAS_B200_BF16_STRASSEN=1): let policy STRASSEN
                               run one Strassen level on BF16 squares */
     int peer_wait_ms = 5000; /* "peer_wait_ms": how long a kernel waits for another GPU's flag */

@@ -96,11 +96,20 @@ struct BlockTask {
 constexpr int kBlockDepth = 128; /* bytes = E4M3 elements per stage row */
 constexpr int kSwappedRowLimit = 128; /* most token rows the swapped (weight-streaming) modes take */
 
+/* Swapped modes: every epilogue warp keeps the scale products a_scale * w_scale
+ * of the next kScaleChunk K blocks for the BN token columns of its tile in a
+ * table of its own ([block][column], rows padded by one float so that the
+ * fill is free of bank conflicts). Fetching them block by block put an L2 round
+ * trip (about a microsecond) in front of every 128-deep K block, which is all a
+ * few-token tile costs otherwise. */
+constexpr int kScaleChunk = 16;
+
 /* Dynamic shared memory of fp8_block_gemm: the BF16 kernel's layout plus, in the
- * swapped modes, BN scale products for each of the four epilogue warps. */
+ * swapped modes, the scale tables of the four epilogue warps. */
 template <int BN, int Stages, int Mode> constexpr int block_smem_bytes()
 {
-    return GemmSmem<BN, Stages, Mode>::kTotal + (Mode == kStoreRows ? 0 : 4 * BN * 4);
+    return GemmSmem<BN, Stages, Mode>::kTotal + 256 +
+           (Mode == kStoreRows ? 0 : 4 * kScaleChunk * (BN + 1) * 4);
 }
 
 template <int BN, int Stages, int Mode>
@@ -111,7 +120,14 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
 {
     using namespace sm100;
     using Layout = GemmSmem<BN, Stages, Mode>; /* 128 B rows: same byte layout as BF16 x 64 */
-    constexpr uint32_t kTmemColumns = BN * 2 < 32 ? 32 : BN * 2;
+    /* Accumulator buffers in tensor memory, one per K block in flight. The swapped
+     * modes have narrow tiles and take eight, so that the MMA issuer runs up to
+     * seven K blocks ahead of the promotion warps: with two, every 128-deep block
+     * paid a round trip MMA -> barrier -> promotion warp -> barrier -> MMA, about a
+     * microsecond for a multiplication of a few hundred cycles. */
+    constexpr int kBuffers = Mode == kStoreRows ? 2 : 8;
+    constexpr uint32_t kTmemColumns = BN * kBuffers < 32 ? 32 : BN * kBuffers;
+    static_assert(kTmemColumns <= 512 && (kTmemColumns & (kTmemColumns - 1)) == 0, "TMEM size");
     static_assert(Mode != kStoreRows || BN == 128, "row store: one 128-column weight band per tile");
 
     extern __shared__ uint8_t raw_smem[];
@@ -121,12 +137,13 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
     uint64_t *full = reinterpret_cast<uint64_t *>(staging + Layout::kStaging);
     uint64_t *empty = full + Stages;
     uint64_t *tmem_full = empty + Stages;
-    uint64_t *tmem_empty = tmem_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    uint64_t *tmem_empty = tmem_full + kBuffers;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + kBuffers);
     volatile uint32_t *abort = tmem_slot + 1;
-    /* swapped modes: the token-side scale products of the K block in flight, BN
-     * floats per epilogue warp, behind the 256-byte barrier area */
-    float *scale_area = reinterpret_cast<float *>(full) + 64;
+    static_assert((2 * Stages + 2 * kBuffers + 1) * 8 <= 512, "barrier area");
+    /* swapped modes: the scale tables of the epilogue warps, behind the barrier area
+     * (512 bytes: the 256 of the BF16 layout plus 256 counted in block_smem_bytes) */
+    float *scale_area = reinterpret_cast<float *>(full) + 128;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = task.r_blocks * task.c_blocks * task.split;
@@ -137,7 +154,7 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kBuffers; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 4);
         }
@@ -216,7 +233,7 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                 int kb0 = part * task.k_blocks_per_split;
                 int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
                 for (int kb = kb0; kb < kb1; ++kb, ++block) {
-                    uint32_t buffer = block & 1, use = block >> 1;
+                    uint32_t buffer = block % kBuffers, use = block / kBuffers;
                     if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
                         report(task.status, abort, kRoleMmaTmemEmpty);
                         ok = false;
@@ -266,22 +283,47 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                 lane_scale = task.p_scale + static_cast<long long>(min(row, task.rows - 1)) * groups;
             else
                 lane_scale = task.p_scale + static_cast<long long>(rb) * groups;
+            float *const table = scale_area + (warp - 2) * kScaleChunk * (BN + 1);
             for (int kb = kb0; kb < kb1; ++kb, ++block) {
-                const uint32_t buffer = block & 1, use = block >> 1;
-                const float own = lane_scale[kb];
-                float band = 1.f;
-                if (Mode == kStoreRows)
+                const uint32_t buffer = block % kBuffers, use = block / kBuffers;
+                float own = 0.f, band = 1.f;
+                if (Mode == kStoreRows) {
+                    own = lane_scale[kb];
                     band = task.q_scale[static_cast<long long>(cb) * groups + kb];
-                float *column_scale = scale_area + (warp - 2) * BN;
-                if (Mode != kStoreRows) {
-                    __syncwarp(); /* every lane is done with the previous block's products */
-                    for (int i = lane; i < BN; i += 32) {
-                        const int c = min(col0 + i, task.cols - 1);
-                        column_scale[i] =
-                            __fmul_rn(task.q_scale[static_cast<long long>(c) * groups + kb], own);
+                }
+                const int slot = (kb - kb0) % kScaleChunk;
+                if (Mode != kStoreRows && slot == 0) {
+                    /* Refill this warp's table with the products for blocks kb .. kb+count-1.
+                     * Element e of the chunk is (column e / 16, block e % 16), so that
+                     * neighbouring lanes fetch neighbouring floats of one scale row. A
+                     * lane has sixteen loads in flight before it uses the first: issued one
+                     * by one, each refill paid an L2 round trip per element. */
+                    __syncwarp(); /* every lane is done with the previous chunk */
+                    const int count = min(kScaleChunk, kb1 - kb);
+                    constexpr int kInFlight = 16;
+                    static_assert(kScaleChunk == 16, "element index split by shifts");
+                    for (int e0 = lane; e0 < kScaleChunk * BN; e0 += 32 * kInFlight) {
+                        float token_side[kInFlight], weight_side[kInFlight];
+#pragma unroll
+                        for (int u = 0; u < kInFlight; ++u) {
+                            const int e = e0 + u * 32, i = e >> 4, j = e & 15;
+                            if (e < kScaleChunk * BN && j < count) {
+                                const int c = min(col0 + i, task.cols - 1);
+                                token_side[u] =
+                                    task.q_scale[static_cast<long long>(c) * groups + kb + j];
+                                weight_side[u] = lane_scale[kb + j];
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kInFlight; ++u) {
+                            const int e = e0 + u * 32, i = e >> 4, j = e & 15;
+                            if (e < kScaleChunk * BN && j < count)
+                                table[j * (BN + 1) + i] = __fmul_rn(token_side[u], weight_side[u]);
+                        }
                     }
                     __syncwarp();
                 }
+                const float *column_scale = table + slot * (BN + 1);
                 if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
                     report(task.status, abort, kRoleEpilogueFull);
                     ok = false;
@@ -795,7 +837,7 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
      * 128 x 128 row tiling would leave most SMs idle (32 tiles for N = 4096): those
      * shapes take the swapped kernel, one or two 64-token column blocks per weight
      * band with the K range split over the SMs. */
-    if (rows > kSwappedRowLimit) {
+    if (rows > std::min(kSwappedRowLimit, context->options.fp8_swapped_rows)) {
         task.rows = rows, task.cols = outputs;
         task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;
         task.split = 1, task.k_blocks_per_split = task.k_blocks;

@@ -340,6 +340,9 @@ int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *
  *                    product (CAMBLAS_B200_PUSH_WIDTH)
  *   "fp8_rows"       0 current, 1 four-warp, 2 one-block-per-stage FP8 row
  *                    kernel; same bits (CAMBLAS_B200_FP8_ROWS=four|single)
+ *   "fp8_swapped_rows" 64..128: most token rows for which the FP8 block GEMM
+ *                    streams the weights with the K range split over the SMs
+ *                    instead of tiling the rows (default 128)
  *   "bf16_strassen"  1 lets policy STRASSEN run one Strassen level on BF16
  *                    squares (CAMBLAS_B200_BF16_STRASSEN)
  *   "peer_wait_ms"   1..60000, how long a kernel of the row-parallel layer waits
