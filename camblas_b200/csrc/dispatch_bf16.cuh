@@ -187,6 +187,31 @@ inline int choose_split(int tiles, int k_blocks, int sms)
     return best;
 }
 
+/* Whether a K split pays at all. The split buys a better fill of the SMs and
+ * costs a second launch plus a write and a read of `split` FP32 copies of the
+ * result. Rough microseconds for a weight-streaming tile of 128 rows by `bn`
+ * token columns whose K blocks are 128 bytes deep: a CTA alone takes about
+ * 0.19 us per block; with every SM streaming, HBM (6.5 TB/s) allows one block
+ * per SM every 148 * bytes / 6.5 MB us. When the tiles alone already give
+ * most SMs work (N = 24576: 192 tiles), not splitting wins even though the fill
+ * is worse: measured 17 against 31 us for 64 tokens. */
+inline int split_if_it_pays(int split, int tiles, int k_blocks, int sms, int tokens, int outputs,
+                            int bn)
+{
+    if (split <= 1)
+        return 1;
+    const double step_bytes = 128.0 * 128 + 128.0 * bn;
+    auto main_us = [&](int parts) {
+        const long long units = 1ll * tiles * parts;
+        const double waves = double((units + sms - 1) / sms);
+        const double busy = double(units < sms ? units : sms);
+        const double step = std::max(0.19, busy * step_bytes / 6.5e6);
+        return waves * ((k_blocks + parts - 1) / parts) * step;
+    };
+    const double reduce_us = 3.0 + 2.0 * split * double(tokens) * outputs * 4 / 3.0e6;
+    return main_us(1) <= main_us(split) + reduce_us ? 1 : split;
+}
+
 inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
 {
     sm100::GemmTask task{};
@@ -531,6 +556,8 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     task.c_blocks = (x.n + bn - 1) / bn;
     task.k_blocks = (x.k + 63) / 64;
     task.split = choose_split(task.r_blocks * task.c_blocks, task.k_blocks, context->sm_count);
+    task.split = split_if_it_pays(task.split, task.r_blocks * task.c_blocks, task.k_blocks,
+                                  context->sm_count, x.n, x.m, bn);
     task.k_blocks_per_split = (task.k_blocks + task.split - 1) / task.split;
     task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
@@ -566,11 +593,13 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
         int status = launched(context, "tcgen05 split-K BF16 GEMM");
         if (status != 0)
             return status;
-        dim3 grid((x.m + 255) / 256, x.n);
-        sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(
-            x.m, x.n, task.split, plane, x.alpha, x.beta, task.partial, x.addend, x.ld_add, x.bias,
-            x.c, x.ldc);
-        return launched(context, "split-K reduction");
+        cudaError_t error = sm100::launch_split_reduce(context->stream, x.m, x.n, task.split, plane,
+                                                       x.alpha, x.beta, task.partial, x.addend,
+                                                       x.ld_add, x.bias, x.c, x.ldc);
+        if (error != cudaSuccess)
+            return fail(context, "split-K reduction", error);
+        context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        return 0;
     }
     if (bn == 16)
         launch_tensor<16, 8, sm100::kStoreColumns>(context, p, q, p, p, p, task);

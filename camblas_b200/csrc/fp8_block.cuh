@@ -148,6 +148,11 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = task.r_blocks * task.c_blocks * task.split;
     const int groups = task.k_blocks;
+    if constexpr (Mode == kStorePartial) {
+        /* the reduction that follows may become resident now; it waits for this
+         * grid's completion itself (griddepcontrol.wait) */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Stages; ++s) {
@@ -872,6 +877,8 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
     task.c_blocks = (rows + bn - 1) / bn;
     task.split = host::choose_split(task.r_blocks * task.c_blocks, task.k_blocks * 2,
                                     context->sm_count);
+    task.split = host::split_if_it_pays(task.split, task.r_blocks * task.c_blocks, task.k_blocks,
+                                        context->sm_count, rows, outputs, bn);
     task.k_blocks_per_split = (task.k_blocks + task.split - 1) / task.split;
     task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
@@ -897,11 +904,13 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
         int status = host::launched(context, "tcgen05 FP8 split-K block GEMM");
         if (status != 0)
             return status;
-        dim3 grid((outputs + 255) / 256, rows);
-        sm100::gemm_split_reduce<<<grid, 256, 0, context->stream>>>(
-            outputs, rows, task.split, plane, 1.f, 0.f, task.partial, nullptr, 0, nullptr,
-            task.out, ldo);
-        return host::launched(context, "FP8 split-K reduction");
+        cudaError_t error = sm100::launch_split_reduce(context->stream, outputs, rows, task.split,
+                                                       plane, 1.f, 0.f, task.partial, nullptr, 0,
+                                                       nullptr, task.out, ldo);
+        if (error != cudaSuccess)
+            return host::fail(context, "FP8 split-K reduction", error);
+        context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        return 0;
     }
     if (bn == 16)
         launch_block<16, 8, kStoreColumns>(context, p, qm, p, task);

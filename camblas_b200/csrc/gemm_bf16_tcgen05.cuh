@@ -719,6 +719,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if constexpr (Mode == kStorePartial) {
+        /* the reduction that follows may become resident now; it waits for this
+         * grid's completion itself (griddepcontrol.wait) */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     if (task.skip_if_set != nullptr && *task.skip_if_set != 0)
         return;
     if (task.run_if_set != nullptr && *task.run_if_set == 0)
@@ -994,25 +999,63 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 /* Ordered reduction of the K splits written by kStorePartial:
- * out[c*ld_out + r] = rnd(alpha * sum_s partial[s][c][r] + beta*addend + bias[r]). */
-__global__ void gemm_split_reduce(int rows, int cols, int split, long long plane, float alpha,
-                                  float beta, const float *partial, const __nv_bfloat16 *addend,
-                                  long long ld_add, const __nv_bfloat16 *bias, __nv_bfloat16 *out,
-                                  long long ld_out)
+ * out[c*ld_out + r] = rnd(alpha * sum_s partial[s][c][r] + beta*addend + bias[r]).
+ * Launched as a programmatic dependent of the product kernel (which releases
+ * its dependents when it starts), so that this grid is already resident when the
+ * product ends and only the wait below separates them; the loads of eight
+ * splits are in flight at a time and are added in ascending split order. */
+__global__ void __launch_bounds__(256)
+    gemm_split_reduce(int rows, int cols, int split, long long plane, float alpha, float beta,
+                      const float *partial, const __nv_bfloat16 *addend, long long ld_add,
+                      const __nv_bfloat16 *bias, __nv_bfloat16 *out, long long ld_out)
 {
-    int r = blockIdx.x * blockDim.x + threadIdx.x;
-    int c = blockIdx.y;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = blockIdx.y;
     if (r >= rows)
         return;
+    const float *source = partial + static_cast<long long>(c) * plane + r;
+    const long long step = static_cast<long long>(cols) * plane;
     float sum = 0.f;
-    for (int s = 0; s < split; ++s)
-        sum += partial[(static_cast<long long>(s) * cols + c) * plane + r];
+    int s = 0;
+    for (; s + 8 <= split; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v[i] = __ldcg(source + (s + i) * step);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            sum += v[i];
+    }
+    for (; s < split; ++s)
+        sum += __ldcg(source + s * step);
     float v = alpha * sum;
     if (bias != nullptr)
         v += __bfloat162float(bias[r]);
     if (beta != 0.f)
         v = fmaf(beta, __bfloat162float(addend[c * ld_add + r]), v);
     out[c * ld_out + r] = __float2bfloat16_rn(v);
+}
+
+/* Launch gemm_split_reduce behind a product kernel on `stream` with programmatic
+ * stream serialization. */
+inline cudaError_t launch_split_reduce(cudaStream_t stream, int rows, int cols, int split,
+                                       long long plane, float alpha, float beta,
+                                       const float *partial, const __nv_bfloat16 *addend,
+                                       long long ld_add, const __nv_bfloat16 *bias,
+                                       __nv_bfloat16 *out, long long ld_out)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((rows + 255) / 256, cols);
+    config.blockDim = dim3(256);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, gemm_split_reduce, rows, cols, split, plane, alpha, beta,
+                              partial, addend, ld_add, bias, out, ld_out);
 }
 
 /* Second pass of the stream-K tail: add the pieces of every stream-K tile in

@@ -17,11 +17,14 @@
  *      owner's arrival word for it. Tiles leave as they finish, so the
  *      transfer of early tiles overlaps the multiplication of later ones.
  *   2. peer_reduce_broadcast, launched as a programmatic dependent so that it
- *      is resident before the product ends: on the owner, one CTA per slab
- *      waits (bounded) until all `world` partial slabs are there, clears the
- *      word, adds the partials in rank order in FP32, adds bias and residual,
- *      rounds once and writes the finished slab into the result buffer of
- *      EVERY GPU, then adds one to each GPU's delivery counter.
+ *      is resident before the product ends: on the owner, one CTA per 64-column
+ *      piece of a slab (256 CTAs per GPU for the benchmark's down projection at
+ *      eight ranks, so that every SM issues loads and peer stores) waits
+ *      (bounded) until all `world` partial slabs are there, adds the partials in
+ *      rank order in FP32, adds bias and residual, rounds once and writes its
+ *      piece into the result buffer of EVERY GPU; the last CTA to have read a
+ *      slab clears its arrival word; then each adds one to every GPU's
+ *      delivery counter.
  *   3. the wait (bounded) until this GPU's delivery counter has reached the
  *      number of slabs of the whole matrix: done by the CTA of launch 2 that
  *      finishes last, or by the small kernel peer_wait_delivered when the
@@ -67,9 +70,10 @@ namespace peer
 
 constexpr int kMaxWorld = 8;
 constexpr int kFlagWords = 65536; /* word 0: delivery counter; word 1: CTAs of the reduction
-                                     done; words 64..: arrival words */
+                                     done; words 64..: one arrival word per slab, then one
+                                     word per slab counting the CTAs that have read it */
 constexpr int kFlagHeader = 64;
-constexpr int kMaxUnits = kFlagWords - kFlagHeader;
+constexpr int kMaxUnits = (kFlagWords - kFlagHeader) / 2;
 
 inline size_t slot_bytes(size_t capacity)
 {
@@ -135,83 +139,81 @@ __device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned exp
         atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
 }
 
-/* grid = (column blocks this GPU owns, 8 * r_blocks); 256 threads. Each CTA
- * finishes one 32-row slab of one owned tile: it waits for the slab's `world`
- * partial copies (staging layout: see sm100::epilogue_push), adds them in rank
- * order, applies bias and residual, rounds once and writes the slab, now as
- * ordinary matrix rows (a warp stores 512 contiguous bytes of one row), into
- * every GPU's result. With `wait_inline` the CTA that finishes last also waits
- * for the deliveries to this GPU, which saves the launch of peer_wait_delivered. */
+/* grid = (column blocks this GPU owns, 8 * r_blocks, width / 64); 256 threads.
+ * Each CTA finishes 64 columns of one 32-row slab of one owned tile - in the
+ * staging layout (see sm100::epilogue_push) that is one contiguous 4 KB chunk
+ * per rank: it waits for the slab's `world` partial copies, adds them in rank
+ * order (one 16-byte piece per thread, all ranks' loads in flight together),
+ * applies bias and residual, rounds once and writes the piece, now as ordinary
+ * matrix rows (eight threads store 128 contiguous bytes of a row), into every
+ * GPU's result. The CTAs of a slab count themselves on the slab's second flag
+ * word; the last one clears both words, before any of its deliveries is
+ * announced, so the next call finds them zero. With `wait_inline` the CTA that
+ * finishes last also waits for the deliveries to this GPU, which saves the
+ * launch of peer_wait_delivered. */
 __global__ void __launch_bounds__(256)
     peer_reduce_broadcast(const ReduceTask task, unsigned expected, int wait_inline)
 {
     __shared__ int failed;
     const int cb = task.rank + blockIdx.x * task.world;
     const int rb = blockIdx.y >> 3, slab = blockIdx.y & 7;
+    const int chunk = blockIdx.z, chunks = gridDim.z;
     const int unit = (rb * task.c_blocks + cb) * 8 + slab;
+    unsigned *const arrived = task.arrive + unit;
+    unsigned *const readers = task.arrive + kMaxUnits + unit;
     if (threadIdx.x == 0) {
-        unsigned *word = task.arrive + unit;
-        const bool ok = sm100::flag_wait_system(word, unsigned(task.world), task.wait_ns);
-        if (ok)
-            sm100::flag_store_relaxed_system(word, 0u);
-        else
+        const bool ok = sm100::flag_wait_system(arrived, unsigned(task.world), task.wait_ns);
+        if (!ok)
             atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
         failed = ok ? 0 : 1;
     }
     __syncthreads();
     if (!failed) {
-        const int row0 = rb * 256 + slab * 32;
-        const int pieces_per_row = task.width >> 3; /* 16-byte pieces in a slab row: 32 or 16 */
-        const int rows_per_step = 256 / pieces_per_row;
-        const int steps = 32 / rows_per_step;
-        const int piece = threadIdx.x % pieces_per_row;
-        const long long unit_offset = static_cast<long long>(unit) * (32 * task.width);
-        /* two steps at a time: up to sixteen 16-byte loads in flight per thread */
-#pragma unroll 1
-        for (int step = 0; step < steps; step += 2) {
-            uint4 part[2][kMaxWorld];
+        const int r = threadIdx.x >> 3, piece = threadIdx.x & 7;
+        const int row = rb * 256 + slab * 32 + r, c = cb * task.width + chunk * 64 + piece * 8;
+        const long long offset = static_cast<long long>(unit) * (32 * task.width) + chunk * 2048 +
+                                 r * 64 + ((piece ^ (r & 7)) << 3);
+        uint4 part[kMaxWorld];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int r = (step + half) * rows_per_step + threadIdx.x / pieces_per_row;
-                const long long offset =
-                    unit_offset + (piece >> 3) * 2048 + r * 64 + (((piece & 7) ^ (r & 7)) << 3);
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (s < task.world)
+                part[s] = __ldcg(
+                    reinterpret_cast<const uint4 *>(task.staging + s * task.slot_elements + offset));
+        if (row < task.rows && c < task.cols) {
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int s = 0; s < kMaxWorld; ++s)
-                    if (s < task.world)
-                        part[half][s] = __ldcg(reinterpret_cast<const uint4 *>(
-                            task.staging + s * task.slot_elements + offset));
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < task.world)
+                    accumulate8(sum, part[s]);
+            if (task.bias != nullptr)
+                accumulate8(sum, *reinterpret_cast<const uint4 *>(task.bias + c));
+            if (task.residual != nullptr)
+                accumulate8(sum, *reinterpret_cast<const uint4 *>(
+                                     task.residual + static_cast<long long>(row) * task.ld_residual +
+                                     c));
+            uint4 packed;
+            packed.x = sm100::pack_bf16(sum[0], sum[1]);
+            packed.y = sm100::pack_bf16(sum[2], sum[3]);
+            packed.z = sm100::pack_bf16(sum[4], sum[5]);
+            packed.w = sm100::pack_bf16(sum[6], sum[7]);
+            const long long target_offset = static_cast<long long>(row) * task.cols + c;
+            /* start with the next GPU so that the owners do not all write to the same one */
+            for (int hop = 1; hop <= task.world; ++hop) {
+                int target = task.rank + hop;
+                if (target >= task.world)
+                    target -= task.world;
+                *reinterpret_cast<uint4 *>(task.result[target] + target_offset) = packed;
             }
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int r = (step + half) * rows_per_step + threadIdx.x / pieces_per_row;
-                const int row = row0 + r, c = cb * task.width + piece * 8;
-                if (row >= task.rows || c >= task.cols)
-                    continue;
-                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int s = 0; s < kMaxWorld; ++s)
-                    if (s < task.world)
-                        accumulate8(sum, part[half][s]);
-                if (task.bias != nullptr)
-                    accumulate8(sum, *reinterpret_cast<const uint4 *>(task.bias + c));
-                if (task.residual != nullptr)
-                    accumulate8(sum, *reinterpret_cast<const uint4 *>(
-                                         task.residual +
-                                         static_cast<long long>(row) * task.ld_residual + c));
-                uint4 packed;
-                packed.x = sm100::pack_bf16(sum[0], sum[1]);
-                packed.y = sm100::pack_bf16(sum[2], sum[3]);
-                packed.z = sm100::pack_bf16(sum[4], sum[5]);
-                packed.w = sm100::pack_bf16(sum[6], sum[7]);
-                const long long target_offset = static_cast<long long>(row) * task.cols + c;
-                /* start with the next GPU so that the owners do not all write to the same one */
-                for (int hop = 1; hop <= task.world; ++hop) {
-                    int target = task.rank + hop;
-                    if (target >= task.world)
-                        target -= task.world;
-                    *reinterpret_cast<uint4 *>(task.result[target] + target_offset) = packed;
-                }
-            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (!failed && threadIdx.x == 0) {
+        /* the partials of this slab have been read by this CTA; the last reader
+         * hands the two words back as zeros */
+        if (atomicAdd(readers, 1u) == unsigned(chunks) - 1u) {
+            sm100::flag_store_relaxed_system(readers, 0u);
+            sm100::flag_store_relaxed_system(arrived, 0u);
         }
         __threadfence_system();
     }
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(256)
         /* word 1 of this GPU's flags counts the CTAs of this launch that are done */
         unsigned *ticket = task.delivered[task.rank] + 1;
         const unsigned done = atomicAdd(ticket, 1u);
-        if (done == gridDim.x * gridDim.y - 1) {
+        if (done == gridDim.x * gridDim.y * gridDim.z - 1) {
             *ticket = 0;
             wait_delivered(task.delivered[task.rank], expected, task.status, task.wait_ns);
         }
@@ -342,7 +344,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
              * may become resident while that kernel still runs (it says so at its
              * start) and wait on the arrival words, not on the kernel boundary. */
             cudaLaunchConfig_t config = {};
-            config.gridDim = dim3(owned, 8 * r_blocks);
+            config.gridDim = dim3(owned, 8 * r_blocks, bn / 64);
             config.blockDim = dim3(256);
             config.stream = context->stream;
             cudaLaunchAttribute attribute[1];
@@ -352,7 +354,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
             config.numAttrs = 1;
             wait_inline = (call.phases & 4) != 0;
             cudaError_t error = cudaLaunchKernelEx(&config, peer_reduce_broadcast, task,
-                                                   unsigned(units), int(wait_inline));
+                                                   unsigned(units * (bn / 64)), int(wait_inline));
             if (error != cudaSuccess)
                 return fail(context, "peer reduction and broadcast", error);
             context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
@@ -360,7 +362,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
     }
     if ((call.phases & 4) && !wait_inline) {
         peer_wait_delivered<<<1, 32, 0, context->stream>>>(
-            own.flags, unsigned(units), context->status,
+            own.flags, unsigned(units * (bn / 64)), context->status,
             1000000ull * unsigned(context->options.peer_wait_ms));
         return launched(context, "peer delivery wait");
     }
