@@ -433,3 +433,177 @@ def fp8_linear(x, weight, weight_scale):
                     _pointer(weight_scale), row_stride, column_stride, ct.c_void_p(), 0,
                     _pointer(out))
     return out
+
+
+def _is_e8m0(tensor):
+    return tensor.dtype in (torch.float8_e8m0fnu, torch.uint8)
+
+
+def _packed_weight(weight):
+    packed_dtype = getattr(torch, "float4_e2m1fn_x2", None)
+    if packed_dtype is not None and weight.dtype == packed_dtype:
+        return True
+    _require(weight.dtype == torch.float8_e4m3fn,
+             "Quantized weight must be FP8 E4M3 or packed FP4 E2M1")
+    return False
+
+
+def quantized_matmul(x, x_scale, weight, weight_scale, activation_block=32):
+    """Block-scaled product with power-of-two (E8M0) scales, BF16 ``[..., outputs]``.
+
+    ``x`` is E4M3 ``[..., inner]`` with scales ``[..., inner/activation_block]``;
+    ``weight`` is E4M3 ``[outputs, inner]`` with scales ``[ceil(outputs/32),
+    inner/32]``, or packed E2M1 ``[outputs, inner/2]`` with scales ``[outputs,
+    inner/32]``. Argument meaning and checks follow ``quantized_matmul_public``
+    (``torch_bindings.cpp:328-377``).
+    """
+    _require(x.is_cuda and x.dtype == torch.float8_e4m3fn, "Quantized input must be CUDA FP8 E4M3")
+    packed = _packed_weight(weight)
+    _require(_is_e8m0(x_scale) and _is_e8m0(weight_scale), "Quantized scales must be E8M0")
+    for tensor in (x, x_scale, weight, weight_scale):
+        _require(tensor.device == x.device and tensor.is_contiguous(),
+                 "Quantized operands must be contiguous and on the same CUDA device")
+    _require(x.dim() >= 1 and weight.dim() == 2 and x_scale.dim() == x.dim()
+             and weight_scale.dim() == 2, "Quantized matrix and scale ranks do not match")
+    inner, outputs = x.shape[-1], weight.shape[0]
+    _require(inner >= 32 and inner % 32 == 0 and outputs >= 8 and outputs % 8 == 0
+             and weight.shape[1] == inner // (2 if packed else 1)
+             and (activation_block == 32 or (packed and activation_block == 128))
+             and inner % activation_block == 0,
+             "Invalid quantized matrix dimensions or activation block")
+    rows = 1
+    for index in range(x.dim() - 1):
+        _require(x_scale.shape[index] == x.shape[index], "Input scale shape mismatch")
+        rows *= x.shape[index]
+    _require(rows <= 65535, "Quantized multiplication supports at most 65535 rows")
+    _require(x_scale.shape[-1] == inner // activation_block
+             and weight_scale.shape[0] == (outputs if packed else (outputs + 31) // 32)
+             and weight_scale.shape[1] == inner // 32,
+             "Quantized scale shapes do not match their blocks")
+    out = torch.empty(tuple(x.shape[:-1]) + (outputs,), dtype=torch.bfloat16, device=x.device)
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("quantized_matmul", int(packed), rows, outputs, inner, activation_block,
+                        _pointer(x), _pointer(x_scale), _pointer(weight), _pointer(weight_scale),
+                        _pointer(out))
+    return out
+
+
+class QuantizedGroups:
+    """Weights and scales of a set of experts for ``matmul`` over routed rows.
+
+    Mirrors the reference's ``QuantizedGroups`` (``torch_bindings.cpp:466-550``):
+    the constructor records the device addresses of every expert's weight and
+    scale tensor in a device table, ``matmul`` multiplies batch ``b`` of ``x``
+    ``[groups, rows, inner]`` with expert ``active[b]`` for its first
+    ``counts[b]`` rows and returns BF16 ``[groups, rows, outputs]`` with every
+    other row zero.
+    """
+
+    def __init__(self, weights, scales):
+        _require(len(weights) >= 1 and len(weights) <= 65535 and len(weights) == len(scales),
+                 "Supply matching non-empty weight and scale groups")
+        first = weights[0]
+        _require(first.is_cuda and first.dim() == 2, "Grouped weights must be CUDA matrices")
+        self.packed = _packed_weight(first)
+        self.outputs = first.shape[0]
+        self.inner = first.shape[1] * (2 if self.packed else 1)
+        _require(self.outputs >= 8 and self.outputs % 8 == 0 and self.inner % 32 == 0,
+                 "Invalid grouped weight dimensions")
+        scale_rows = self.outputs if self.packed else (self.outputs + 31) // 32
+        addresses = []
+        for weight, scale in zip(weights, scales):
+            _require(weight.device == first.device and weight.dtype == first.dtype
+                     and weight.shape == first.shape and weight.is_contiguous()
+                     and scale.device == first.device and _is_e8m0(scale) and scale.dim() == 2
+                     and tuple(scale.shape) == (scale_rows, self.inner // 32)
+                     and scale.is_contiguous(),
+                     "Grouped weight shapes, dtypes, devices or scales differ")
+            addresses.append([weight.data_ptr(), scale.data_ptr()])
+        self.weights, self.scales = list(weights), list(scales)
+        self.metadata = torch.tensor(addresses, dtype=torch.int64).to(first.device)
+
+    def matmul(self, x, x_scale, active, counts, activation_block=32):
+        """Multiply each batch of ``x`` with its expert; see the class docstring."""
+        _require(x.device == self.metadata.device and x.dtype == torch.float8_e4m3fn
+                 and x.dim() == 3 and x.shape[0] <= 65535 and x.shape[1] <= 65535
+                 and x.shape[2] == self.inner
+                 and (activation_block == 32 or (self.packed and activation_block == 128))
+                 and self.inner % activation_block == 0,
+                 "Invalid grouped input dimensions or activation block")
+        _require(x_scale.device == x.device and _is_e8m0(x_scale)
+                 and tuple(x_scale.shape) == (x.shape[0], x.shape[1], self.inner // activation_block),
+                 "Grouped input scale shape or dtype mismatch")
+        for index in (active, counts):
+            _require(index.device == x.device and index.dtype == torch.int32 and index.dim() == 1
+                     and index.numel() == x.shape[0],
+                     "Grouped indices/counts require one CUDA int32 value per group")
+        for value in (x, x_scale, active, counts):
+            _require(value.is_contiguous(), "Grouped operands must be contiguous")
+        for weight, scale, (w_address, s_address) in zip(self.weights, self.scales,
+                                                         self.metadata.tolist()):
+            _require(weight.data_ptr() == w_address and scale.data_ptr() == s_address,
+                     "Captured weight storage changed; recreate the group")
+        out = torch.empty((x.shape[0], x.shape[1], self.outputs), dtype=torch.bfloat16,
+                          device=x.device)
+        if x.shape[0] and x.shape[1]:
+            with torch.cuda.device(x.device):
+                native = _native.context(x.device.index)
+                native.call("grouped_quantized_matmul", int(self.packed), x.shape[0],
+                            len(self.weights), x.shape[1], self.outputs, self.inner,
+                            activation_block, _pointer(x), _pointer(x_scale),
+                            _pointer(self.metadata), _pointer(active), _pointer(counts),
+                            _pointer(out))
+        return out
+
+
+def route_groups(experts, active, first_expert, rows):
+    """Route ``experts`` ``[tokens, choices]`` (int64 ids) to the local groups ``active``.
+
+    Returns ``(slots [groups, rows], reverse [tokens, choices], counts [groups])``
+    as ``route_groups_public`` does (``torch_bindings.cpp:552-576``). Row ``r`` of
+    group ``g`` is the ``r``-th routed slot in ascending slot order.
+    """
+    _require(experts.is_cuda and experts.dtype == torch.int64 and experts.dim() == 2
+             and experts.is_contiguous() and 1 <= experts.shape[1] <= 64
+             and experts.numel() <= _INT_MAX and active.device == experts.device
+             and active.dtype == torch.int32 and active.dim() == 1 and active.is_contiguous()
+             and 1 <= active.numel() <= 65535 and 1 <= rows <= 65535
+             and active.numel() * rows <= _INT_MAX and first_expert >= 0,
+             "Invalid expert routing dimensions, indices or devices")
+    groups = active.numel()
+    counts = torch.empty((groups,), dtype=torch.int32, device=experts.device)
+    slots = torch.empty((groups, rows), dtype=torch.int32, device=experts.device)
+    reverse = torch.empty(experts.shape, dtype=torch.int32, device=experts.device)
+    with torch.cuda.device(experts.device):
+        native = _native.context(experts.device.index)
+        native.call("route_groups", experts.shape[0], experts.shape[1], int(first_expert), groups,
+                    int(rows), _pointer(experts), _pointer(active), _pointer(counts),
+                    _pointer(slots), _pointer(reverse))
+    return slots, reverse, counts
+
+
+def reduce_groups(grouped, experts, reverse):
+    """Sum the routed BF16 rows of every token in ascending (expert, choice) order.
+
+    ``grouped`` is ``[groups, rows, width]``; returns FP32 ``[tokens, width]``
+    (``reduce_groups_public``, ``torch_bindings.cpp:578-600``).
+    """
+    _require(grouped.is_cuda and grouped.dtype == torch.bfloat16 and grouped.dim() == 3
+             and grouped.is_contiguous() and grouped.shape[0] * grouped.shape[1] <= _INT_MAX
+             and grouped.shape[2] >= 1 and experts.device == grouped.device
+             and experts.dtype == torch.int64 and experts.dim() == 2 and experts.is_contiguous()
+             and 1 <= experts.shape[1] <= 64 and experts.numel() <= _INT_MAX
+             and reverse.device == grouped.device and reverse.dtype == torch.int32
+             and reverse.shape == experts.shape and reverse.is_contiguous(),
+             "Invalid grouped reduction shapes, types or devices")
+    out = torch.empty((experts.shape[0], grouped.shape[2]), dtype=torch.float32,
+                      device=grouped.device)
+    if experts.shape[0]:
+        with torch.cuda.device(grouped.device):
+            native = _native.context(grouped.device.index)
+            native.call("reduce_groups", experts.shape[0], experts.shape[1], grouped.shape[2],
+                        grouped.shape[0] * grouped.shape[1], _pointer(experts), _pointer(reverse),
+                        _pointer(grouped), _pointer(out))
+    return out

@@ -8,6 +8,7 @@
 #include "context.cuh"
 #include "dispatch_bf16.cuh"
 #include "fp8_block.cuh"
+#include "quantized.cuh"
 #include "rms_norm.cuh"
 #include "row_parallel.cuh"
 #include "static_scratch.cuh"
@@ -130,6 +131,8 @@ extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
     cudaError_t error = cudaStreamSynchronize(context->stream);
     if (context->scratch)
         cudaFree(context->scratch);
+    if (context->operands)
+        cudaFree(context->operands);
     for (void *allocation : context->retired)
         cudaFree(allocation);
     if (context->status)
@@ -753,27 +756,4 @@ extern "C" int camblas_cuda_mlp_backward(camblas_cuda_context *context, int, int
                                          void *)
 {
     return host::unavailable(context, "camblas_cuda_mlp_backward");
-}
-extern "C" int camblas_cuda_quantized_matmul(camblas_cuda_context *context, int, int, int, int, int,
-                                             const void *, const void *, const void *,
-                                             const void *, void *)
-{
-    return host::unavailable(context, "camblas_cuda_quantized_matmul");
-}
-extern "C" int camblas_cuda_grouped_quantized_matmul(camblas_cuda_context *context, int, int, int,
-                                                     int, int, int, int, const void *,
-                                                     const void *, const void *, const void *,
-                                                     const void *, void *)
-{
-    return host::unavailable(context, "camblas_cuda_grouped_quantized_matmul");
-}
-extern "C" int camblas_cuda_route_groups(camblas_cuda_context *context, int, int, int, int, int,
-                                         const void *, const void *, void *, void *, void *)
-{
-    return host::unavailable(context, "camblas_cuda_route_groups");
-}
-extern "C" int camblas_cuda_reduce_groups(camblas_cuda_context *context, int, int, int, int,
-                                          const void *, const void *, const void *, void *)
-{
-    return host::unavailable(context, "camblas_cuda_reduce_groups");
 }

@@ -62,6 +62,12 @@ struct camblas_cuda_context {
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     bool scratch_captured = false;
+    /* second arena, same rules: operands that an entry point rewrites before it
+     * multiplies (the BF16 images of block-scaled FP8/FP4 matrices), kept apart
+     * from `scratch` because the GEMM that follows uses that one from offset 0 */
+    void *operands = nullptr;
+    size_t operands_bytes = 0;
+    bool operands_captured = false;
     std::vector<void *> retired;
     unsigned *status = nullptr; /* device words: [0] written by bounded waits that gave up,
                                    [1] Strassen range-guard flag of the call in flight */
@@ -151,42 +157,56 @@ inline int launched(camblas_cuda_context *context, const char *what)
     return error == cudaSuccess ? 0 : fail(context, what, error);
 }
 
-/* Make the arena at least `required` bytes. During stream capture growth is
+/* Make an arena at least `required` bytes. During stream capture growth is
  * refused and the arena is marked as recorded; a recorded arena is retired, not
- * freed, when it later grows, so replayed graphs keep valid addresses
- * (reference: backend.cu:397-434). */
-inline int reserve_scratch(camblas_cuda_context *context, size_t required)
+ * freed, when it later grows, so replayed graphs keep valid addresses (the rules
+ * of the reference's workspace, backend.cu:397-434). */
+inline int reserve_arena(camblas_cuda_context *context, void *&base, size_t &bytes, bool &recorded,
+                         size_t required, const char *what)
 {
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
     cudaError_t error = cudaStreamIsCapturing(context->stream, &capture);
     if (error != cudaSuccess)
         return fail(context, "scratch capture status", error);
-    if (capture != cudaStreamCaptureStatusNone) {
-        if (required > context->scratch_bytes)
-            return fail(context, "warm up scratch storage before CUDA graph capture", 1);
-        context->scratch_captured = true;
+    const bool capturing = capture != cudaStreamCaptureStatusNone;
+    if (required <= bytes) {
+        recorded = recorded || capturing;
         return 0;
     }
-    if (required <= context->scratch_bytes)
-        return 0;
+    if (capturing)
+        return fail(context, "warm up scratch storage before CUDA graph capture", 1);
+    /* the stream may still be using the old block */
     error = cudaStreamSynchronize(context->stream);
     if (error != cudaSuccess)
         return fail(context, "scratch synchronisation", error);
-    size_t rounded = (required + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    void *replacement = nullptr;
-    error = cudaMalloc(&replacement, rounded);
+    constexpr size_t granule = size_t(1) << 20;
+    const size_t rounded = (required + granule - 1) / granule * granule;
+    void *fresh = nullptr;
+    error = cudaMalloc(&fresh, rounded);
     if (error != cudaSuccess) {
         cudaGetLastError();
-        return fail(context, "scratch allocation", error);
+        return fail(context, what, error);
     }
-    if (context->scratch_captured)
-        context->retired.push_back(context->scratch);
-    else if (context->scratch)
-        cudaFree(context->scratch);
-    context->scratch = replacement;
-    context->scratch_bytes = rounded;
-    context->scratch_captured = false;
+    if (base != nullptr) {
+        if (recorded)
+            context->retired.push_back(base);
+        else
+            cudaFree(base);
+    }
+    base = fresh, bytes = rounded, recorded = false;
     return 0;
+}
+
+inline int reserve_scratch(camblas_cuda_context *context, size_t required)
+{
+    return reserve_arena(context, context->scratch, context->scratch_bytes,
+                         context->scratch_captured, required, "scratch allocation");
+}
+
+inline int reserve_operands(camblas_cuda_context *context, size_t required)
+{
+    return reserve_arena(context, context->operands, context->operands_bytes,
+                         context->operands_captured, required, "operand image allocation");
 }
 
 /* 2-D tensor map over a row-major [extent1][extent0] array of `element_bytes`

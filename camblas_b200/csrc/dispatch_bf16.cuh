@@ -191,10 +191,12 @@ inline int choose_split(int tiles, int k_blocks, int sms)
  * costs a second launch plus a write and a read of `split` FP32 copies of the
  * result. Rough microseconds for a weight-streaming tile of 128 rows by `bn`
  * token columns whose K blocks are 128 bytes deep: a CTA alone takes about
- * 0.19 us per block; with every SM streaming, HBM (6.5 TB/s) allows one block
- * per SM every 148 * bytes / 6.5 MB us. When the tiles alone already give
+ * 0.29 us per block (measured: 64 tiles of the Llama down projection without a
+ * split stream at 3.6 TB/s); with every SM streaming, HBM (6.5 TB/s) allows one
+ * block per SM every 148 * bytes / 6.5 MB us. When the tiles alone already give
  * most SMs work (N = 24576: 192 tiles), not splitting wins even though the fill
- * is worse: measured 17 against 31 us for 64 tokens. */
+ * is worse: measured 22 against 31 us for 64 tokens. The model is rough, so the
+ * unsplit form has to win by a quarter to be taken. */
 inline int split_if_it_pays(int split, int tiles, int k_blocks, int sms, int tokens, int outputs,
                             int bn)
 {
@@ -205,11 +207,11 @@ inline int split_if_it_pays(int split, int tiles, int k_blocks, int sms, int tok
         const long long units = 1ll * tiles * parts;
         const double waves = double((units + sms - 1) / sms);
         const double busy = double(units < sms ? units : sms);
-        const double step = std::max(0.19, busy * step_bytes / 6.5e6);
+        const double step = std::max(0.29, busy * step_bytes / 6.5e6);
         return waves * ((k_blocks + parts - 1) / parts) * step;
     };
     const double reduce_us = 3.0 + 2.0 * split * double(tokens) * outputs * 4 / 3.0e6;
-    return main_us(1) <= main_us(split) + reduce_us ? 1 : split;
+    return 1.25 * main_us(1) <= main_us(split) + reduce_us ? 1 : split;
 }
 
 inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)

@@ -5,9 +5,10 @@
  * here with the same name, argument list and status convention, so a caller
  * compiled against the reference links against this library unchanged. Each
  * declaration cites the reference declaration and implementation it stands in
- * for. Entry points that are outside the BF16/FP8 GEMM path are exported but
- * return -1 with a message naming the operation; nothing here falls back to a
- * CPU or to a vendor GEMM library.
+ * for. Entry points that are outside the BF16/FP8 GEMM path (FP32/FP64 GEMM,
+ * affine, MLP, attention, MLP backward) are exported but return -1 with a
+ * message naming the operation; nothing here falls back to a CPU or to a vendor
+ * GEMM library.
  *
  * Conventions shared by all entry points
  *   status      0 on success, negative on failure; the text of the last
@@ -355,12 +356,69 @@ int camblas_cuda_set_option(camblas_cuda_context *context, const char *name, int
  * with status -1 instead of silently using another one. For tests. */
 int camblas_cuda_force_kernel(camblas_cuda_context *context, int family);
 
+/* ---- block-scaled products with power-of-two scales, expert routing ------- */
+
+/* Replaces camblas_cuda_quantized_matmul (camblas_cuda.h:122-135;
+ * backend.cu:1165-1191; quantized.cuh:22-177). output[rows,outputs] (BF16) =
+ * input . weight^T with FP32 accumulation, where input is E4M3 [rows,inner]
+ * with E8M0 scales [rows, inner/activation_block] and weight is E4M3
+ * [outputs,inner] with E8M0 scales [ceil(outputs/32), inner/32] (packed = 0,
+ * activation_block 32) or packed E2M1, two values per byte, low nibble first,
+ * [outputs, inner/2] with E8M0 scales [outputs, inner/32] (packed = 1,
+ * activation_block 32 or 128). An E8M0 byte v is 2^(v-127), 0 is 2^-127, 255
+ * NaN. Where the reference scales and adds 32-deep block sums in order, this
+ * library folds the scales into exact BF16 images of both operands (context
+ * operand arena, grown on first use, not during stream capture) and multiplies
+ * them on the tensor cores: every term is exact in both, only the order of the
+ * FP32 additions differs. rows <= 65535; outputs a positive multiple of 8; inner
+ * a positive multiple of 32 and of activation_block. input and weight 16-byte
+ * aligned (8 for a packed weight); all five buffers distinct. */
+int camblas_cuda_quantized_matmul(camblas_cuda_context *context, int packed, int rows, int outputs,
+                                  int inner, int activation_block, const void *input,
+                                  const void *input_scale, const void *weight,
+                                  const void *weight_scale, void *output);
+/* Replaces camblas_cuda_grouped_quantized_matmul (camblas_cuda.h:165-176;
+ * backend.cu:1258-1304). input [groups,rows,inner], input scales
+ * [groups,rows,inner/activation_block], output BF16 [groups,rows,outputs].
+ * metadata is device uint64 [weight_groups][2]: the device addresses of each
+ * expert's weight and weight-scale storage in the layouts above (16-byte
+ * aligned). active and counts are device int32 [groups]: batch b is multiplied
+ * with expert active[b] for its first min(max(counts[b],0),rows) rows; every
+ * other row of the output, and every row of a batch whose active[b] is not in
+ * [0, weight_groups), is zero. One product launch per batch after two image
+ * kernels over all batches; needs groups * (rows + outputs) * inner * 2 bytes of
+ * the context's operand arena. */
+int camblas_cuda_grouped_quantized_matmul(camblas_cuda_context *context, int packed, int groups,
+                                          int weight_groups, int rows, int outputs, int inner,
+                                          int activation_block, const void *input,
+                                          const void *input_scale, const void *metadata,
+                                          const void *active, const void *counts, void *output);
+/* Replaces camblas_cuda_route_groups (camblas_cuda.h:177-185;
+ * backend.cu:1306-1338; routing.cuh:2-24). experts is device int64
+ * [tokens,choices]; slot s = token*choices+choice is routed to the first group
+ * g with active[g] == experts[s] - first_expert (ids below first_expert or not
+ * below INT_MAX are ignored). counts[g] = slots routed to g (may exceed rows);
+ * slots[g][r] = the r-th such slot in ascending slot order for r < rows, else
+ * -1; reverse[s] = g*rows + r, or -1 for slots without a row. The reference
+ * numbers rows in the order its atomics happen to complete; this numbering is
+ * the same on every run. Uses 4 bytes of context scratch per slot. */
+int camblas_cuda_route_groups(camblas_cuda_context *context, int tokens, int choices,
+                              int first_expert, int groups, int rows, const void *experts,
+                              const void *active, void *counts, void *slots, void *reverse);
+/* Replaces camblas_cuda_reduce_groups (camblas_cuda.h:186-192;
+ * backend.cu:1340-1361; routing.cuh:26-60). output[t][c] (FP32) = sum over the
+ * choices of token t, in ascending (expert id, choice index) order, of the BF16
+ * value input[reverse[t][choice]][c]; invalid expert ids and reverse rows
+ * outside [0, grouped_rows) are skipped. Same additions in the same order as
+ * the reference, so the same bits. choices 1..64. */
+int camblas_cuda_reduce_groups(camblas_cuda_context *context, int tokens, int choices, int width,
+                               int grouped_rows, const void *experts, const void *reverse,
+                               const void *input, void *output);
+
 /* ---- exported for link compatibility; not on the BF16/FP8 GEMM path ------- */
 /* Each returns -1 and sets "<name> is not provided by the B200 build".
  * Reference declarations: camblas_cuda.h:57-62 (sgemm/dgemm), :77-82 (affine,
- * mlp), :87-89 (attention), :94-99 (mlp_backward), :131-135 (quantized_matmul),
- * :171-176 (grouped_quantized_matmul), :183-185 (route_groups), :190-192
- * (reduce_groups). */
+ * mlp), :87-89 (attention), :94-99 (mlp_backward). */
 int camblas_cuda_sgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
                        int k, float alpha, const float *a, int lda, const float *b, int ldb,
                        float beta, float *c, int ldc);
@@ -381,21 +439,6 @@ int camblas_cuda_mlp_backward(camblas_cuda_context *context, int dtype, int rows
                               const void *w2, const void *hidden_output, const void *grad_output,
                               void *grad_hidden, void *dx, void *dw1, void *db1, void *dw2,
                               void *db2);
-int camblas_cuda_quantized_matmul(camblas_cuda_context *context, int packed, int rows, int outputs,
-                                  int inner, int activation_block, const void *input,
-                                  const void *input_scale, const void *weight,
-                                  const void *weight_scale, void *output);
-int camblas_cuda_grouped_quantized_matmul(camblas_cuda_context *context, int packed, int groups,
-                                          int weight_groups, int rows, int outputs, int inner,
-                                          int activation_block, const void *input,
-                                          const void *input_scale, const void *metadata,
-                                          const void *active, const void *counts, void *output);
-int camblas_cuda_route_groups(camblas_cuda_context *context, int tokens, int choices,
-                              int first_expert, int groups, int rows, const void *experts,
-                              const void *active, void *counts, void *slots, void *reverse);
-int camblas_cuda_reduce_groups(camblas_cuda_context *context, int tokens, int choices, int width,
-                               int grouped_rows, const void *experts, const void *reverse,
-                               const void *input, void *output);
 
 #ifdef __cplusplus
 }
