@@ -303,6 +303,36 @@ def gate_up_swiglu(x, weight_interleaved):
     return out.reshape(tuple(x.shape[:-1]) + (intermediate,))
 
 
+def gate_up_swiglu_fp8(x, weight_interleaved):
+    """``fp8_quantize(gate_up_swiglu(x, weight))`` from one GEMM pass.
+
+    Returns ``(q, scale)``: E4M3 ``[rows, intermediate]`` and FP32
+    ``[rows, intermediate/128]``, bit-equal to quantising the BF16 result of
+    ``gate_up_swiglu`` with ``fp8_quantize``; the BF16 tensor is never stored.
+    """
+    _check_tensor(x, x)
+    _check_tensor(weight_interleaved, x, "weight")
+    _require(x.dim() == 2 and weight_interleaved.dim() == 2
+             and x.shape[1] == weight_interleaved.shape[1]
+             and weight_interleaved.shape[0] % 256 == 0,
+             "gate_up_swiglu_fp8 requires x [rows, inner] and an interleaved [2*intermediate, inner] weight")
+    rows, inner = x.shape
+    intermediate = weight_interleaved.shape[0] // 2
+    x2 = x if x.stride(1) == 1 and x.stride(0) >= inner and x.stride(0) % 8 == 0 else x.contiguous()
+    w2 = weight_interleaved
+    if w2.stride(1) != 1 or w2.stride(0) < inner or w2.stride(0) % 8:
+        w2 = w2.contiguous()
+    q = torch.empty((rows, intermediate), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty((rows, intermediate // 128), dtype=torch.float32, device=x.device)
+    if rows:
+        with torch.cuda.device(x.device):
+            native = _native.context(x.device.index)
+            native.call("gate_up_swiglu_fp8", rows, inner, intermediate, _pointer(x2),
+                        x2.stride(0) if rows > 1 else inner, _pointer(w2), w2.stride(0),
+                        _pointer(q), _pointer(scale))
+    return q, scale
+
+
 def swiglu(gate, up, limit=0.0, routing=None):
     """Return ``rnd(silu(gate) * up [* routing[row]])`` with optional clipping."""
     _require(gate.is_cuda and gate.shape == up.shape and gate.dtype == up.dtype

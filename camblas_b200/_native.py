@@ -77,6 +77,7 @@ _SIGNATURES = {
     "linear_bf16": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P, _I], _I),
     "linear_bf16_static": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _I], _I),
     "gate_up_swiglu_bf16": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _I], _I),
+    "gate_up_swiglu_fp8": ([_P, _I, _I, _I, _P, _I, _P, _I, _P, _P], _I),
     "peer_bytes": ([_I, ct.c_size_t], ct.c_size_t),
     "peer_alloc": ([_P, ct.c_size_t, ct.POINTER(_P), _P], _I),
     "peer_open": ([_P, _P, ct.POINTER(_P)], _I),

@@ -362,6 +362,32 @@ extern "C" int camblas_cuda_gate_up_swiglu_bf16(camblas_cuda_context *context, i
     });
 }
 
+extern "C" int camblas_cuda_gate_up_swiglu_fp8(camblas_cuda_context *context, int rows, int inner,
+                                               int intermediate, const void *x, int ldx,
+                                               const void *w, int ldw, void *q, float *scale)
+{
+    return guarded(context, [&] {
+        if (rows < 0 || inner < 1 || intermediate < 0 || ldx < inner || ldw < inner ||
+            intermediate > INT_MAX / 2)
+            return fail(context, "invalid gate_up SwiGLU dimensions", 1);
+        if (rows == 0 || intermediate == 0)
+            return 0;
+        if (!x || !w || !q || !scale || q == x || q == w)
+            return fail(context, "missing or aliased gate_up SwiGLU operand", 1);
+        if (intermediate % 128 != 0)
+            return fail(context, "gate_up SwiGLU needs an intermediate width that is a multiple of 128",
+                        1);
+        if (ldx % 8 != 0 || ldw % 8 != 0 || !host::aligned16(x) || !host::aligned16(w) ||
+            !host::aligned16(q) || (uintptr_t(scale) & 3))
+            return fail(context, "gate_up SwiGLU needs 16-byte aligned rows (multiples of 8 elements)",
+                        1);
+        return host::run_gate_up_swiglu(context, rows, inner, intermediate,
+                                        static_cast<const __nv_bfloat16 *>(x), ldx,
+                                        static_cast<const __nv_bfloat16 *>(w), ldw, nullptr, 0,
+                                        static_cast<uint8_t *>(q), scale);
+    });
+}
+
 /* ---- RMS normalisation ---- */
 
 namespace

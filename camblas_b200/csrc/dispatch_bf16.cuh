@@ -107,6 +107,9 @@ inline int prepare_kernels()
     status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwiglu>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        PairSmem<256, 3, 2>::kTotal));
+    status |= int(cudaFuncSetAttribute(gemm_bf16_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwigluQuant>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       PairSmem<256, 3, 2>::kTotal));
     status |= prepare_row_kernels<kMajorK, kMajorMN>();
     status |= prepare_row_kernels<kMajorMN, kMajorK>();
     status |= prepare_row_kernels<kMajorMN, kMajorMN>();
@@ -495,8 +498,12 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
  * its second pass. */
 inline int run_gate_up_swiglu(camblas_cuda_context *context, int rows, int inner, int intermediate,
                               const __nv_bfloat16 *x, long long ldx, const __nv_bfloat16 *w,
-                              long long ldw, __nv_bfloat16 *out, long long ldo)
+                              long long ldw, __nv_bfloat16 *out, long long ldo,
+                              uint8_t *quant_out = nullptr, float *quant_scale = nullptr)
 {
+    /* with quant_out the result leaves as E4M3 [rows, intermediate] plus FP32
+     * scales [rows, intermediate / 128] and `out` is not written */
+    const bool quantise = quant_out != nullptr;
     sm100::GemmTask task{};
     const int packed = 2 * intermediate;
     task.rows = rows, task.cols = packed, task.depth = inner;
@@ -510,6 +517,8 @@ inline int run_gate_up_swiglu(camblas_cuda_context *context, int rows, int inner
     task.cut0 = task.cut1 = packed;
     task.batch = 1;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    task.quant_out = quant_out, task.ld_quant = intermediate;
+    task.quant_scale = quant_scale, task.quant_groups = intermediate / 128;
     const int pairs_max = context->sm_count / 2;
     if (task.r_blocks <= 8 && pairs_max / task.r_blocks >= 2 && task.k_blocks >= 16) {
         /* the policy of run_tensor_pair for 256-column tiles */
@@ -532,20 +541,29 @@ inline int run_gate_up_swiglu(camblas_cuda_context *context, int rows, int inner
     CUtensorMap p, q, d;
     const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     bool ok = encode_2d(context, &p, bf16, 2, x, inner, rows, uint64_t(ldx) * 2, 64, 128) &&
-              encode_2d(context, &q, bf16, 2, w, inner, packed, uint64_t(ldw) * 2, 64, 128) &&
-              encode_2d(context, &d, bf16, 2, out, intermediate, rows, uint64_t(ldo) * 2, 64, 32);
+              encode_2d(context, &q, bf16, 2, w, inner, packed, uint64_t(ldw) * 2, 64, 128);
+    if (quantise)
+        d = q; /* the kernel only prefetches its output map in this mode */
+    else
+        ok = ok && encode_2d(context, &d, bf16, 2, out, intermediate, rows, uint64_t(ldo) * 2, 64, 32);
     if (!ok)
         return fail(context, "tensor map encoding", 1);
     using namespace sm100;
     cudaError_t error =
-        launch_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwiglu>(context, pairs, p, q, d, d, d, task);
+        quantise ? launch_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwigluQuant>(context, pairs, p, q, d,
+                                                                         d, d, task)
+                 : launch_pair<256, 3, kMajorK, kMajorK, 2, kEpiSwiglu>(context, pairs, p, q, d, d, d,
+                                                                    task);
     if (error != cudaSuccess)
         return fail(context, "two-SM tcgen05 gate_up GEMM with SwiGLU", error);
     context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
     if (task.sk_cols == 0)
         return 0;
     dim3 grid(task.sk_cols, 16, task.r_blocks);
-    sm100::sk_fixup_pair_swiglu<<<grid, 256, 0, context->stream>>>(task, pairs);
+    if (quantise)
+        sm100::sk_fixup_pair_swiglu<true><<<grid, 256, 0, context->stream>>>(task, pairs);
+    else
+        sm100::sk_fixup_pair_swiglu<false><<<grid, 256, 0, context->stream>>>(task, pairs);
     return launched(context, "stream-K fix-up with SwiGLU");
 }
 

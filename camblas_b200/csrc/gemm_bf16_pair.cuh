@@ -122,6 +122,7 @@ constexpr int kPairRows = 256;
 constexpr int kEpiStore = 0;  /* alpha, bias, addend, one rounding, TMA store */
 constexpr int kEpiPush = 1;   /* BF16 partial tile to the GPU that owns it (row_parallel.cuh) */
 constexpr int kEpiSwiglu = 2; /* tile = 128 gate + 128 up columns: SiLU(gate) * up */
+constexpr int kEpiSwigluQuant = 3; /* the same, written as E4M3 with 1 x 128 scales */
 
 
 template <int BN, int Stages, int Sub = 1> struct PairSmem {
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     static_assert(!kDynamic || QMajor == kMajorK, "run-time width needs a K-major Q operand");
     constexpr bool Push = Epi == kEpiPush;
     static_assert(Epi == kEpiStore || !kDynamic, "the special epilogues work on fixed-width tiles");
-    static_assert(Epi != kEpiSwiglu || (BNT == 256 && QMajor == kMajorK),
+    static_assert((Epi != kEpiSwiglu && Epi != kEpiSwigluQuant) || (BNT == 256 && QMajor == kMajorK),
                   "the SwiGLU epilogue pairs 128 gate with 128 up columns of a K-major weight");
     const int BN = kDynamic ? task.width : BNT;
     const int kHalf = BN / 2;
@@ -354,12 +355,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                     mbar_arrive_cluster(map_to_rank(smem_u32(&tmem_empty[buffer]), 0));
             };
-            if constexpr (Epi == kEpiSwiglu) {
+            if constexpr (Epi == kEpiSwiglu || Epi == kEpiSwigluQuant) {
                 if (u.slot >= 0) {
                     float *slot = task.sk_partial +
                                   (static_cast<long long>(u.slot) * 2 + rank) * kBlockR * BNT;
                     epilogue_partial<kLayoutWidth>(slot, taddr, quarter, lane, slab, slab_use, roomy,
                                                    release);
+                } else if constexpr (Epi == kEpiSwigluQuant) {
+                    epilogue_swiglu_quant(task, taddr, row0 + lane, u.cb * 128, release);
                 } else {
                     epilogue_swiglu(task, &map_d0, taddr, row0, u.cb * 128, lane, slab, slab_use,
                                     roomy, release);
@@ -467,21 +470,25 @@ __global__ void __launch_bounds__(256)
  * gate + 128 up): one thread per eight output columns adds the pieces of its
  * gate columns and of the matching up columns in ascending K order and stores
  * SiLU(gate) * up. grid = (stream-K column blocks, 16, 256-row blocks). */
+template <bool Quantise>
 __global__ void __launch_bounds__(256) sk_fixup_pair_swiglu(const GemmTask task, int pairs)
 {
     const int vector = blockIdx.y * 256 + threadIdx.x;
     const int r = vector >> 4, c8 = (vector & 15) * 8; /* r in [0, 256), c8 in [0, 128) */
     const int rb = blockIdx.z, cb = task.dp_cols + blockIdx.x;
     const int row = rb * kPairRows + r, col = cb * 128 + c8; /* output column */
-    if (row >= task.rows || cb * 256 + c8 >= task.cols)
+    const bool live = row < task.rows && cb * 256 + c8 < task.cols;
+    if (!Quantise && !live)
         return;
     float gate[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float up[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     auto slot_of = [&](int team, int piece) {
         return (2ll * (team * task.r_blocks + rb) + piece) * 2 + (r >> 7);
     };
-    sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, c8, slot_of, gate);
-    sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, 128 + c8, slot_of, up);
+    if (live) {
+        sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, c8, slot_of, gate);
+        sum_pieces<256>(task, pairs / task.r_blocks, blockIdx.x, r & 127, 128 + c8, slot_of, up);
+    }
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -491,7 +498,38 @@ __global__ void __launch_bounds__(256) sk_fixup_pair_swiglu(const GemmTask task,
     packed.y = pack_bf16(v[2], v[3]);
     packed.z = pack_bf16(v[4], v[5]);
     packed.w = pack_bf16(v[6], v[7]);
-    *reinterpret_cast<uint4 *>(task.out + static_cast<long long>(row) * task.ld_out + col) = packed;
+    if constexpr (!Quantise) {
+        *reinterpret_cast<uint4 *>(task.out + static_cast<long long>(row) * task.ld_out + col) = packed;
+    } else {
+        /* sixteen neighbouring threads hold the 128 outputs of one row: their
+         * largest magnitude (of the BF16-rounded values) is the group's */
+        const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+        float largest = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            largest = fmaxf(largest, fmaxf(fabsf(bf16_low(words[w])), fabsf(bf16_high(words[w]))));
+#pragma unroll
+        for (int offset = 1; offset < 16; offset <<= 1)
+            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
+        if (!live)
+            return;
+        const float maximum = fmaxf(largest, 1e-10f);
+        if ((vector & 15) == 0)
+            task.quant_scale[static_cast<long long>(row) * task.quant_groups + cb] =
+                __fmul_rn(maximum, 1.0f / 448.0f);
+        const float inverse = __fdiv_rn(448.0f, maximum);
+        uint2 bytes;
+        bytes.x = quantise_e4m3(bf16_low(words[0]), inverse) |
+                  (quantise_e4m3(bf16_high(words[0]), inverse) << 8) |
+                  (quantise_e4m3(bf16_low(words[1]), inverse) << 16) |
+                  (quantise_e4m3(bf16_high(words[1]), inverse) << 24);
+        bytes.y = quantise_e4m3(bf16_low(words[2]), inverse) |
+                  (quantise_e4m3(bf16_high(words[2]), inverse) << 8) |
+                  (quantise_e4m3(bf16_low(words[3]), inverse) << 16) |
+                  (quantise_e4m3(bf16_high(words[3]), inverse) << 24);
+        *reinterpret_cast<uint2 *>(task.quant_out + static_cast<long long>(row) * task.ld_quant + col) =
+            bytes;
+    }
 }
 
 } // namespace sm100

@@ -84,6 +84,14 @@ struct GemmTask {
     int push_world;
     __nv_bfloat16 *push_staging[8];
     unsigned *push_arrive[8];
+    /* SwiGLU epilogue that also quantises (kEpiSwigluQuant): the 128 outputs a
+     * tile holds for one row are one 1 x 128 quantisation group, written as E4M3
+     * bytes to quant_out[row * ld_quant + column] with their FP32 scale
+     * (max(amax, 1e-10) / 448) in quant_scale[row * quant_groups + column / 128]. */
+    uint8_t *quant_out;
+    long long ld_quant;
+    float *quant_scale;
+    int quant_groups;
 };
 
 constexpr int kBlockR = 128;
@@ -491,6 +499,72 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmTask &task, const CUte
             tma_store_commit();
         }
         ++slab_use;
+    }
+}
+
+/* E4M3 byte of value * inverse, clamped to the finite range: the conversion of
+ * the activation quantiser (fp8::quantize_rows_kernel). */
+__device__ __forceinline__ uint32_t quantise_e4m3(float value, float inverse)
+{
+    const float scaled = fminf(fmaxf(__fmul_rn(value, inverse), -448.f), 448.f);
+    uint16_t pair;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.f), "f"(scaled));
+    return pair & 255u;
+}
+
+/* SwiGLU epilogue that hands the down projection its FP8 input directly: the
+ * 128 outputs SiLU(gate) * up of this thread's row (one quantisation group) are
+ * rounded to BF16 exactly as epilogue_swiglu would store them, their largest
+ * magnitude gives the group's scale, and the E4M3 bytes and the scale are
+ * written instead of the BF16 values - what fp8::quantize_rows_kernel would
+ * produce from the BF16 tensor, without that tensor ever reaching memory.
+ * Four passes of 32 columns keep the registers in hand: 64 packed BF16 pairs
+ * stay live next to one pass of gate and up accumulators. */
+template <typename Release>
+__device__ __forceinline__ void epilogue_swiglu_quant(const GemmTask &task, uint32_t taddr, int row,
+                                                      int out_col0, Release release)
+{
+    const float alpha = task.alpha;
+    uint32_t kept[64]; /* the row's 128 outputs as BF16 pairs */
+    float largest = 0.f;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        uint32_t gate[32], up[32];
+        tmem_ld_32x32(taddr + pass * 32, gate);
+        tmem_ld_32x32(taddr + 128 + pass * 32, up);
+        tmem_ld_wait();
+        if (pass == 3)
+            release();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float low = swiglu_value(alpha * __uint_as_float(gate[i]), alpha * __uint_as_float(up[i]));
+            const float high =
+                swiglu_value(alpha * __uint_as_float(gate[i + 1]), alpha * __uint_as_float(up[i + 1]));
+            const uint32_t pair = pack_bf16(low, high);
+            kept[pass * 16 + i / 2] = pair;
+            largest = fmaxf(largest, fmaxf(fabsf(bf16_low(pair)), fabsf(bf16_high(pair))));
+        }
+    }
+    if (row >= task.rows)
+        return;
+    const float maximum = fmaxf(largest, 1e-10f);
+    task.quant_scale[static_cast<long long>(row) * task.quant_groups + (out_col0 >> 7)] =
+        __fmul_rn(maximum, 1.0f / 448.0f);
+    const float inverse = __fdiv_rn(448.0f, maximum);
+    uint4 *target =
+        reinterpret_cast<uint4 *>(task.quant_out + static_cast<long long>(row) * task.ld_quant + out_col0);
+#pragma unroll
+    for (int piece = 0; piece < 8; ++piece) {
+        uint32_t words[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t first = kept[piece * 8 + w * 2], second = kept[piece * 8 + w * 2 + 1];
+            words[w] = quantise_e4m3(bf16_low(first), inverse) |
+                       (quantise_e4m3(bf16_high(first), inverse) << 8) |
+                       (quantise_e4m3(bf16_low(second), inverse) << 16) |
+                       (quantise_e4m3(bf16_high(second), inverse) << 24);
+        }
+        target[piece] = make_uint4(words[0], words[1], words[2], words[3]);
     }
 }
 

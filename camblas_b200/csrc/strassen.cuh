@@ -115,8 +115,14 @@ inline int run(camblas_cuda_context *context, const host::Product &x)
     const size_t plane = size_t(h) * h;
     const size_t bytes = plane * 7 * (2 + 2 + 4);
     int status = host::reserve_scratch(context, bytes);
-    if (status != 0)
-        return status;
+    if (status != 0) {
+        /* No room for the planes: multiply classically and count it, as the
+         * reference does when its Strassen workspace cannot be had
+         * (backend.cu:490-526). The failed allocation left no CUDA error behind. */
+        context->counts[5]++;
+        context->error[0] = 0;
+        return host::run_product(context, x);
+    }
     auto *left = static_cast<__nv_bfloat16 *>(context->scratch);
     auto *right = left + 7 * plane;
     auto *products = reinterpret_cast<float *>(right + 7 * plane);

@@ -160,6 +160,19 @@ int camblas_cuda_gate_up_swiglu_bf16(camblas_cuda_context *context, int rows, in
                                      int intermediate, const void *x, int ldx, const void *w,
                                      int ldw, void *out, int ldo);
 
+/* No counterpart in the reference ABI. camblas_cuda_gate_up_swiglu_bf16 whose
+ * result leaves as the FP8 input of the down projection: q[rows, intermediate]
+ * (E4M3, contiguous) and scale[rows, intermediate/128] (FP32) are exactly what
+ * camblas_cuda_fp8_quantize_rows produces from the BF16 result of
+ * camblas_cuda_gate_up_swiglu_bf16 - every 128 outputs that a GEMM tile holds
+ * for a row are one quantisation group - without that BF16 tensor being written
+ * or read. The reference quantises the activated product in the prologue of its
+ * block-128 kernel (camblas/_hopper.py:66-98). Same weight layout and
+ * requirements as camblas_cuda_gate_up_swiglu_bf16; q 16-byte aligned. */
+int camblas_cuda_gate_up_swiglu_fp8(camblas_cuda_context *context, int rows, int inner,
+                                    int intermediate, const void *x, int ldx, const void *w,
+                                    int ldw, void *q, float *scale);
+
 /* ---- row-parallel linear layer over several GPUs ------------------------ */
 
 /* None of the following has a counterpart in the reference, which has no

@@ -114,3 +114,20 @@ def test_rejects_bad_shapes():
         _kernels.gate_up_swiglu(x, torch.zeros((200, 64), dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(ValueError):
         _kernels.gate_up_swiglu(x, torch.zeros((256, 32), dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("rows,inner,intermediate", [(300, 512, 384), (512, 1024, 1280), (64, 512, 256),
+                                                     (512, 8192, 28672)])
+def test_quantising_epilogue_equals_quantising_the_bf16_result(rows, inner, intermediate):
+    """gate_up_swiglu_fp8 must give the bytes and scales that fp8_quantize gives on the
+    BF16 result of gate_up_swiglu (the last shape has a stream-K tail, whose second
+    pass quantises too), and an FP8 down projection on them the same product."""
+    torch.manual_seed(20261127 + rows + intermediate)
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(2 * intermediate, inner, device="cuda") * (2.0 / inner ** 0.5)).bfloat16()
+    mixed = _kernels.interleave_gate_up(w)
+    q, scale = _kernels.gate_up_swiglu_fp8(x, mixed)
+    assert _native.context(0).device_status() == 0
+    expected_q, expected_scale = _kernels.fp8_quantize(_kernels.gate_up_swiglu(x, mixed))
+    assert torch.equal(scale, expected_scale)
+    assert torch.equal(q.view(torch.uint8), expected_q.view(torch.uint8))

@@ -72,3 +72,50 @@ def test_peer_region_capacity_counts_whole_tiles():
     assert PeerRegions.capacity_for(512, 8192) == 512 * 8192
     assert PeerRegions.capacity_for(300, 1000) == 512 * 1024
     assert PeerRegions.capacity_for(1, 8) == 256 * 256
+
+
+def _failing_linear(x, weight, bias=None, residual=None):
+    raise RuntimeError("injected: this rank's GEMM failed")
+
+
+def _faulty_worker(rank, world, port, results):
+    """Rank 1's product raises before the sum; rank 0 must get an error, not wait for ever."""
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    generator = torch.Generator().manual_seed(7)
+    down = torch.randn(64, 128, generator=generator)
+    hidden = torch.randn(6, 128, generator=generator)
+    linear = _failing_linear if rank == 1 else _host_linear
+    row = tp.RowParallelLinear(down, rank, world, linear=linear)
+    dist.barrier()
+    started = time.monotonic()
+    try:
+        row(row.slice_input(hidden))
+        results[rank] = ("returned", time.monotonic() - started)
+    except RuntimeError as error:
+        results[rank] = ("raised", time.monotonic() - started, str(error)[:80])
+    # no collective after a failure: the ranks leave on their own
+
+
+def test_a_rank_that_fails_before_the_sum_gives_the_others_an_error_not_a_hang():
+    """Failure injected on the host (an exception in one rank's GEMM): the rank that did
+    compute its partial product finds out through the process group's timeout and gets a
+    RuntimeError from the all-reduce within seconds; nothing waits indefinitely."""
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    import time
+
+    context = mp.spawn(_faulty_worker, args=(2, port, results), nprocs=2, join=False)
+    deadline = time.monotonic() + 90
+    while not context.join(timeout=5):  # joins the ranks one at a time
+        assert time.monotonic() < deadline, "the ranks did not finish: a hang"
+    assert results[1][0] == "raised" and "injected" in results[1][2]
+    assert results[0][0] == "raised", results[0]
+    assert results[0][1] < 30
