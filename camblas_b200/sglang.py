@@ -8,14 +8,18 @@ Mirrors ``camblas/sglang.py:199-747`` of the reference for the dense path:
 * ``linear``: an AROUND hook on ``UnquantizedLinearMethod.apply``; eligible calls
   (CUDA, BF16, contiguous, same device and dtype, no gradient) go through
   ``F.linear`` under the ATen overrides, everything else through the original.
+* ``linear`` also hooks ``ColumnParallelBatchedLinear.forward`` (``sglang.py:294-336``):
+  a batched BF16 projection ``[batch, rows, inner] x [batch, outputs, inner]`` runs
+  as one GEMM per batch entry. The reference takes exactly the shape
+  ``(2, 1, 128) x (2, 2048, 128)`` on Hopper with its Gluon kernel; here any
+  contiguous BF16 shape of that form is taken.
 * ``fp8``: AROUND hooks on the block-128 dense entry point, the block-32
   pre-quantised product and the block-32 BF16-input linear. The block-128 hook
   takes any number of token rows (the reference takes one row and a fixed list
   of eleven shapes, ``sglang.py:458-470``).
 
 The expert-parallel hooks of the reference (``fused_experts``, the stable MoE
-ordering, the batched 2x1x128 product) are not part of the dense GEMM path and
-are not installed. Every hook returns ``original(...)`` for inputs it does not
+ordering) are not part of the dense GEMM path and are not installed. Every hook returns ``original(...)`` for inputs it does not
 take, and counts what it does take in ``dispatch_counts()``.
 """
 
@@ -66,6 +70,19 @@ def install():
             output = torch.nn.functional.linear(x.view(-1, x.shape[-1]), weight, bias)
             return output.view(*x.shape[:-1], weight.shape[0])
         return original(method, layer, x, bias)
+
+    def batched(original, layer, input):
+        """Batched BF16 projection: ``output[b] = input[b] @ weight[b].T`` for every entry."""
+        weight = layer.weight
+        if (input.is_cuda and input.ndim == 3 and weight.ndim == 3
+                and input.shape[0] == weight.shape[0] and input.shape[2] == weight.shape[2]
+                and input.dtype == weight.dtype == torch.bfloat16 and input.is_contiguous()
+                and weight.is_contiguous() and weight.device == input.device
+                and not torch.is_grad_enabled() and not torch._dynamo.is_compiling()):
+            _count("bmm")
+            return torch.stack([cb.linear(input[entry], weight[entry])
+                                for entry in range(input.shape[0])])
+        return original(layer, input)
 
     def dense(original, input, weight, block_size, weight_scale, input_scale=None, bias=None):
         """Block-128 w8a8 linear: quantise the BF16 rows, then the block-scaled GEMM."""
@@ -137,6 +154,8 @@ def install():
         HookRegistry.register(
             "sglang.srt.layers.quantization.unquant.UnquantizedLinearMethod.apply", linear,
             HookType.AROUND)
+        HookRegistry.register("sglang.srt.layers.linear.ColumnParallelBatchedLinear.forward", batched,
+                              HookType.AROUND)
     if "fp8" in selected:
         HookRegistry.register(
             "sglang.srt.layers.quantization.fp8_utils.deepgemm_w8a8_block_fp8_linear_with_fallback",

@@ -9,7 +9,8 @@ from camblas_b200 import sglang as plugin
 from tests.sglang_stub import HookType, install_stub
 
 TARGETS = {
-    "linear": ["sglang.srt.layers.quantization.unquant.UnquantizedLinearMethod.apply"],
+    "linear": ["sglang.srt.layers.quantization.unquant.UnquantizedLinearMethod.apply",
+               "sglang.srt.layers.linear.ColumnParallelBatchedLinear.forward"],
     "fp8": ["sglang.srt.layers.quantization.fp8_utils.deepgemm_w8a8_block_fp8_linear_with_fallback",
             "sglang.kernels.ops.quantization.fp8_kernel.w8a8_block_fp8_matmul_triton",
             "sglang.srt.layers.quantization.fp8_utils.triton_w8a8_block_fp8_linear"],
@@ -73,3 +74,7 @@ def test_linear_hook_falls_back_for_ineligible_inputs(monkeypatch):
     calls = []
     result = hook(lambda *arguments: calls.append(arguments) or "original", "method", layer, x, None)
     assert result == "original" and calls == [("method", layer, x, None)]
+    batched = registry.hooks[TARGETS["linear"][1]][0]
+    stacked = types.SimpleNamespace(weight=torch.zeros(2, 8, 16, dtype=torch.bfloat16))
+    entries = torch.zeros(2, 1, 16, dtype=torch.bfloat16)
+    assert batched(lambda *arguments: "original", stacked, entries) == "original"  # CPU tensors

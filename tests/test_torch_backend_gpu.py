@@ -162,7 +162,7 @@ def test_sglang_hooks_on_cuda_tensors():
     registry = install_stub()
     plugin.install()
     hooks = {name.rsplit(".", 1)[-1]: function for name, (function, _) in registry.hooks.items()}
-    assert len(hooks) == 4
+    assert len(hooks) == 5
 
     def original(*arguments):
         raise AssertionError("an eligible call fell back to the original function")
@@ -174,6 +174,15 @@ def test_sglang_hooks_on_cuda_tensors():
     y = hooks["apply"](original, None, layer, x, bias)
     assert y.shape == (2, 3, 128)
     close(y, x.double().cpu() @ layer.weight.double().cpu().t() + bias.double().cpu())
+    # batched projection, the reference's shape (2, 1, 128) x (2, 2048, 128) and a larger one
+    torch.set_grad_enabled(False)
+    for batch, rows, outputs, inner in ((2, 1, 2048, 128), (3, 70, 136, 256)):
+        entries = torch.randn(batch, rows, inner, device="cuda").bfloat16()
+        stacked = types.SimpleNamespace(weight=torch.randn(batch, outputs, inner, device="cuda").bfloat16())
+        y = hooks["forward"](original, stacked, entries)
+        assert y.shape == (batch, rows, outputs)
+        close(y, torch.bmm(entries.double().cpu(), stacked.weight.double().cpu().transpose(1, 2)))
+    torch.set_grad_enabled(True)
     # block-128 dense hook, several token rows
     rows, outputs, inner = 5, 384, 512
     x = torch.randn(rows, inner, device="cuda").bfloat16()
@@ -199,6 +208,7 @@ def test_sglang_hooks_on_cuda_tensors():
     assert fused.shape == split.shape == (1, outputs) and torch.equal(fused, split)
     counts = plugin.dispatch_counts()
     assert counts["linear"] == 1 and counts["fp8"] == 3 and counts["fp8_dense_block128"] == 1
+    assert counts["bmm"] == 2
     # ineligible inputs reach the original
     marker = object()
     assert hooks["apply"](lambda *a: marker, None, layer, x.float()[:, :256], None) is marker
