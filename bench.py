@@ -1137,6 +1137,13 @@ def run_decode_tp(args):
     rows_out = Rows(rank)
     collective = (dist, world, device) if world > 1 else None
     failures = []
+    peers = None
+    if world > 1:
+        try:
+            peers = tp.PeerRegions.create(tp.PeerRegions.capacity_for(64, 8192), device.index)
+        except RuntimeError as error:
+            if rank == 0:
+                print(f"bench: peer regions unavailable ({error}); NCCL only", file=sys.stderr)
     for name, outputs, inner, mode in (("down", 8192, 28672, "row"), ("gate_up", 57344, 8192, "column")):
         generator = torch.Generator(device=device).manual_seed(705537 + 4)
         weight = (torch.randn((outputs, inner), device=device, generator=generator) * 0.02).bfloat16()
@@ -1172,6 +1179,23 @@ def run_decode_tp(args):
                     entry["all_reduce_us"] = None
                     entry["note_all_reduce"] = f"not captured in a graph: {error}"
                 entry["all_reduce_bytes"] = 2 * tokens * outputs
+                if peers is not None:
+                    # the library's own one-shot exchange over peer memory
+                    entry["peer_all_reduce_us"] = round(graph_time_us(
+                        lambda i: peers.all_reduce(payload, out=payload), 1, collective=collective), 2)
+
+                    def fused(i):
+                        partial = _kernels.linear(x_local, shards[i % copies])
+                        return peers.all_reduce(partial, out=partial)
+
+                    entry["product_plus_peer_all_reduce_us"] = round(
+                        graph_time_us(fused, copies, collective=collective), 2)
+                    summed = peers.all_reduce(_kernels.linear(x_local, shard))
+                    whole_sum = _kernels.linear(x, weight).float()
+                    entry["peer_sum_rel_l2_vs_unsharded"] = (
+                        (summed.float() - whole_sum).norm() / whole_sum.norm()).item()
+                    if not entry["peer_sum_rel_l2_vs_unsharded"] <= 1e-2:
+                        failures.append((name, tokens, "peer sum"))
             # parity: own shard by sampled FP64 dots, assembled result against the unsharded product
             local = layer.linear(x_local, shard)
             entry["shard_rel_l2_fp64_samples"] = sampled_dots(torch, x_local, shard, local)
@@ -1193,7 +1217,7 @@ def run_decode_tp(args):
         del shards, layer, weight
         torch.cuda.empty_cache()
     rows_out.save(args.json)
-    shutdown(torch, dist, world)
+    shutdown(torch, dist, world, peers)
     if failures:
         raise SystemExit(f"parity failures: {failures}")
 

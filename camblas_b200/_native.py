@@ -84,6 +84,7 @@ _SIGNATURES = {
     "peer_close": ([_P, _P], _I),
     "peer_free": ([_P, _P], _I),
     "peer_reset": ([_P, _P, _I, ct.c_size_t], _I),
+    "peer_allreduce_bf16": ([_P, _I, _I, ct.c_size_t, ct.POINTER(_P), _I, ct.c_size_t, _P, _P], _I),
     "linear_bf16_allreduce": (
         [_P, _I, _I, ct.c_size_t, ct.POINTER(_P), _I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I],
         _I,

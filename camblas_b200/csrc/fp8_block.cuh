@@ -491,8 +491,16 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
     volatile uint32_t *abort = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int units = task.r_blocks * task.c_blocks;
+    /* a unit is a tile, or one of `split` contiguous K ranges of a tile when the
+     * tiles alone would leave most SMs idle; consecutive units are the K ranges
+     * of one tile */
+    const int units = task.r_blocks * task.c_blocks * task.split;
     const int groups = task.k_blocks;
+    if (task.split > 1) {
+        /* the reduction over the K ranges may become resident now; it waits for
+         * this grid's completion itself */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Stages; ++s) {
@@ -518,7 +526,13 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto decode = [&](int tile, int &rb, int &cb) {
+    auto range = [&](int unit, int &kb0, int &kb1) {
+        const int part = unit % task.split;
+        kb0 = part * task.k_blocks_per_split;
+        kb1 = min(groups, kb0 + task.k_blocks_per_split);
+    };
+    auto decode = [&](int unit, int &rb, int &cb) {
+        const int tile = unit / task.split;
         int per_panel = task.panel * task.c_blocks;
         int panel = tile / per_panel;
         int local = tile - panel * per_panel;
@@ -535,16 +549,17 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
             bool ok = true;
             for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
-                int rb, cb;
+                int rb, cb, kb0, kb1;
                 decode(unit, rb, cb);
-                for (int kb = 0; kb < groups; kb += Sub) {
+                range(unit, kb0, kb1);
+                for (int kb = kb0; kb < kb1; kb += Sub) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
                         report(task.status, abort, kRoleProducer);
                         ok = false;
                         break;
                     }
-                    /* a stage holds up to Sub K blocks; the last of a tile may hold fewer */
-                    const int blocks = min(Sub, groups - kb);
+                    /* a stage holds up to Sub K blocks; the last of a range may hold fewer */
+                    const int blocks = min(Sub, kb1 - kb);
                     mbar_arrive_expect_tx(&full[stage], blocks * Layout::kBlockBytes);
                     for (int sub = 0; sub < blocks; ++sub) {
                         uint8_t *p_tile =
@@ -575,13 +590,15 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             uint32_t stage = 0, phase = 0, block = 0;
             bool ok = true;
             for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
-                for (int kb = 0; ok && kb < groups; kb += Sub) {
+                int kb0, kb1;
+                range(unit, kb0, kb1);
+                for (int kb = kb0; ok && kb < kb1; kb += Sub) {
                     if (!mbar_wait(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
                     }
-                    const int blocks = min(Sub, groups - kb);
+                    const int blocks = min(Sub, kb1 - kb);
                     for (int sub = 0; sub < blocks; ++sub, ++block) {
                         const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
                         if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
@@ -616,8 +633,9 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
         uint8_t *slab = staging + (warp - 2) * 4096;
         uint32_t block = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-            int rb, cb;
+            int rb, cb, kb0, kb1;
             decode(unit, rb, cb);
+            range(unit, kb0, kb1);
             const int row = rb * kBlockR + quarter * 32 + lane;
             float acc[64];
 #pragma unroll
@@ -626,12 +644,12 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             const float *lane_scale =
                 task.p_scale + static_cast<long long>(min(row, task.rows - 1)) * groups;
             const float *band_scale = task.q_scale + static_cast<long long>(cb) * groups;
-            float own = lane_scale[0], band = band_scale[0];
+            float own = lane_scale[kb0], band = band_scale[kb0];
             bool ok = true;
-            for (int kb = 0; kb < groups; ++kb, ++block) {
+            for (int kb = kb0; kb < kb1; ++kb, ++block) {
                 const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
                 const float s = __fmul_rn(own, band);
-                if (kb + 1 < groups) { /* next block's scales travel while this one is added */
+                if (kb + 1 < kb1) { /* next block's scales travel while this one is added */
                     own = lane_scale[kb + 1];
                     band = band_scale[kb + 1];
                 }
@@ -656,6 +674,22 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             }
             if (!ok)
                 break;
+            if (task.split > 1) {
+                /* FP32 sums of this K range: [range][row][column], 256 contiguous
+                 * bytes per thread; fp8_rows_reduce adds the ranges in order */
+                if (row < task.rows) {
+                    float *target = task.partial +
+                                    (static_cast<long long>(unit % task.split) * task.rows + row) *
+                                        task.cols +
+                                    cb * BN + half * 64;
+#pragma unroll
+                    for (int i = 0; i < 64; i += 4)
+                        if (cb * BN + half * 64 + i < task.cols)
+                            *reinterpret_cast<float4 *>(target + i) =
+                                make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                }
+                continue;
+            }
             /* this warp's 32 rows x 64 columns: one swizzled 4 KB slab, one TMA store */
             if (lane == 0)
                 tma_store_wait_read<0>();
@@ -684,6 +718,40 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+/* out[row][column] = rnd(sum over the K ranges, in order, of partial[range][row][column]);
+ * four columns per thread (cols is a multiple of eight). Launched as a
+ * programmatic dependent of fp8_block_rows. */
+__global__ void __launch_bounds__(256)
+    fp8_rows_reduce(int rows, int cols, int split, const float *partial, __nv_bfloat16 *out,
+                    long long ld_out)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const long long quads = static_cast<long long>(rows) * (cols >> 2);
+    const long long plane = static_cast<long long>(rows) * cols;
+    for (long long quad = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; quad < quads;
+         quad += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long row = quad / (cols >> 2);
+        const int column = static_cast<int>(quad - row * (cols >> 2)) << 2;
+        const float *source = partial + row * cols + column;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < split; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (s0 + i < split)
+                    v[i] = __ldcg(reinterpret_cast<const float4 *>(source + (s0 + i) * plane));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (s0 + i < split)
+                    sum.x += v[i].x, sum.y += v[i].y, sum.z += v[i].z, sum.w += v[i].w;
+        }
+        uint2 packed;
+        packed.x = sm100::pack_bf16(sum.x, sum.y);
+        packed.y = sm100::pack_bf16(sum.z, sum.w);
+        *reinterpret_cast<uint2 *>(out + row * ld_out + column) = packed;
     }
 }
 
@@ -842,10 +910,33 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
      * 128 x 128 row tiling would leave most SMs idle (32 tiles for N = 4096): those
      * shapes take the swapped kernel, one or two 64-token column blocks per weight
      * band with the K range split over the SMs. */
-    if (rows > std::min(kSwappedRowLimit, context->options.fp8_swapped_rows)) {
+    /* between 65 and 128 rows the swapped kernel reads the weights twice (two
+     * 64-token column blocks); it still wins while the 128 x 128 row tiling has
+     * few tiles to offer (measured: N = 2112 16 against 30 us, N = 7168 15
+     * against 12 us) */
+    const bool swapped = rows <= 64 || (rows <= std::min(kSwappedRowLimit,
+                                                         context->options.fp8_swapped_rows) &&
+                                        outputs <= 24 * 128);
+    if (!swapped) {
         task.rows = rows, task.cols = outputs;
         task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;
         task.split = 1, task.k_blocks_per_split = task.k_blocks;
+        /* few tiles and a long K: cut K into ranges, one unit each, summed by a
+         * second launch (the tiles of M = 128, N = 4096 alone fill 32 of 148 SMs) */
+        const int tiles = task.r_blocks * task.c_blocks;
+        if (context->options.fp8_rows == 0 && 2 * tiles <= context->sm_count && task.k_blocks >= 16 &&
+            outputs % 4 == 0) {
+            int split = host::choose_split(tiles, task.k_blocks * 2, context->sm_count);
+            task.k_blocks_per_split = (task.k_blocks + split - 1) / split;
+            task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
+            if (task.split > 1) {
+                int status = host::reserve_scratch(context,
+                                                   size_t(task.split) * rows * outputs * sizeof(float));
+                if (status != 0)
+                    return status;
+                task.partial = static_cast<float *>(context->scratch);
+            }
+        }
         task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
         task.p_scale = q_scale, task.q_scale = w_scale;
         bool ok = encode_2d(context, &p, type, 1, q, inner, rows, inner, 128, 128) &&
@@ -858,7 +949,7 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
         if (variant == 1) {
             launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
         } else {
-            const int units = task.r_blocks * task.c_blocks;
+            const int units = task.r_blocks * task.c_blocks * task.split;
             const int grid = units < context->sm_count ? units : context->sm_count;
             /* two K blocks per stage: 5 % faster than one (fewer barrier round trips) */
             if (variant == 2)
@@ -868,7 +959,26 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
                 fp8_block_rows<3, 2><<<grid, kRowsThreads, RowsSmem<3, 2>::kTotal, context->stream>>>(
                     p, qm, d, task);
         }
-        return host::launched(context, "tcgen05 FP8 block GEMM");
+        int status = host::launched(context, "tcgen05 FP8 block GEMM");
+        if (status != 0 || task.split == 1)
+            return status;
+        cudaLaunchConfig_t config = {};
+        const long long quads = 1ll * rows * (outputs / 4);
+        config.gridDim = dim3(unsigned(std::min<long long>((quads + 255) / 256, 4ll * context->sm_count)));
+        config.blockDim = dim3(256);
+        config.stream = context->stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        cudaError_t error =
+            cudaLaunchKernelEx(&config, fp8_rows_reduce, rows, outputs, task.split,
+                               static_cast<const float *>(task.partial), task.out, (long long)ldo);
+        if (error != cudaSuccess)
+            return host::fail(context, "FP8 K-range reduction", error);
+        context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+        return 0;
     }
     /* few tokens: weights on the 128-row side, tokens on the narrow side */
     task.rows = outputs, task.cols = rows;

@@ -73,7 +73,12 @@ constexpr int kFlagWords = 65536; /* word 0: delivery counter; word 1: CTAs of t
                                      done; words 64..: one arrival word per slab, then one
                                      word per slab counting the CTAs that have read it */
 constexpr int kFlagHeader = 64;
-constexpr int kMaxUnits = (kFlagWords - kFlagHeader) / 2;
+constexpr int kMaxUnits = 24576; /* slabs of the tile path: two words each from kFlagHeader on */
+/* The rest of the flag words belongs to the small all-reduce: three words per
+ * 2048-element chunk (arrived, consumed, pending). */
+constexpr int kSmallBase = kFlagHeader + 2 * kMaxUnits;
+constexpr int kSmallChunks = (kFlagWords - kSmallBase) / 3;
+constexpr int kSmallChunkElements = 2048; /* 256 threads x 8 BF16 */
 
 inline size_t slot_bytes(size_t capacity)
 {
@@ -248,6 +253,128 @@ __global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsi
 {
     if (threadIdx.x == 0)
         wait_delivered(delivered, expected, status, wait_ns);
+}
+
+/* ---- all-reduce of a small BF16 tensor through the peer regions -----------------
+ *
+ * For the few token rows of decoding the product is a weight-streaming kernel
+ * of some ten microseconds and its partial result is 16 KB to 1 MB; a library
+ * all-reduce then costs as much as the product (measured 11-17 us on two
+ * GPUs). This kernel is a one-shot exchange instead: every rank stores its
+ * tensor into slot `rank` of EVERY GPU's staging area (16-byte stores over
+ * NVLink), tells each GPU so, waits until all `world` tensors have arrived in
+ * its own staging area, adds them in rank order in FP32, rounds once and writes
+ * its own copy of the sum. All ranks add the same values in the same order, so
+ * they hold the same bits.
+ *
+ * The work is cut into chunks of 2048 elements, one CTA each, and every chunk
+ * synchronises on its own three flag words of the region, so no CTA depends on
+ * another CTA of its own GPU and nothing spans the grid:
+ *   arrived[c]   raised by each rank (release, system scope) once its copy of
+ *                chunk c is in this GPU's staging; the summing CTA waits for
+ *                `world` of them and clears the word;
+ *   consumed[c]  raised on every GPU by each rank once it has summed chunk c and
+ *                so no longer reads the copies it was sent; before a rank
+ *                overwrites its slot on its peers in the next call it waits until
+ *                its own word has reached `world`, and clears it;
+ *   pending[c]   local: whether a previous call left a `consumed` count to wait
+ *                for (zero after camblas_cuda_peer_alloc / peer_reset).
+ * Waits are bounded like the others; after one expires the words are undefined
+ * until camblas_cuda_peer_reset. `phases` 1 (wait consumed, store, announce) and
+ * 2 (wait arrived, add, announce consumed) can be issued separately so that one
+ * process can drive several ranks on one GPU in turn without any kernel waiting
+ * for an unlaunched one. */
+struct SmallTask {
+    int rank, world;
+    long long elements; /* multiple of 8 */
+    const __nv_bfloat16 *input;
+    __nv_bfloat16 *output;
+    __nv_bfloat16 *slot_at[kMaxWorld]; /* this rank's slot in every GPU's staging */
+    unsigned *flags_at[kMaxWorld];     /* every GPU's small-path words */
+    const __nv_bfloat16 *staging;      /* this GPU's staging slots */
+    long long slot_elements;
+    unsigned *flags;                   /* this GPU's small-path words */
+    unsigned *status;
+    unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(256) peer_small_allreduce(const SmallTask task, int phases)
+{
+    __shared__ int failed;
+    const int chunk = blockIdx.x;
+    const long long element = static_cast<long long>(chunk) * kSmallChunkElements + threadIdx.x * 8;
+    const bool live = element < task.elements;
+    unsigned *const arrived = task.flags + chunk;
+    unsigned *const consumed = task.flags + kSmallChunks + chunk;
+    unsigned *const pending = task.flags + 2 * kSmallChunks + chunk;
+    if (threadIdx.x == 0)
+        failed = 0;
+    __syncthreads();
+    if (phases & 1) {
+        if (threadIdx.x == 0 && *pending != 0u) {
+            /* the peers must be done with what this rank sent them last time */
+            if (sm100::flag_wait_system(consumed, unsigned(task.world), task.wait_ns)) {
+                sm100::flag_store_relaxed_system(consumed, 0u);
+                *pending = 0u;
+            } else {
+                atomicCAS(task.status, 0u, sm100::kRolePeerDelivered | (blockIdx.x << 4));
+                failed = 1;
+            }
+        }
+        __syncthreads();
+        if (failed)
+            return;
+        if (live) {
+            const uint4 mine = *reinterpret_cast<const uint4 *>(task.input + element);
+            for (int hop = 0; hop < task.world; ++hop) {
+                int target = task.rank + 1 + hop; /* peers first, own copy last */
+                if (target >= task.world)
+                    target -= task.world;
+                *reinterpret_cast<uint4 *>(task.slot_at[target] + element) = mine;
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < task.world)
+            sm100::flag_add_release_system(task.flags_at[threadIdx.x] + chunk, 1u);
+    }
+    if (phases & 2) {
+        if (threadIdx.x == 0) {
+            if (sm100::flag_wait_system(arrived, unsigned(task.world), task.wait_ns)) {
+                sm100::flag_store_relaxed_system(arrived, 0u);
+            } else {
+                atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
+                failed = 1;
+            }
+        }
+        __syncthreads();
+        if (failed)
+            return;
+        if (live) {
+            uint4 part[kMaxWorld];
+#pragma unroll
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < task.world)
+                    part[s] = __ldcg(reinterpret_cast<const uint4 *>(
+                        task.staging + s * task.slot_elements + element));
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < task.world)
+                    accumulate8(sum, part[s]);
+            uint4 packed;
+            packed.x = sm100::pack_bf16(sum[0], sum[1]);
+            packed.y = sm100::pack_bf16(sum[2], sum[3]);
+            packed.z = sm100::pack_bf16(sum[4], sum[5]);
+            packed.w = sm100::pack_bf16(sum[6], sum[7]);
+            *reinterpret_cast<uint4 *>(task.output + element) = packed;
+        }
+        __syncthreads(); /* every thread has its operands in registers */
+        if (threadIdx.x < task.world)
+            sm100::flag_add_release_system(task.flags_at[threadIdx.x] + kSmallChunks + chunk, 1u);
+        if (threadIdx.x == 0)
+            *pending = 1u;
+    }
 }
 
 struct Call {
@@ -461,6 +588,49 @@ extern "C" int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memo
         cudaError_t error = cudaMemsetAsync(region.flags, 0, size_t(peer::kFlagWords) * 4,
                                             context->stream);
         return error == cudaSuccess ? 0 : host::fail(context, "peer flag reset", error);
+    });
+}
+
+extern "C" int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, int rank, int world,
+                                                size_t capacity, void *const *memory, int phases,
+                                                size_t count, const void *input, void *output)
+{
+    return host::guarded(context, [&] {
+        if (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world || !memory ||
+            capacity == 0 || (phases & ~3) != 0 || phases == 0)
+            return host::fail(context, "invalid all-reduce group description", 1);
+        for (int r = 0; r < world; ++r)
+            if (!memory[r])
+                return host::fail(context, "missing peer region", 1);
+        if (count == 0)
+            return 0;
+        if (!input || !output || count % 8 != 0 || !host::aligned16(input) || !host::aligned16(output))
+            return host::fail(context,
+                              "peer all-reduce needs 16-byte aligned BF16 buffers of a multiple of 8 elements",
+                              1);
+        const size_t chunks = (count + peer::kSmallChunkElements - 1) / peer::kSmallChunkElements;
+        if (count > capacity || chunks > size_t(peer::kSmallChunks))
+            return host::fail(context, "peer all-reduce exceeds the region capacity or 11 million elements",
+                              1);
+        peer::SmallTask task{};
+        task.rank = rank, task.world = world;
+        task.elements = static_cast<long long>(count);
+        task.input = static_cast<const __nv_bfloat16 *>(input);
+        task.output = static_cast<__nv_bfloat16 *>(output);
+        for (int r = 0; r < world; ++r) {
+            const peer::Region region = peer::carve(memory[r], world, capacity);
+            task.slot_at[r] = region.staging + size_t(rank) * region.slot_elements;
+            task.flags_at[r] = region.flags + peer::kSmallBase;
+            if (r == rank) {
+                task.staging = region.staging;
+                task.slot_elements = static_cast<long long>(region.slot_elements);
+                task.flags = region.flags + peer::kSmallBase;
+            }
+        }
+        task.status = context->status;
+        task.wait_ns = 1000000ull * unsigned(context->options.peer_wait_ms);
+        peer::peer_small_allreduce<<<unsigned(chunks), 256, 0, context->stream>>>(task, phases);
+        return host::launched(context, "peer all-reduce");
     });
 }
 

@@ -201,6 +201,24 @@ class PeerRegions:
                     (r2.stride(0) if rows > 1 else outputs) if r2 is not None else 0)
         return self.result(rows, outputs)
 
+    def all_reduce(self, tensor, out=None, phases=3):
+        """Sum a small contiguous BF16 tensor over the ranks; returns the sum (``out`` or new).
+
+        One kernel per rank over peer memory (``camblas_cuda_peer_allreduce_bf16``):
+        FP32 sum in rank order, one rounding, identical bits on every rank. The
+        element count must be a multiple of 8 and fit the regions' capacity.
+        """
+        if tensor.dtype != torch.bfloat16 or not tensor.is_contiguous():
+            raise ValueError("the peer all-reduce takes a contiguous BF16 tensor")
+        if tensor.numel() % 8 or tensor.numel() > self.capacity:
+            raise ValueError("element count must be a multiple of 8 within the region capacity")
+        if out is None:
+            out = torch.empty_like(tensor)
+        native = self._native(self.device)
+        native.call("peer_allreduce_bf16", self.rank, self.world, self.capacity, self._array, phases,
+                    tensor.numel(), tensor.data_ptr(), out.data_ptr())
+        return out
+
     def reset(self):
         """Clear this rank's flag words (after a failed call; all ranks idle)."""
         self._native(self.device).call("peer_reset", self._owned, self.world, self.capacity)
@@ -256,8 +274,10 @@ class RowParallelLinear:
         return x[..., self.bounds[0]:self.bounds[1]].contiguous()
 
     # Below this many token rows the product is a weight-streaming kernel (GEMV or
-    # swapped tcgen05) and the payload of the sum is at most 1 MB: the NCCL path is used.
-    # The peer-memory path multiplies with 256-row tiles, which is what prefill needs.
+    # swapped tcgen05) and the payload of the sum is at most 1 MB: the partial results
+    # meet in the one-shot peer all-reduce. From here on the peer-memory path multiplies
+    # with 256-row tiles and exchanges them from the GEMM epilogue, which is what
+    # prefill needs.
     PEER_ROWS = 65
 
     def __call__(self, x_local):
@@ -269,5 +289,8 @@ class RowParallelLinear:
                                      self.full_bias)
         partial = self.linear(x_local, self.weight, self.bias)
         if self.world > 1:
+            if (self.peers is not None and partial.dtype == torch.bfloat16 and partial.is_cuda
+                    and partial.numel() % 8 == 0 and partial.numel() <= self.peers.capacity):
+                return self.peers.all_reduce(partial, out=partial)
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
         return partial

@@ -237,6 +237,25 @@ int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, 
                                        const void *w, int ldw, const void *bias,
                                        const void *residual, int ldr);
 
+/* No counterpart in the reference (SGLang's all-reduce follows the hooked
+ * F.linear there). Sum of one BF16 tensor of `count` elements per rank over
+ * the ranks of a peer-region group, for the small results of decoding (a few
+ * token rows): output = rnd(input_0 + input_1 + ... in rank order, FP32), the
+ * same bits on every rank. One kernel per rank on the context's stream: it
+ * stores `input` into this rank's staging slot on every GPU over NVLink, waits
+ * (bounded, "peer_wait_ms") until all ranks' copies have arrived in its own
+ * region, and adds them; chunks of 2048 elements synchronise on their own flag
+ * words, so the exchange needs no collective library and no second launch. All
+ * ranks must make the same sequence of calls with the same count. count is a
+ * multiple of 8, at most min(capacity, 11 141 120); input and output 16-byte
+ * aligned, output may be input. `phases` is 3 in production; 1 (send) and 2
+ * (receive and add) exist so that one process can drive several ranks on one
+ * GPU in turn. After a wait has expired (device status) the region needs
+ * camblas_cuda_peer_reset. */
+int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, int rank, int world,
+                                     size_t capacity, void *const *memory, int phases,
+                                     size_t count, const void *input, void *output);
+
 /* ---- residual add + RMS normalisation ---------------------------------- */
 
 /* Replaces camblas_cuda_rms_norm (camblas_cuda.h:171-175; backend.cu:1423-1440).

@@ -51,6 +51,26 @@ def main():
     for other in gathered:
         assert torch.equal(other, results[0]), "ranks hold different results"
 
+    # decode-sized rows: product, then the one-shot peer all-reduce instead of NCCL's
+    for tokens in (1, 16, 64):
+        x_small = torch.randn((tokens, inner), generator=generator).bfloat16().cuda()
+        local = fused.slice_input(x_small)
+        summed = [fused(local).clone() for _ in range(3)]
+        reference = plain(local)
+        torch.cuda.synchronize()
+        assert _native.context(device).device_status() == 0
+        for repeat in summed[1:]:
+            assert torch.equal(repeat, summed[0]), "repeated small all-reduces differ"
+        error = (summed[0].float() - reference.float()).norm() / reference.float().norm()
+        assert error.item() <= 1e-2, f"small all-reduce against NCCL {error.item():.3e}"
+        whole = _kernels.linear(x_small, w, bias).float()
+        error = (summed[0].float() - whole).norm() / whole.norm()
+        assert error.item() <= 1e-2, f"small all-reduce against the unsharded product {error.item():.3e}"
+        gathered = [torch.empty_like(summed[0]) for _ in range(world)]
+        dist.all_gather(gathered, summed[0])
+        for other in gathered:
+            assert torch.equal(other, summed[0]), "ranks hold different sums"
+
     torch.cuda.synchronize()
     dist.barrier()
     peers.close(free=False)  # unmap the others' regions before anyone frees its own

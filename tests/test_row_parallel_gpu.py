@@ -215,3 +215,46 @@ def test_expired_wait_reports_and_reset_recovers():
         close_all(views)
     for r in range(world):
         assert np.array_equal(again[r], good[r])
+
+
+@pytest.mark.parametrize("world,count", [(1, 8192), (2, 8), (2, 8192), (4, 64 * 8192), (8, 16 * 8192),
+                                         (8, 3 * 2048 + 264)])
+def test_small_all_reduce_sums_in_rank_order(world, count):
+    """`camblas_cuda_peer_allreduce_bf16` with emulated ranks: every rank's result is the FP32
+    sum of the ranks' tensors in rank order, rounded once - bit for bit - and stays so over
+    repeated calls (the flag words hand themselves back), in place as well. The two phases
+    of the ranks are issued in turn so that no kernel waits for an unlaunched one."""
+    torch.manual_seed(705537 + world + count)
+    capacity = PeerRegions.capacity_for(64, 8192)
+    views = PeerRegions.emulate(capacity, world, 0)
+    try:
+        for call in range(3):
+            inputs = [torch.randn(count, device="cuda").bfloat16() for _ in range(world)]
+            total = torch.zeros(count, device="cuda")
+            for tensor in inputs:
+                total = total + tensor.float()
+            expected = total.bfloat16()
+            outputs = [tensor.clone() if call == 2 else torch.empty_like(tensor) for tensor in inputs]
+            sources = outputs if call == 2 else inputs  # third call: in place
+            for phase in (1, 2):
+                for view, source, output in zip(views, sources, outputs):
+                    view.all_reduce(source, out=output, phases=phase)
+            torch.cuda.synchronize()
+            assert _native.context(0).device_status() == 0
+            for output in outputs:
+                assert torch.equal(output, expected)
+    finally:
+        close_all(views)
+
+
+def test_small_all_reduce_rejects_what_it_cannot_take():
+    views = PeerRegions.emulate(PeerRegions.capacity_for(1, 8), 2, 0)
+    try:
+        with pytest.raises(ValueError):
+            views[0].all_reduce(torch.zeros(12, device="cuda", dtype=torch.bfloat16))
+        with pytest.raises(ValueError):
+            views[0].all_reduce(torch.zeros(16, device="cuda"))
+        with pytest.raises(ValueError):
+            views[0].all_reduce(torch.zeros(256 * 256 + 8, device="cuda", dtype=torch.bfloat16))
+    finally:
+        close_all(views)
