@@ -922,9 +922,11 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
         task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;
         task.split = 1, task.k_blocks_per_split = task.k_blocks;
         /* few tiles and a long K: cut K into ranges, one unit each, summed by a
-         * second launch (the tiles of M = 128, N = 4096 alone fill 32 of 148 SMs) */
+         * second launch (the tiles of M = 128, N = 4096 alone fill 32 of 148 SMs:
+         * 22 against 30 us). With half the SMs busy or a short K the second launch
+         * costs more than it recovers (N = 7168, K = 2048: 15.6 against 12.1 us). */
         const int tiles = task.r_blocks * task.c_blocks;
-        if (context->options.fp8_rows == 0 && 2 * tiles <= context->sm_count && task.k_blocks >= 16 &&
+        if (context->options.fp8_rows == 0 && 3 * tiles <= context->sm_count && task.k_blocks >= 32 &&
             outputs % 4 == 0) {
             int split = host::choose_split(tiles, task.k_blocks * 2, context->sm_count);
             task.k_blocks_per_split = (task.k_blocks + split - 1) / split;
