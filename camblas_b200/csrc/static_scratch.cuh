@@ -5,11 +5,9 @@
  * Who needs it. The ordinary entry points grow a per-context scratch arena
  * with cudaMalloc the first time a K split needs it, and a context itself is
  * created with cudaMalloc. Some callers cannot do either at the point where
- * they need the product: code running while its stream is being captured into
- * a CUDA graph (allocation is illegal there), serving processes that hand all
- * device memory to their own pool at start-up and forbid later driver
- * allocations, and real-time paths where the latency of an allocation is not
- * acceptable. This entry point takes no context and touches no allocator: the
+ * they need the product: serving processes that hand all device memory to their
+ * own pool at start-up and forbid later driver allocations, and real-time paths
+ * where the latency of an allocation is not acceptable. This entry point takes no context and touches no allocator: the
  * FP32 partial sums of the K split live in a fixed array that is part of the
  * library image, so every GPU that loads the library holds those 8 MiB until
  * the process exits.

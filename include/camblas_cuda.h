@@ -123,10 +123,9 @@ int camblas_cuda_qkv_linear_bf16(camblas_cuda_context *context, int rows, int in
 /* Has no counterpart in the reference. A linear layer for one to four token
  * rows, out[rows,outputs] = x[rows,inner] . w[outputs,inner]^T (row strides
  * ldx/ldw/ldo in elements, BF16, FP32 accumulation, one rounding), for callers
- * that may not allocate device memory when they need the product: code that
- * runs while its stream is under CUDA-graph capture, processes whose own
- * memory pool owns the whole device and forbids later driver allocations, and
- * latency-bound paths. It takes a cudaStream_t (as void*) instead of a context,
+ * that may not allocate device memory when they need the product: processes
+ * whose own memory pool owns the whole device and forbids later driver
+ * allocations, and latency-bound paths that cannot absorb an allocation. It takes a cudaStream_t (as void*) instead of a context,
  * runs on the calling thread's current device, and calls no allocator: the FP32
  * partial sums of its K split live in a fixed 8 MiB array inside the library
  * image (held by every GPU that loads the library until the process exits).

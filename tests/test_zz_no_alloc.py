@@ -1,8 +1,8 @@
 """The allocation-free few-token linear entry point against the ordinary one.
 
 `camblas_cuda_linear_bf16_static` serves callers that may not allocate device
-memory at the moment they need a product - a stream under CUDA-graph capture, a
-process whose own memory pool owns the device, a latency-bound path - by
+memory at the moment they need a product - a process whose own memory pool owns
+the device, a latency-bound path that cannot absorb an allocation - by
 keeping the split-K partial sums in a fixed array inside the library instead of
 a `cudaMalloc`-grown arena. It must give what `camblas_cuda_linear_bf16` gives.
 The two are compared within the BF16 tolerance of the other GEMM tests (rel-L2
