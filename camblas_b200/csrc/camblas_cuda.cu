@@ -8,6 +8,7 @@
 #include "context.cuh"
 #include "dispatch_bf16.cuh"
 #include "fp8_block.cuh"
+#include "gemm_simt.cuh"
 #include "quantized.cuh"
 #include "rms_norm.cuh"
 #include "row_parallel.cuh"
@@ -179,6 +180,7 @@ extern "C" int camblas_cuda_set_option(camblas_cuda_context *context, const char
         {"push_width", &options.push_width, 0, 256},
         {"fp8_rows", &options.fp8_rows, 0, 2},
         {"fp8_swapped_rows", &options.fp8_swapped_rows, 64, 128},
+        {"cluster_split", &options.cluster_split, 0, 2},
         {"bf16_strassen", &options.bf16_strassen, 0, 1},
         {"peer_wait_ms", &options.peer_wait_ms, 1, 60000},
     };
@@ -750,15 +752,59 @@ extern "C" int camblas_cuda_swiglu(camblas_cuda_context *context, int dtype, uin
 
 /* ---- exported for link compatibility only ---- */
 
-extern "C" int camblas_cuda_sgemm(camblas_cuda_context *context, char, char, int, int, int, float,
-                                  const float *, int, const float *, int, float, float *, int)
+namespace
 {
-    return host::unavailable(context, "camblas_cuda_sgemm");
+/* FP32 / FP64 GEMM with the argument rules of the reference's gemm<T>
+ * (backend.cu:786-806). */
+template <typename T>
+int simt_gemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n, int k, T alpha,
+              const T *a, int lda, const T *b, int ldb, T beta, T *c, int ldc)
+{
+    return guarded(context, [&] {
+        const bool na = trans_a == 'N' || trans_a == 'n', ta = trans_a == 'T' || trans_a == 't';
+        const bool nb = trans_b == 'N' || trans_b == 'n', tb = trans_b == 'T' || trans_b == 't';
+        if ((!na && !ta) || (!nb && !tb) || m < 0 || n < 0 || k < 0 || lda < 1 || ldb < 1 || ldc < 1)
+            return fail(context, "invalid GEMM arguments", 1);
+        if (m == 0 || n == 0)
+            return 0;
+        if (!c || lda < std::max(1, na ? m : k) || ldb < std::max(1, nb ? k : n) || ldc < m)
+            return fail(context, "invalid device pointer or leading dimension", 1);
+        if (alpha == T(0) || k == 0) {
+            if (beta == T(1))
+                return 0;
+            simt::scale_window<T><<<unsigned((size_t(m) * n + 255) / 256), 256, 0, context->stream>>>(
+                m, n, beta, c, ldc);
+            return launched(context, "scale output");
+        }
+        if (!a || !b || a == c || b == c)
+            return fail(context, "missing or aliased GEMM operand", 1);
+        simt::Task<T> task{};
+        task.m = m, task.n = n, task.k = k;
+        task.ta = ta, task.tb = tb;
+        task.lda = lda, task.ldb = ldb, task.ldc = ldc;
+        task.alpha = alpha, task.beta = beta;
+        task.a = a, task.b = b, task.c = c;
+        dim3 grid((m + simt::kTileM - 1) / simt::kTileM, (n + simt::kTileN - 1) / simt::kTileN);
+        if (grid.y > 65535)
+            return fail(context, "GEMM column count", 1);
+        context->counts[0]++;
+        simt::gemm_simt<T><<<grid, 256, 0, context->stream>>>(task);
+        return launched(context, "classical GEMM");
+    });
 }
-extern "C" int camblas_cuda_dgemm(camblas_cuda_context *context, char, char, int, int, int, double,
-                                  const double *, int, const double *, int, double, double *, int)
+} // namespace
+
+extern "C" int camblas_cuda_sgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m,
+                                  int n, int k, float alpha, const float *a, int lda, const float *b,
+                                  int ldb, float beta, float *c, int ldc)
 {
-    return host::unavailable(context, "camblas_cuda_dgemm");
+    return simt_gemm<float>(context, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+}
+extern "C" int camblas_cuda_dgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m,
+                                  int n, int k, double alpha, const double *a, int lda,
+                                  const double *b, int ldb, double beta, double *c, int ldc)
+{
+    return simt_gemm<double>(context, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
 }
 extern "C" int camblas_cuda_affine(camblas_cuda_context *context, int, int, int, int, const void *,
                                    const void *, const void *, int, void *)

@@ -39,6 +39,8 @@ struct ContextOptions {
                               many-row FP8 kernels, which give the same bits */
     int fp8_swapped_rows = 128; /* "fp8_swapped_rows": most token rows the weight-streaming
                                    (swapped, split-K) FP8 modes take, 64 or 128 */
+    int cluster_split = 1; /* "cluster_split": K split inside a thread-block cluster: 0 never,
+                              1 for row tiles (65 rows and more), 2 also for few-token tiles */
     int bf16_strassen = 0; /* "bf16_strassen" (CAMBLAS_B200_BF16_STRASSEN=1): let policy STRASSEN
                               run one Strassen level on BF16 squares */
     int peer_wait_ms = 5000; /* "peer_wait_ms": how long a kernel waits for another GPU's flag */
@@ -81,6 +83,9 @@ struct camblas_cuda_context {
     static constexpr int kMapSlots = 128;
     TensorMapEntry maps[kMapSlots];
     uint64_t map_hits = 0, map_misses = 0;
+    /* clusters of each cluster-split kernel the device keeps resident, by kernel
+     * slot and cluster size (0 not asked yet, -1 none) */
+    int cluster_capacity[5][9] = {};
     std::atomic<uint64_t> counts[8] = {};
     std::atomic<uint64_t> kernel_launches{0}; /* every kernel this context put on its stream */
     char error[256] = "";

@@ -19,6 +19,7 @@
 #pragma once
 
 #include "context.cuh"
+#include "gemm_bf16_cluster.cuh"
 #include "gemm_bf16_pair.cuh"
 #include "gemm_bf16_tcgen05.cuh"
 #include "gemm_generic.cuh"
@@ -90,10 +91,22 @@ template <int PMajor, int QMajor> int prepare_pair_kernels()
     return status;
 }
 
+template <int BN, int Stages, int Mode> int prepare_cluster_kernel()
+{
+    return int(cudaFuncSetAttribute(sm100::gemm_bf16_cluster<BN, Stages, Mode>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    sm100::GemmSmem<BN, Stages, sm100::kStoreColumns>::kTotal));
+}
+
 inline int prepare_kernels()
 {
     using namespace sm100;
     int status = prepare_row_kernels<kMajorK, kMajorK>();
+    status |= prepare_cluster_kernel<256, 4, kStoreRows>();
+    status |= prepare_cluster_kernel<128, 6, kStoreRows>();
+    status |= prepare_cluster_kernel<16, 8, kStoreColumns>();
+    status |= prepare_cluster_kernel<32, 8, kStoreColumns>();
+    status |= prepare_cluster_kernel<64, 8, kStoreColumns>();
     status |= prepare_pair_kernels<kMajorK, kMajorK>();
     status |= prepare_pair_kernels<kMajorK, kMajorMN>();
     status |= prepare_pair_kernels<kMajorMN, kMajorK>();
@@ -190,6 +203,80 @@ inline int choose_split(int tiles, int k_blocks, int sms)
     return best;
 }
 
+/* ---- K split inside a cluster (gemm_bf16_cluster.cuh) ---- */
+
+template <int BN, int Stages, int Mode>
+cudaLaunchConfig_t cluster_config(camblas_cuda_context *context, int tiles, int parts,
+                                  cudaLaunchAttribute *attribute)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(unsigned(tiles) * unsigned(parts));
+    config.blockDim = dim3(sm100::kThreads);
+    config.dynamicSmemBytes = sm100::GemmSmem<BN, Stages, sm100::kStoreColumns>::kTotal;
+    config.stream = context->stream;
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = unsigned(parts);
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return config;
+}
+
+/* How many clusters of `parts` CTAs of this kernel the device runs at once (a
+ * cluster lives inside one GPC, so this is less than SMs / parts); asked once
+ * per kernel and size, kept in the context. */
+template <int BN, int Stages, int Mode>
+int resident_clusters(camblas_cuda_context *context, int slot, int parts)
+{
+    int &cached = context->cluster_capacity[slot][parts];
+    if (cached == 0) {
+        cudaLaunchAttribute attribute[1];
+        cudaLaunchConfig_t config = cluster_config<BN, Stages, Mode>(context, 1, parts, attribute);
+        int clusters = 0;
+        cudaError_t error = cudaOccupancyMaxActiveClusters(
+            &clusters, sm100::gemm_bf16_cluster<BN, Stages, Mode>, &config);
+        if (error != cudaSuccess) {
+            cudaGetLastError();
+            clusters = 0;
+        }
+        cached = clusters > 0 ? clusters : -1;
+    }
+    return cached > 0 ? cached : 0;
+}
+
+/* Largest cluster size (2..8) whose clusters for all `tiles` are resident
+ * together and whose K ranges keep at least four K blocks; 0 when the tiles
+ * would still occupy less than half of the SMs, or when switched off. */
+template <int BN, int Stages, int Mode>
+int choose_cluster_parts(camblas_cuda_context *context, int slot, int tiles, int k_blocks)
+{
+    if (context->options.cluster_split == 0)
+        return 0;
+    for (int parts = 8; parts >= 2; --parts) {
+        if (k_blocks / parts < 4 || 1ll * tiles * parts > context->sm_count)
+            continue;
+        if (resident_clusters<BN, Stages, Mode>(context, slot, parts) < tiles)
+            continue;
+        return 2 * tiles * parts >= context->sm_count ? parts : 0;
+    }
+    return 0;
+}
+
+template <int BN, int Stages, int Mode>
+int launch_cluster(camblas_cuda_context *context, int tiles, int parts, const CUtensorMap &p,
+                   const CUtensorMap &q, const sm100::GemmTask &task)
+{
+    cudaLaunchAttribute attribute[1];
+    cudaLaunchConfig_t config = cluster_config<BN, Stages, Mode>(context, tiles, parts, attribute);
+    cudaError_t error =
+        cudaLaunchKernelEx(&config, sm100::gemm_bf16_cluster<BN, Stages, Mode>, p, q, task);
+    if (error != cudaSuccess)
+        return fail(context, "cluster split-K tcgen05 BF16 GEMM", error);
+    context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    return 0;
+}
+
 /* Whether a K split pays at all. The split buys a better fill of the SMs and
  * costs a second launch plus a write and a read of `split` FP32 copies of the
  * result. Rough microseconds for a weight-streaming tile of 128 rows by `bn`
@@ -247,6 +334,30 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
     }
     task.c_blocks = (x.m + bn - 1) / bn;
     task.panel = task.r_blocks < 8 ? task.r_blocks : 8;
+    /* Few tiles and a long K in the layout of a linear layer: one cluster per
+     * tile, K split over its CTAs, sums through distributed shared memory: one
+     * launch, no scratch, 2-5 % faster than the stream-K pieces on the QKV shards
+     * of tensor-parallel ranks (23.1 against 23.8 us at 512 x 8192 -> 1280). Both
+     * forms pull the same 126 MB through L2 for that product, which is what
+     * bounds them. */
+    if (x.ta && !x.tb && x.run_if_set == nullptr && bn >= 128 && task.k_blocks >= 16) {
+        const int tiles = task.r_blocks * task.c_blocks;
+        const int parts = bn == 256 ? choose_cluster_parts<256, 4, sm100::kStoreRows>(
+                                          context, 0, tiles, task.k_blocks)
+                                    : choose_cluster_parts<128, 6, sm100::kStoreRows>(
+                                          context, 1, tiles, task.k_blocks);
+        if (parts >= 2) {
+            task.out1 = x.c1, task.out2 = x.c2;
+            task.ld_out1 = x.ldc1, task.ld_out2 = x.ldc2;
+            CUtensorMap p, q;
+            const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            if (!encode_2d(context, &p, bf16, 2, x.b, x.k, x.n, x.ldb * 2, 64, 128) ||
+                !encode_2d(context, &q, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, bn))
+                return fail(context, "tensor map encoding", 1);
+            return bn == 256 ? launch_cluster<256, 4, sm100::kStoreRows>(context, tiles, parts, p, q, task)
+                             : launch_cluster<128, 6, sm100::kStoreRows>(context, tiles, parts, p, q, task);
+        }
+    }
     if (task.r_blocks <= 8 && sms / task.r_blocks >= 2) {
         const int teams = sms / task.r_blocks;
         const int rest = task.c_blocks % teams;
@@ -588,6 +699,34 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     task.status = context->status;
     task.cut0 = task.cut1 = x.m;
     task.batch = 1;
+    if (task.split > 1 && context->options.cluster_split == 2) {
+        /* The split inside a cluster needs neither scratch nor a second launch, but
+         * for few tokens the partial sums are small and the second launch is a
+         * programmatic dependent: measured on the Llama down projection it is 1-3 %
+         * slower than the scratch route (16 tokens 78.4 against 77.5 us), so it is
+         * taken here only on request. */
+        const int tiles = task.r_blocks * task.c_blocks;
+        int parts = 0;
+        if (bn == 16)
+            parts = choose_cluster_parts<16, 8, sm100::kStoreColumns>(context, 2, tiles, task.k_blocks);
+        else if (bn == 32)
+            parts = choose_cluster_parts<32, 8, sm100::kStoreColumns>(context, 3, tiles, task.k_blocks);
+        else
+            parts = choose_cluster_parts<64, 8, sm100::kStoreColumns>(context, 4, tiles, task.k_blocks);
+        if (parts >= 2) {
+            task.split = 1, task.k_blocks_per_split = task.k_blocks;
+            CUtensorMap p, q;
+            const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            if (!encode_2d(context, &p, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, 128) ||
+                !encode_2d(context, &q, bf16, 2, x.b, x.k, x.n, x.ldb * 2, 64, bn))
+                return fail(context, "tensor map encoding", 1);
+            if (bn == 16)
+                return launch_cluster<16, 8, sm100::kStoreColumns>(context, tiles, parts, p, q, task);
+            if (bn == 32)
+                return launch_cluster<32, 8, sm100::kStoreColumns>(context, tiles, parts, p, q, task);
+            return launch_cluster<64, 8, sm100::kStoreColumns>(context, tiles, parts, p, q, task);
+        }
+    }
     long long plane = 1ll * task.r_blocks * 128;
     if (task.split > 1) {
         size_t bytes = size_t(task.split) * x.n * plane * sizeof(float);

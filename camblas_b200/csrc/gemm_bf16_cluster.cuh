@@ -1,0 +1,359 @@
+/*
+ * BF16 GEMM for products with few tiles and a long K: the K range of every tile
+ * is split over the CTAs of a thread-block cluster and the partial accumulators
+ * are added through distributed shared memory.
+ *
+ * The other kernels of this library handle "fewer tiles than SMs" by writing
+ * FP32 partial sums to global scratch and adding them in a second launch
+ * (kStorePartial + gemm_split_reduce, the stream-K pieces + sk_fixup). For the
+ * shapes where that matters - a few token rows against a Llama-sized weight,
+ * the QKV shard of a rank at tensor-parallel 4 or 8 - the second launch and the
+ * scratch round trip cost as much as the multiplication. Here a cluster of S
+ * CTAs (2..8) owns one 128 x BN tile: CTA p multiplies K range p into its own
+ * tensor memory exactly as gemm_bf16_tcgen05 does (TMA producer warp, MMA
+ * issuer warp, four epilogue warps), and then
+ *   1. every CTA tells every other that its MMAs are complete, i.e. that its
+ *      operand ring is idle (one remote mbarrier arrival per pair);
+ *   2. every epilogue warp reads its 32 accumulator rows from tensor memory and
+ *      stores each row into the operand ring of the CTA that OWNS that row
+ *      (row i of the tile belongs to CTA i*S/128), slot p of that CTA's inbox,
+ *      with st.shared::cluster; then it arrives on every CTA's inbox barrier
+ *      (release at cluster scope);
+ *   3. every CTA waits for the 4*S arrivals on its own inbox barrier (acquire at
+ *      cluster scope), adds the S slots of its rows in K order in FP32, applies
+ *      alpha, bias and beta*addend, rounds once and stores its rows.
+ * One tile per cluster, so the ring is never needed again after step 1 and no
+ * further hand-shake is required: after step 3 nothing remote touches the CTA
+ * (all arrivals on its barriers and all stores into its inbox precede the
+ * completion of its inbox barrier), so it may exit at once.
+ *
+ * The sums are added in ascending K order by exactly one CTA per row, so results
+ * are repeatable; every wait is bounded as elsewhere, and because the only
+ * hardware cluster barrier is the one after set-up, a CTA that gives up cannot
+ * leave the others waiting for longer than their own limits.
+ *
+ * Mode kStoreRows: D[R,C] row-major (tokens on the tile rows), optional second
+ * and third outputs of a packed projection. Mode kStoreColumns: operands
+ * swapped (weights on the tile rows, up to 64 tokens on the columns), D^T stored.
+ */
+#pragma once
+
+#include "gemm_bf16_pair.cuh"
+
+namespace sm100
+{
+
+__device__ __forceinline__ uint32_t cluster_size()
+{
+    uint32_t size;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(size));
+    return size;
+}
+
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_address, float a, float b, float c,
+                                              float d)
+{
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_address), "f"(a),
+                 "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_cluster()
+{
+    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
+
+/* Bounded wait whose completion makes the shared-memory stores of other CTAs of
+ * the cluster, released before their arrivals, visible to this thread. */
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity,
+                                                  volatile uint32_t *abort)
+{
+    unsigned long long started = 0;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile("{\n"
+                     ".reg .pred p;\n"
+                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n"
+                     "}\n"
+                     : "=r"(done)
+                     : "r"(smem_u32(bar)), "r"(parity)
+                     : "memory");
+        if (done)
+            return true;
+        if ((spin & 255u) == 255u) {
+            if (*abort)
+                return false;
+            const unsigned long long now = global_timer_ns();
+            if (started == 0)
+                started = now;
+            else if (now - started > kWaitLimitNs)
+                return false;
+        }
+    }
+    return false;
+}
+
+constexpr int kInboxPad = 4; /* floats added to an inbox row: keeps 16-byte alignment, spreads banks */
+
+/* First tile row owned by CTA `part` of `parts`: rows are dealt out in
+ * contiguous, nearly equal ranges. */
+__host__ __device__ constexpr int cluster_first_row(int part, int parts)
+{
+    return (part * kBlockR + parts - 1) / parts;
+}
+
+template <int BN, int Stages, int Mode>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_bf16_cluster(const __grid_constant__ CUtensorMap map_p,
+                      const __grid_constant__ CUtensorMap map_q, const GemmTask task)
+{
+    static_assert(Mode == kStoreRows || Mode == kStoreColumns, "cluster split: rows or swapped");
+    using Layout = GemmSmem<BN, Stages, kStoreColumns>; /* ring + barriers, no staging buffers */
+    constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
+    constexpr int kPitch = BN + kInboxPad; /* floats per inbox row */
+    static_assert((kBlockR + 8) * kPitch * 4 <= Stages * Layout::kStageBytes,
+                  "the inbox fits in the operand ring");
+
+    extern __shared__ uint8_t raw_smem[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + Stages * Layout::kStageBytes);
+    uint64_t *empty = full + Stages;
+    uint64_t *tmem_full = empty + Stages;
+    uint64_t *all_done = tmem_full + 1;   /* S arrivals: every CTA's MMAs are complete */
+    uint64_t *inbox_full = all_done + 1;  /* 4*S arrivals: every warp of every CTA has delivered */
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(inbox_full + 1);
+    volatile uint32_t *abort = tmem_slot + 1;
+    float *inbox = reinterpret_cast<float *>(smem); /* [S slots][rows owned][kPitch], over the ring */
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int parts = static_cast<int>(cluster_size());
+    const int part = static_cast<int>(cluster_rank());
+    int rb, cb, batch;
+    locate_tile(task, blockIdx.x / parts, rb, cb, batch);
+    const int per_part = (task.k_blocks + parts - 1) / parts;
+    const int kb0 = min(task.k_blocks, part * per_part), kb1 = min(task.k_blocks, kb0 + per_part);
+    const int rows_owned_max = (kBlockR + parts - 1) / parts;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(all_done, parts);
+        mbar_init(inbox_full, 4 * parts);
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync(); /* every CTA's barriers exist before any remote arrival */
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            /* ---- producer: this CTA's K range of the tile ---- */
+            const uint64_t keep = policy_evict_last(), stream = policy_evict_first();
+            /* swapped: P is the weight, read once; rows: Q is the weight */
+            const uint64_t policy_p = Mode == kStoreColumns ? stream : keep;
+            const uint64_t policy_q = Mode == kStoreColumns ? keep : stream;
+            uint32_t stage = 0, phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                    report(task.status, abort, kRoleProducer);
+                    break;
+                }
+                uint8_t *p_tile = smem + stage * Layout::kStageBytes;
+                mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
+                tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockK, rb * kBlockR, policy_p);
+                tma_load_2d_hint(p_tile + Layout::kPBytes, &map_q, &full[stage], kb * kBlockK, cb * BN,
+                                 policy_q);
+                if (++stage == Stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            /* ---- MMA issuer ---- */
+            constexpr uint32_t idesc = make_idesc(1, kBlockR, BN, kMajorK, kMajorK);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(&full[stage], phase, abort)) {
+                    report(task.status, abort, kRoleMma);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                const uint32_t q_address = p_address + Layout::kPBytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / kUmmaK; ++k)
+                    umma_f16(tmem_base, desc_kmajor_sw128(p_address) + 2 * k,
+                             desc_kmajor_sw128(q_address) + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[stage]);
+                if (++stage == Stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok) {
+                if (kb1 > kb0)
+                    umma_commit(tmem_full);
+                else
+                    mbar_arrive(tmem_full); /* an empty K range: nothing to wait for */
+            }
+        }
+    } else {
+        /* ---- epilogue warps: exchange, then finish the rows this CTA owns ---- */
+        const int quarter = warp & 3;
+        bool ok = mbar_wait(tmem_full, 0, abort);
+        if (!ok)
+            report(task.status, abort, kRoleEpilogueFull);
+        tcgen05_fence_after();
+        if (ok && warp == 2 && lane < parts)
+            mbar_arrive_cluster(map_to_rank(smem_u32(all_done), lane));
+        if (ok && !mbar_wait_cluster(all_done, 0, abort)) {
+            report(task.status, abort, kRoleDrain);
+            ok = false;
+        }
+        if (ok) {
+            /* step 2: this lane's accumulator row to its owner's inbox, slot `part` */
+            const int row = quarter * 32 + lane; /* row of the tile */
+            const int owner = (row * parts) / kBlockR;
+            const int local_row = row - cluster_first_row(owner, parts);
+            const uint32_t target =
+                map_to_rank(smem_u32(inbox + (part * rows_owned_max + local_row) * kPitch), owner);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            constexpr int kPiece = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / kPiece; ++chunk) {
+                uint32_t acc[kPiece];
+                if (kb1 > kb0) {
+                    if constexpr (kPiece == 32)
+                        tmem_ld_32x32(taddr + chunk * kPiece, acc);
+                    else
+                        tmem_ld_32x16(taddr + chunk * kPiece, acc);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kPiece; ++i)
+                        acc[i] = 0u;
+                }
+#pragma unroll
+                for (int i = 0; i < kPiece; i += 4)
+                    st_cluster_v4(target + (chunk * kPiece + i) * 4, __uint_as_float(acc[i]),
+                                  __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
+                                  __uint_as_float(acc[i + 3]));
+            }
+            fence_cluster();
+            __syncwarp();
+            if (lane < parts)
+                mbar_arrive_cluster(map_to_rank(smem_u32(inbox_full), lane));
+            if (!mbar_wait_cluster(inbox_full, 0, abort)) {
+                report(task.status, abort, kRoleDrain);
+                ok = false;
+            }
+        }
+        if (ok) {
+            /* step 3: add the slots of the owned rows in K order and store them */
+            const int first = cluster_first_row(part, parts);
+            const int owned = cluster_first_row(part + 1, parts) - first;
+            const int thread = (warp - 2) * 32 + lane; /* 0..127 */
+            if constexpr (Mode == kStoreRows) {
+                /* eight consecutive columns per thread and step */
+                constexpr int kVectors = BN / 8;
+                for (int item = thread; item < owned * kVectors; item += 128) {
+                    const int local_row = item / kVectors, c8 = (item - local_row * kVectors) * 8;
+                    const int row = rb * kBlockR + first + local_row, col = cb * BN + c8;
+                    if (row >= task.rows || col >= task.cols)
+                        continue;
+                    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int s = 0; s < parts; ++s) {
+                        const float4 *source = reinterpret_cast<const float4 *>(
+                            inbox + (s * rows_owned_max + local_row) * kPitch + c8);
+                        const float4 low = source[0], high = source[1];
+                        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
+                        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
+                    }
+                    __nv_bfloat16 *out = task.out;
+                    long long ld = task.ld_out;
+                    int shift = 0, limit = min(task.cols, task.cut0);
+                    if (col >= task.cut0) {
+                        const bool third = col >= task.cut1;
+                        out = third ? task.out2 : task.out1;
+                        ld = third ? task.ld_out2 : task.ld_out1;
+                        shift = third ? task.cut1 : task.cut0;
+                        limit = third ? task.cols : task.cut1;
+                    }
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[i] = task.alpha * sum[i];
+                        if (col + i < task.cols) {
+                            if (task.bias != nullptr)
+                                v[i] += __bfloat162float(task.bias[col + i]);
+                            if (task.beta != 0.f)
+                                v[i] = fmaf(task.beta,
+                                            __bfloat162float(task.addend[static_cast<long long>(row) *
+                                                                             task.ld_add +
+                                                                         col + i]),
+                                            v[i]);
+                        }
+                    }
+                    __nv_bfloat16 *target = out + static_cast<long long>(row) * ld + (col - shift);
+                    if (col + 8 <= limit && (reinterpret_cast<uintptr_t>(target) & 15) == 0) {
+                        uint4 packed;
+                        packed.x = pack_bf16(v[0], v[1]);
+                        packed.y = pack_bf16(v[2], v[3]);
+                        packed.z = pack_bf16(v[4], v[5]);
+                        packed.w = pack_bf16(v[6], v[7]);
+                        *reinterpret_cast<uint4 *>(target) = packed;
+                    } else {
+                        for (int i = 0; i < 8 && col + i < limit; ++i)
+                            target[i] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            } else {
+                /* swapped: tile rows are output features (contiguous in memory), tile
+                 * columns are tokens; consecutive threads take consecutive features */
+                for (int item = thread; item < owned * BN; item += 128) {
+                    const int token = item / owned, local_row = item - token * owned;
+                    const int feature = rb * kBlockR + first + local_row, column = cb * BN + token;
+                    if (feature >= task.rows || column >= task.cols)
+                        continue;
+                    float sum = 0.f;
+                    for (int s = 0; s < parts; ++s)
+                        sum += inbox[(s * rows_owned_max + local_row) * kPitch + token];
+                    float v = task.alpha * sum;
+                    if (task.bias != nullptr)
+                        v += __bfloat162float(task.bias[feature]);
+                    const long long at = static_cast<long long>(column);
+                    if (task.beta != 0.f)
+                        v = fmaf(task.beta, __bfloat162float(task.addend[at * task.ld_add + feature]), v);
+                    task.out[at * task.ld_out + feature] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+} // namespace sm100

@@ -5,8 +5,8 @@
  * here with the same name, argument list and status convention, so a caller
  * compiled against the reference links against this library unchanged. Each
  * declaration cites the reference declaration and implementation it stands in
- * for. Entry points that are outside the BF16/FP8 GEMM path (FP32/FP64 GEMM,
- * affine, MLP, attention, MLP backward) are exported but return -1 with a
+ * for. Entry points that are outside the GEMM path (affine, MLP, attention,
+ * MLP backward) are exported but return -1 with a
  * message naming the operation; nothing here falls back to a CPU or to a vendor
  * GEMM library.
  *
@@ -375,6 +375,10 @@ int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *
  *   "fp8_swapped_rows" 64..128: most token rows for which the FP8 block GEMM
  *                    streams the weights with the K range split over the SMs
  *                    instead of tiling the rows (default 128)
+ *   "cluster_split"  K split inside a thread-block cluster with the partial
+ *                    sums added through distributed shared memory: 0 never,
+ *                    1 for products of 65 token rows and more with few tiles
+ *                    (default), 2 also for the few-token kernels
  *   "bf16_strassen"  1 lets policy STRASSEN run one Strassen level on BF16
  *                    squares (CAMBLAS_B200_BF16_STRASSEN)
  *   "peer_wait_ms"   1..60000, how long a kernel of the row-parallel layer waits
@@ -446,16 +450,25 @@ int camblas_cuda_reduce_groups(camblas_cuda_context *context, int tokens, int ch
                                int grouped_rows, const void *experts, const void *reverse,
                                const void *input, void *output);
 
-/* ---- exported for link compatibility; not on the BF16/FP8 GEMM path ------- */
-/* Each returns -1 and sets "<name> is not provided by the B200 build".
- * Reference declarations: camblas_cuda.h:57-62 (sgemm/dgemm), :77-82 (affine,
- * mlp), :87-89 (attention), :94-99 (mlp_backward). */
+/* ---- FP32 / FP64 GEMM ----------------------------------------------------- */
+
+/* Replace camblas_cuda_sgemm / camblas_cuda_dgemm (camblas_cuda.h:57-62;
+ * backend.cu:786-866, 1057-1073). Column-major C = alpha op(A) op(B) + beta C
+ * in the storage type, argument rules as for camblas_cuda_bgemm. Off the
+ * BF16/FP8 path: a tiled CUDA-core kernel (B200 has no tensor-core mode that
+ * keeps FP32 products, and the reference keeps TF32 off); every policy value
+ * multiplies classically, no Strassen levels, no Gram shortcut. */
 int camblas_cuda_sgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
                        int k, float alpha, const float *a, int lda, const float *b, int ldb,
                        float beta, float *c, int ldc);
 int camblas_cuda_dgemm(camblas_cuda_context *context, char trans_a, char trans_b, int m, int n,
                        int k, double alpha, const double *a, int lda, const double *b, int ldb,
                        double beta, double *c, int ldc);
+
+/* ---- exported for link compatibility; not on the BF16/FP8 GEMM path ------- */
+/* Each returns -1 and sets "<name> is not provided by the B200 build".
+ * Reference declarations: camblas_cuda.h:77-82 (affine, mlp), :87-89
+ * (attention), :94-99 (mlp_backward). */
 int camblas_cuda_affine(camblas_cuda_context *context, int dtype, int rows, int inner, int columns,
                         const void *x, const void *weight, const void *bias, int relu,
                         void *output);

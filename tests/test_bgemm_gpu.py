@@ -201,10 +201,9 @@ def test_argument_validation_and_error_text():
 def test_cold_entry_points_say_so():
     context = _native.context(0)
     library = _native.library()
-    status = library.camblas_cuda_sgemm(context.handle, b"N", b"N", 1, 1, 1, 1.0, None, 1, None, 1,
-                                        0.0, None, 1)
+    status = library.camblas_cuda_attention(context.handle, 0, 1, 1, 1, 1, 1.0, None, None, None, None)
     assert status == -1
-    assert error_text(context) == "camblas_cuda_sgemm is not provided by the B200 build"
+    assert error_text(context) == "camblas_cuda_attention is not provided by the B200 build"
 
 
 def test_counters_count_launches(rng):
@@ -384,4 +383,74 @@ def test_packed_projection_at_the_sharded_widths(widths):
     picks_c = torch.randint(0, sum(widths), (64,), generator=generator)
     expected = (x[picks_r].double().cpu() * w[picks_c].double().cpu()).sum(1)
     got = packed[picks_r, picks_c].double().cpu()
+    assert ((got - expected).norm() / expected.norm()).item() <= BF16_TOLERANCE
+
+
+@pytest.mark.parametrize("rows,outputs,inner", [
+    (512, 1280, 8192),    # the QKV shard of one rank at tensor-parallel 8: 20 tiles of 128 x 256
+    (130, 1536, 2048),    # ragged rows: 12 tiles, large clusters
+    (200, 2500, 1100),    # ragged columns and a K that is not a multiple of 64
+    (16, 8192, 4096),     # few tokens: swapped kernel, 64 tiles, clusters of two
+    (3, 4096, 8192),      # swapped, 16-column tiles
+    (64, 5000, 2304),     # swapped, 64-column tiles, ragged weight rows
+])
+def test_k_split_inside_a_cluster(rng, rows, outputs, inner):
+    """Products with few tiles and a long K split K over the CTAs of a cluster and add the
+    partial accumulators through distributed shared memory. Checked against the oracle on a
+    row sample, against the route through scratch and a second launch (context option
+    cluster_split=0; different summation order, so by tolerance), with bias and residual,
+    and for repeatability."""
+    with _native.options(cluster_split=2):  # 2: the few-token tiles take it too
+        _k_split_inside_a_cluster(rng, rows, outputs, inner)
+
+
+def _k_split_inside_a_cluster(rng, rows, outputs, inner):
+    x = bits_to_tensor(normal_bits(rng, (rows, inner)))
+    w = bits_to_tensor(normal_bits(rng, (outputs, inner), 0.05))
+    bias = bits_to_tensor(normal_bits(rng, (outputs,)))
+    residual = bits_to_tensor(normal_bits(rng, (rows, outputs)))
+    native = _native.context(0)
+    before = native.kernel_launches()
+    first = _kernels.linear(x, w, bias, residual)
+    launches = native.kernel_launches() - before
+    second = _kernels.linear(x, w, bias, residual)
+    assert native.device_status() == 0
+    assert launches == 1, "the cluster split is one launch"
+    assert torch.equal(first, second)
+    with _native.options(cluster_split=0):
+        other = _kernels.linear(x, w, bias, residual)
+    assert ((first.float() - other.float()).norm() / other.float().norm()).item() <= 2e-3
+    sample = slice(0, min(rows, 6))
+    expected = oracle.bf16_values(oracle.linear_bf16(tensor_to_bits(x[sample]), tensor_to_bits(w),
+                                                     tensor_to_bits(bias), tensor_to_bits(residual[sample])))
+    assert oracle.rel_l2(first[sample].float().cpu().numpy(), expected) <= BF16_TOLERANCE
+    # exact small integers: a wrong row owner or slot shows as a wrong integer
+    xi = bits_to_tensor(oracle.bf16_bits(rng.integers(-1, 2, (rows, inner)).astype(np.float32)))
+    wi = bits_to_tensor(oracle.bf16_bits(rng.integers(-1, 2, (outputs, inner)).astype(np.float32)))
+    exact = (xi.double() @ wi.double().t())
+    keep = exact.abs() <= 256
+    got = _kernels.linear(xi, wi).double()
+    assert torch.equal(got[keep], exact[keep])
+
+
+def test_packed_projection_through_the_cluster_split():
+    """The QKV shard at tensor-parallel 8 (1024 + 128 + 128 outputs, K = 8192) is packed and
+    has 20 tiles: one cluster launch must fill the three outputs like three linears."""
+    torch.manual_seed(705537)
+    rows, inner, widths = 512, 8192, (1024, 128, 128)
+    x = torch.randn(rows, inner, device="cuda").bfloat16()
+    w = (torch.randn(sum(widths), inner, device="cuda") * 0.02).bfloat16()
+    native = _native.context(0)
+    before = native.kernel_launches()
+    q, k, v = _kernels.qkv_linear(x, w, *widths)
+    assert native.kernel_launches() - before == 1
+    assert native.device_status() == 0
+    parts = [_kernels.linear(x, part.contiguous()) for part in torch.split(w, list(widths))]
+    for got, expected in zip((q, k, v), parts):
+        assert ((got.float() - expected.float()).norm() / expected.float().norm()).item() <= 2e-3
+    generator = torch.Generator().manual_seed(3)
+    picks_r = torch.randint(0, rows, (64,), generator=generator)
+    picks_c = torch.randint(0, sum(widths), (64,), generator=generator)
+    expected = (x[picks_r].double().cpu() * w[picks_c].double().cpu()).sum(1)
+    got = torch.cat([q, k, v], dim=1)[picks_r, picks_c].double().cpu()
     assert ((got - expected).norm() / expected.norm()).item() <= BF16_TOLERANCE

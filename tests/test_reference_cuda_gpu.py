@@ -247,3 +247,42 @@ def test_silu_multiply_and_swiglu_bit_for_bit(both, rng, dtype):
             results.append((plain, clipped, routed))
         for mine, reference in zip(*results):
             assert torch.equal(mine, reference)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("ta,tb", [("N", "N"), ("N", "T"), ("T", "N"), ("T", "T")])
+@pytest.mark.parametrize("m,n,k", [(5, 3, 7), (130, 70, 257), (300, 129, 64), (512, 512, 512)])
+def test_sgemm_dgemm_against_the_reference_library_and_float64(both, rng, dtype, ta, tb, m, n, k):
+    """FP32/FP64 GEMM (off the BF16/FP8 path; a tiled CUDA-core kernel here, cuBLAS in the
+    reference): same C-ABI call on both libraries, padded leading dimensions with NaN
+    canaries, alpha/beta; each within a few units of the type's rounding of the float64
+    product, scaled by sqrt(k) for the differing summation orders."""
+    ours, theirs = both
+    name = "sgemm" if dtype is np.float32 else "dgemm"
+    lda, ldb, ldc = (m if ta == "N" else k) + 3, (k if tb == "N" else n) + 5, m + 2
+
+    def padded_matrix(rows, columns, ld):
+        buffer = np.full((columns, ld), np.nan, dtype=dtype)
+        buffer[:, :rows] = rng.standard_normal((columns, rows)).astype(dtype)
+        return buffer
+
+    a = padded_matrix(m if ta == "N" else k, k if ta == "N" else m, lda)
+    b = padded_matrix(k if tb == "N" else n, n if tb == "N" else k, ldb)
+    c = padded_matrix(m, n, ldc)
+    op_a = a[:, :m].T if ta == "N" else a[:, :k]       # m x k
+    op_b = b[:, :k].T if tb == "N" else b[:, :n]       # k x n
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    eps = np.finfo(dtype).eps
+    for alpha, beta in ((1.0, 0.0), (0.5, -1.25)):
+        exact = alpha * (op_a.astype(np.float64) @ op_b.astype(np.float64)) + beta * c[:, :m].T.astype(np.float64)
+        bound = 8 * eps * np.sqrt(k) * (np.abs(alpha) * (np.abs(op_a).astype(np.float64) @ np.abs(op_b))
+                                         + np.abs(beta * c[:, :m].T))
+        for library in (ours, theirs):
+            dc = torch.from_numpy(c).cuda()
+            library.call("set_algorithm", 1)
+            library.call(name, ta.encode(), tb.encode(), m, n, k, alpha, pointer(da), lda, pointer(db),
+                         ldb, beta, pointer(dc), ldc)
+            torch.cuda.synchronize()
+            result = dc.cpu().numpy()
+            assert np.all(np.isnan(result[:, m:])), "padding rows of C were written"
+            assert np.all(np.abs(result[:, :m].T - exact) <= bound + 1e-300)
