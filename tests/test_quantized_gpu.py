@@ -201,3 +201,44 @@ def test_route_and_reduce_groups(rng, reference):
               pointer(reverse), pointer(narrow), pointer(theirs))
     torch.cuda.synchronize()
     assert torch.equal(mine, theirs)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("rows", [1, 8, 17])
+def test_known_answers_and_scale_extremes(reference, packed, rows):
+    """The reference's own known-answer cases (tests/test_quantized.py:238-262, 311-320):
+    x = 1.0 everywhere (E4M3 0x38), weight 1.0 (E4M3 0x38, or E2M1 nibbles 0x22) with unit
+    weight scales, and input scales at the ends of the E8M0 range: 2^-127 (code 0), 1, 2^127
+    and NaN. Every output is inner * 2^(code-127), exactly, NaN for code 255; a NaN input
+    byte (0x7F) makes everything NaN; weight nibbles 0x33 (1.5) with inner = 32 give 48."""
+    outputs, inner = 40, 64
+    weight_dtype = torch.float4_e2m1fn_x2 if packed else torch.float8_e4m3fn
+    x = torch.full((rows, inner), 0x38, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    w = torch.full((outputs, inner // 2 if packed else inner), 0x22 if packed else 0x38,
+                   dtype=torch.uint8, device="cuda").view(weight_dtype)
+    sw = torch.full((outputs if packed else 2, inner // 32), 127, dtype=torch.uint8,
+                    device="cuda").view(torch.float8_e8m0fnu)
+    for code in (0, 127, 254, 255):
+        sx = torch.full((rows, inner // 32), code, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+        out = _kernels.quantized_matmul(x, sx, w, sw)
+        theirs = torch.zeros_like(out)
+        reference("quantized_matmul", int(packed), rows, outputs, inner, 32, pointer(x), pointer(sx),
+                  pointer(w), pointer(sw), pointer(theirs))
+        torch.cuda.synchronize()
+        if code == 255:
+            assert torch.isnan(out).all() and torch.isnan(theirs).all()
+            continue
+        expected = torch.full_like(out, 0).double() + inner * 2.0 ** (code - 127)
+        expected = expected.to(torch.bfloat16)  # 2^134 overflows to inf, 2^-121 is a normal BF16
+        assert torch.equal(theirs, expected)
+        assert torch.equal(out, expected), (code, out[0, :4])
+    ones = torch.full((rows, inner // 32), 127, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+    nan_input = torch.full((rows, inner), 0x7F, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    assert torch.isnan(_kernels.quantized_matmul(nan_input, ones, w, sw)).all()
+    if packed:
+        x32 = torch.full((1, 32), 0x38, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        w32 = torch.full((8, 16), 0x33, dtype=torch.uint8, device="cuda").view(weight_dtype)
+        unit = torch.full((1, 1), 127, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+        units = torch.full((8, 1), 127, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+        out = _kernels.quantized_matmul(x32, unit, w32, units)
+        assert torch.equal(out, torch.full((1, 8), 48, dtype=torch.bfloat16, device="cuda"))
