@@ -655,7 +655,8 @@ def run_ours(args):
             "clocks": clocks,
         }
         if sustained is not None:
-            sustained["frac_of_sustained_peak"] = sustained["value"] / peaks["bf16_tflops_sustained"]
+            sustained["frac_of_sustained_peak"] = sustained["value"] / (
+                world * peaks["bf16_tflops_sustained"])
             line["sustained"] = sustained
         if world == 1:
             sample = CpuSample()

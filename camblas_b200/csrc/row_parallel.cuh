@@ -74,26 +74,43 @@ constexpr int kFlagWords = 65536; /* word 0: delivery counter; word 1: CTAs of t
                                      word per slab counting the CTAs that have read it */
 constexpr int kFlagHeader = 64;
 constexpr int kMaxUnits = 24576; /* slabs of the tile path: two words each from kFlagHeader on */
-/* The rest of the flag words belongs to the small all-reduce: three words per
- * 2048-element chunk (arrived, consumed, pending). */
-constexpr int kSmallBase = kFlagHeader + 2 * kMaxUnits;
-constexpr int kSmallChunks = (kFlagWords - kSmallBase) / 3;
+/* The rest of the flag words belongs to the all-reduce of small tensors: one
+ * call counter per 2048-element chunk of the flagged-line exchange (the last
+ * kLineChunks words), and before them three words per chunk (arrived, consumed,
+ * pending) for tensors too large for that exchange. */
 constexpr int kSmallChunkElements = 2048; /* 256 threads x 8 BF16 */
+constexpr long long kLineMaxElements = 64 * 8192; /* 1 MiB of BF16: 64 token rows of 8192 */
+constexpr int kLineChunks = int(kLineMaxElements / kSmallChunkElements);
+constexpr int kLineBase = kFlagWords - kLineChunks;
+constexpr int kSmallBase = kFlagHeader + 2 * kMaxUnits;
+constexpr int kSmallChunks = (kLineBase - kSmallBase) / 3;
+/* A flagged line is 16 bytes: two 8-byte halves of 4 payload bytes and a 4-byte
+ * flag each. One rank's tensor takes at most kLineSlotLines of them. */
+constexpr size_t kLinesPerChunk = 2 * 256;
+constexpr size_t kLineSlotLines = size_t(kLineChunks) * kLinesPerChunk;
 
 inline size_t slot_bytes(size_t capacity)
 {
     return (capacity * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
 }
 
+/* Two buffers of one slot per rank, directly behind the flag words. */
+inline size_t line_bytes(int world)
+{
+    return 2 * size_t(world) * kLineSlotLines * sizeof(uint4);
+}
+
 inline size_t region_bytes(int world, size_t capacity)
 {
-    return slot_bytes(capacity) * (1 + size_t(world)) + size_t(kFlagWords) * sizeof(unsigned);
+    return slot_bytes(capacity) * (1 + size_t(world)) + size_t(kFlagWords) * sizeof(unsigned) +
+           line_bytes(world);
 }
 
 struct Region {
     __nv_bfloat16 *result;
     __nv_bfloat16 *staging; /* slot s at staging + s * slot_elements */
     unsigned *flags;
+    uint4 *lines; /* [buffer][rank][kLineSlotLines] */
     size_t slot_elements;
 };
 
@@ -105,6 +122,7 @@ inline Region carve(void *memory, int world, size_t capacity)
     region.result = reinterpret_cast<__nv_bfloat16 *>(base);
     region.staging = reinterpret_cast<__nv_bfloat16 *>(base + slot_bytes(capacity));
     region.flags = reinterpret_cast<unsigned *>(base + slot_bytes(capacity) * (1 + size_t(world)));
+    region.lines = reinterpret_cast<uint4 *>(region.flags + kFlagWords);
     return region;
 }
 
@@ -255,17 +273,14 @@ __global__ void peer_wait_delivered(unsigned *delivered, unsigned expected, unsi
         wait_delivered(delivered, expected, status, wait_ns);
 }
 
-/* ---- all-reduce of a small BF16 tensor through the peer regions -----------------
+/* ---- all-reduce of a BF16 tensor through the peer regions, counted arrivals -----
  *
- * For the few token rows of decoding the product is a weight-streaming kernel
- * of some ten microseconds and its partial result is 16 KB to 1 MB; a library
- * all-reduce then costs as much as the product (measured 11-17 us on two
- * GPUs). This kernel is a one-shot exchange instead: every rank stores its
- * tensor into slot `rank` of EVERY GPU's staging area (16-byte stores over
- * NVLink), tells each GPU so, waits until all `world` tensors have arrived in
- * its own staging area, adds them in rank order in FP32, rounds once and writes
- * its own copy of the sum. All ranks add the same values in the same order, so
- * they hold the same bits.
+ * Used for tensors beyond the 1 MiB that the flagged-line exchange further down
+ * takes. A one-shot exchange: every rank stores its tensor into slot `rank` of
+ * EVERY GPU's staging area (16-byte stores over NVLink), tells each GPU so, waits
+ * until all `world` tensors have arrived in its own staging area, adds them in
+ * rank order in FP32, rounds once and writes its own copy of the sum. All ranks
+ * add the same values in the same order, so they hold the same bits.
  *
  * The work is cut into chunks of 2048 elements, one CTA each, and every chunk
  * synchronises on its own three flag words of the region, so no CTA depends on
@@ -374,6 +389,139 @@ __global__ void __launch_bounds__(256) peer_small_allreduce(const SmallTask task
             sm100::flag_add_release_system(task.flags_at[threadIdx.x] + kSmallChunks + chunk, 1u);
         if (threadIdx.x == 0)
             *pending = 1u;
+    }
+}
+
+/* ---- all-reduce of at most 1 MiB of BF16 through flagged lines ------------------
+ *
+ * The exchange above needs three trips over NVLink per call (stores and their
+ * fence, the arrival count, the consumed count). For the tensors of decoding that
+ * latency is the whole cost, so up to kLineMaxElements take this route instead,
+ * which needs one: every 8 bytes of payload travel as a 16-byte line
+ * {4 bytes, flag, 4 bytes, flag}, each 8-byte half written by one store
+ * instruction so that payload and flag become visible together. The receiver
+ * polls the lines themselves until both flags show the number of the current
+ * call; there is no fence, no separate flag word and no acknowledgement.
+ *
+ * Call numbers. Word kLineBase + c of a GPU's flag words counts the calls that
+ * have used chunk c; every rank makes the same calls, so the ranks agree on it
+ * without talking. The flag of a call is that count plus one, cycling through
+ * 1 .. 2^32 - 2 (never zero, which is what a cleared line holds; the cycle length
+ * is even so that consecutive calls always differ in the lowest bit).
+ *
+ * Reuse. The lowest bit of the flag selects one of two line buffers. Rank A
+ * writes call n + 2 into the buffer of call n only after it finished call n + 1,
+ * for which it needed B's lines of call n + 1, which B's stream sent only after
+ * B's kernel of call n had finished reading. So nothing is overwritten while it
+ * is still being read, provided the calls of one rank run in stream order.
+ *
+ * Stale lines. A sender always writes all 512 lines of a chunk (zero payload
+ * beyond the tensor's end), so every line of a chunk carries the flag of the
+ * latest call that used its buffer and an older number cannot be mistaken for the
+ * current one. The line area is written by nothing else and is cleared by
+ * camblas_cuda_peer_alloc and camblas_cuda_peer_reset.
+ *
+ * The sum is formed like above: FP32, rank order (the rank's own tensor comes
+ * from `input`, not through memory), one rounding. Waits are bounded; `phases`
+ * 1 (send) and 2 (receive, add, count the call) can be issued separately. */
+struct LineTask {
+    int rank, world;
+    long long elements; /* multiple of 8 */
+    const __nv_bfloat16 *input;
+    __nv_bfloat16 *output;
+    uint4 *slot_at[kMaxWorld]; /* this rank's slot of buffer 0 in every GPU's line area */
+    const uint4 *lines;        /* this GPU's line area */
+    unsigned *calls;           /* this GPU's call counters, one per chunk */
+    unsigned *status;
+    unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ void store_line(uint4 *line, unsigned low, unsigned high, unsigned flag)
+{
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(line), "r"(low),
+                 "r"(flag), "r"(high), "r"(flag)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 load_line(const uint4 *line)
+{
+    uint4 value;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w)
+                 : "l"(line)
+                 : "memory");
+    return value;
+}
+
+__global__ void __launch_bounds__(256) peer_lines_allreduce(const LineTask task, int phases)
+{
+    const int chunk = blockIdx.x;
+    const long long element = static_cast<long long>(chunk) * kSmallChunkElements + threadIdx.x * 8;
+    const bool live = element < task.elements;
+    const unsigned flag = task.calls[chunk] + 1u;
+    const size_t buffer = size_t(flag & 1u) * size_t(task.world) * kLineSlotLines;
+    const size_t first = size_t(chunk) * kLinesPerChunk + threadIdx.x; /* second line 256 further */
+    const uint4 mine =
+        live ? *reinterpret_cast<const uint4 *>(task.input + element) : make_uint4(0u, 0u, 0u, 0u);
+    if (phases & 1) {
+        for (int hop = 1; hop < task.world; ++hop) {
+            int target = task.rank + hop;
+            if (target >= task.world)
+                target -= task.world;
+            uint4 *const slot = task.slot_at[target] + buffer + first;
+            store_line(slot, mine.x, mine.y, flag);
+            store_line(slot + 256, mine.z, mine.w, flag);
+        }
+    }
+    if (phases & 2) {
+        if (live) {
+            const uint4 *const inbox = task.lines + buffer + first;
+            uint4 part[kMaxWorld];
+            bool complete = false;
+            unsigned long long started = 0;
+            for (uint32_t spin = 0; spin < sm100::kSpinLimit && !complete; ++spin) {
+                uint4 low[kMaxWorld], high[kMaxWorld];
+#pragma unroll
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world && s != task.rank) {
+                        low[s] = load_line(inbox + size_t(s) * kLineSlotLines);
+                        high[s] = load_line(inbox + size_t(s) * kLineSlotLines + 256);
+                    }
+                complete = true;
+#pragma unroll
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world && s != task.rank) {
+                        complete = complete && low[s].y == flag && low[s].w == flag &&
+                                   high[s].y == flag && high[s].w == flag;
+                        part[s] = make_uint4(low[s].x, low[s].z, high[s].x, high[s].z);
+                    }
+                if (!complete && (spin & 63u) == 63u) {
+                    const unsigned long long now = sm100::global_timer_ns();
+                    if (started == 0)
+                        started = now;
+                    else if (now - started > task.wait_ns)
+                        break;
+                }
+            }
+            if (complete) {
+                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world)
+                        accumulate8(sum, s == task.rank ? mine : part[s]);
+                uint4 packed;
+                packed.x = sm100::pack_bf16(sum[0], sum[1]);
+                packed.y = sm100::pack_bf16(sum[2], sum[3]);
+                packed.z = sm100::pack_bf16(sum[4], sum[5]);
+                packed.w = sm100::pack_bf16(sum[6], sum[7]);
+                *reinterpret_cast<uint4 *>(task.output + element) = packed;
+            } else {
+                atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
+            }
+        }
+        __syncthreads(); /* every thread has read the counter */
+        if (threadIdx.x == 0)
+            task.calls[chunk] = flag == 0xFFFFFFFEu ? 0u : flag;
     }
 }
 
@@ -585,8 +733,9 @@ extern "C" int camblas_cuda_peer_reset(camblas_cuda_context *context, void *memo
         if (!memory || world < 1 || world > peer::kMaxWorld || capacity == 0)
             return host::fail(context, "invalid peer region description", 1);
         peer::Region region = peer::carve(memory, world, capacity);
-        cudaError_t error = cudaMemsetAsync(region.flags, 0, size_t(peer::kFlagWords) * 4,
-                                            context->stream);
+        /* the flagged lines lie directly behind the flag words */
+        cudaError_t error = cudaMemsetAsync(
+            region.flags, 0, size_t(peer::kFlagWords) * 4 + peer::line_bytes(world), context->stream);
         return error == cudaSuccess ? 0 : host::fail(context, "peer flag reset", error);
     });
 }
@@ -610,8 +759,27 @@ extern "C" int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, i
                               1);
         const size_t chunks = (count + peer::kSmallChunkElements - 1) / peer::kSmallChunkElements;
         if (count > capacity || chunks > size_t(peer::kSmallChunks))
-            return host::fail(context, "peer all-reduce exceeds the region capacity or 11 million elements",
-                              1);
+            return host::fail(context,
+                              "peer all-reduce exceeds the region capacity or 10.9 million elements", 1);
+        if (count <= size_t(peer::kLineMaxElements)) {
+            peer::LineTask task{};
+            task.rank = rank, task.world = world;
+            task.elements = static_cast<long long>(count);
+            task.input = static_cast<const __nv_bfloat16 *>(input);
+            task.output = static_cast<__nv_bfloat16 *>(output);
+            for (int r = 0; r < world; ++r) {
+                const peer::Region region = peer::carve(memory[r], world, capacity);
+                task.slot_at[r] = region.lines + size_t(rank) * peer::kLineSlotLines;
+                if (r == rank) {
+                    task.lines = region.lines;
+                    task.calls = region.flags + peer::kLineBase;
+                }
+            }
+            task.status = context->status;
+            task.wait_ns = 1000000ull * unsigned(context->options.peer_wait_ms);
+            peer::peer_lines_allreduce<<<unsigned(chunks), 256, 0, context->stream>>>(task, phases);
+            return host::launched(context, "peer all-reduce through flagged lines");
+        }
         peer::SmallTask task{};
         task.rank = rank, task.world = world;
         task.elements = static_cast<long long>(count);

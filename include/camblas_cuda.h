@@ -240,13 +240,17 @@ int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, 
  * F.linear there). Sum of one BF16 tensor of `count` elements per rank over
  * the ranks of a peer-region group, for the small results of decoding (a few
  * token rows): output = rnd(input_0 + input_1 + ... in rank order, FP32), the
- * same bits on every rank. One kernel per rank on the context's stream: it
- * stores `input` into this rank's staging slot on every GPU over NVLink, waits
- * (bounded, "peer_wait_ms") until all ranks' copies have arrived in its own
- * region, and adds them; chunks of 2048 elements synchronise on their own flag
- * words, so the exchange needs no collective library and no second launch. All
- * ranks must make the same sequence of calls with the same count. count is a
- * multiple of 8, at most min(capacity, 11 141 120); input and output 16-byte
+ * same bits on every rank. One kernel per rank on the context's stream, no
+ * collective library and no second launch. Up to 524 288 elements (1 MiB) every
+ * 8 bytes travel to each peer as a 16-byte line that carries the call's number
+ * beside the payload, the receiver polls the lines until the number is the
+ * current one (bounded, "peer_wait_ms"), and the exchange costs one trip over
+ * NVLink; the calls of one rank must then run in stream order, because two line
+ * buffers alternate. Larger tensors are stored into this rank's staging slot on
+ * every GPU, announced and acknowledged through counted flag words per chunk of
+ * 2048 elements. All ranks must make the same sequence of calls with the same
+ * count. count is a multiple of 8, at most min(capacity, 10 964 992); input and
+ * output 16-byte
  * aligned, output may be input. `phases` is 3 in production; 1 (send) and 2
  * (receive and add) exist so that one process can drive several ranks on one
  * GPU in turn. After a wait has expired (device status) the region needs

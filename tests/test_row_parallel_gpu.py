@@ -218,17 +218,19 @@ def test_expired_wait_reports_and_reset_recovers():
 
 
 @pytest.mark.parametrize("world,count", [(1, 8192), (2, 8), (2, 8192), (4, 64 * 8192), (8, 16 * 8192),
-                                         (8, 3 * 2048 + 264)])
+                                         (8, 3 * 2048 + 264), (2, 64 * 8192 + 8), (3, 80 * 8192)])
 def test_small_all_reduce_sums_in_rank_order(world, count):
     """`camblas_cuda_peer_allreduce_bf16` with emulated ranks: every rank's result is the FP32
     sum of the ranks' tensors in rank order, rounded once - bit for bit - and stays so over
-    repeated calls (the flag words hand themselves back), in place as well. The two phases
-    of the ranks are issued in turn so that no kernel waits for an unlaunched one."""
+    repeated calls (both line buffers come round again; the counted flag words of the larger
+    sizes hand themselves back), in place as well. Counts up to 64 x 8192 take the
+    flagged-line exchange, the last two cases the counted one. The two phases of the ranks
+    are issued in turn so that no kernel waits for an unlaunched one."""
     torch.manual_seed(705537 + world + count)
-    capacity = PeerRegions.capacity_for(64, 8192)
+    capacity = PeerRegions.capacity_for(80, 8192)
     views = PeerRegions.emulate(capacity, world, 0)
     try:
-        for call in range(3):
+        for call in range(5):
             inputs = [torch.randn(count, device="cuda").bfloat16() for _ in range(world)]
             total = torch.zeros(count, device="cuda")
             for tensor in inputs:
@@ -243,6 +245,62 @@ def test_small_all_reduce_sums_in_rank_order(world, count):
             assert _native.context(0).device_status() == 0
             for output in outputs:
                 assert torch.equal(output, expected)
+    finally:
+        close_all(views)
+
+
+def test_small_all_reduce_of_changing_sizes_never_takes_an_old_line_for_a_new_one():
+    """Calls of different sizes share the chunks' call counters and line buffers: a long
+    tensor, then short ones, then the long one again. Lines that the short calls did not
+    touch still carry older call numbers and must not pass for current ones."""
+    world = 4
+    torch.manual_seed(20261201)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(64, 8192), world, 0)
+    try:
+        for count in (32 * 8192, 8, 2048 + 8, 8, 32 * 8192, 4096, 32 * 8192):
+            inputs = [torch.randn(count, device="cuda").bfloat16() for _ in range(world)]
+            total = torch.zeros(count, device="cuda")
+            for tensor in inputs:
+                total = total + tensor.float()
+            outputs = [torch.empty_like(tensor) for tensor in inputs]
+            for phase in (1, 2):
+                for view, source, output in zip(views, inputs, outputs):
+                    view.all_reduce(source, out=output, phases=phase)
+            torch.cuda.synchronize()
+            assert _native.context(0).device_status() == 0
+            for output in outputs:
+                assert torch.equal(output, total.bfloat16())
+    finally:
+        close_all(views)
+
+
+def test_small_all_reduce_whose_peer_never_sends_gives_up_and_reset_recovers():
+    """Rank 0 of two emulated ranks receives without rank 1 having sent: the polls of the
+    lines run out after the lowered limit, the kernel returns and the status word names the
+    wait. The ranks' call counters now disagree, which camblas_cuda_peer_reset puts right."""
+    world, count = 2, 4096
+    torch.manual_seed(5)
+    views = PeerRegions.emulate(PeerRegions.capacity_for(1, 8192), world, 0)
+    native = _native.context(0)
+    try:
+        inputs = [torch.randn(count, device="cuda").bfloat16() for _ in range(world)]
+        output = torch.empty_like(inputs[0])
+        with _native.options(peer_wait_ms=50):
+            views[0].all_reduce(inputs[0], out=output, phases=3)
+            torch.cuda.synchronize()  # returns: the wait was bounded
+            status = native.device_status()
+        assert status & 15 == 6, hex(status)  # kRolePeerArrive
+        for view in views:
+            view.reset()
+        torch.cuda.synchronize()
+        outputs = [torch.empty_like(tensor) for tensor in inputs]
+        for phase in (1, 2):
+            for view, source, result in zip(views, inputs, outputs):
+                view.all_reduce(source, out=result, phases=phase)
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        expected = (inputs[0].float() + inputs[1].float()).bfloat16()
+        assert torch.equal(outputs[0], expected) and torch.equal(outputs[1], expected)
     finally:
         close_all(views)
 
