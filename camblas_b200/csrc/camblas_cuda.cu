@@ -8,6 +8,7 @@
 #include "context.cuh"
 #include "dispatch_bf16.cuh"
 #include "fp8_block.cuh"
+#include "fp8_block_wide.cuh"
 #include "gemm_simt.cuh"
 #include "quantized.cuh"
 #include "rms_norm.cuh"
@@ -46,14 +47,11 @@ void options_from_environment(ContextOptions &options)
 }
 } // namespace
 
-extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_context **out)
+namespace
 {
-    if (!out)
-        return fail(nullptr, "missing context output", 1);
-    *out = nullptr;
-    host::DeviceScope scope(device);
-    if (scope.status != cudaSuccess)
-        return fail(nullptr, "activate device", scope.status);
+/* The body of camblas_cuda_create, with `device` current. */
+int create_here(int device, void *stream, camblas_cuda_context **out)
+{
     auto *context = new (std::nothrow) camblas_cuda_context;
     if (!context)
         return fail(nullptr, "context allocation", 2);
@@ -107,7 +105,8 @@ extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_contex
     }
     if (status == 0) {
         what = "kernel attributes";
-        status = host::prepare_kernels() | fp8::prepare_kernels() | prepare_rms_kernels();
+        status = host::prepare_kernels() | fp8::prepare_kernels() | fp8::prepare_wide_kernels() |
+                 prepare_rms_kernels();
     }
     if (status != 0) {
         cudaGetLastError();
@@ -122,13 +121,9 @@ extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_contex
     return 0;
 }
 
-extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
+/* The body of camblas_cuda_destroy, with the context's device current. */
+int destroy_here(camblas_cuda_context *context)
 {
-    if (!context)
-        return 0;
-    host::DeviceScope scope(context->device);
-    if (scope.status != cudaSuccess)
-        return fail(context, "activate device for destruction", scope.status);
     cudaError_t error = cudaStreamSynchronize(context->stream);
     if (context->scratch)
         cudaFree(context->scratch);
@@ -142,6 +137,30 @@ extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
         cudaFreeHost(context->guard_hits);
     delete context;
     return error == cudaSuccess ? 0 : fail(nullptr, "stream completion during destruction", error);
+}
+} // namespace
+
+extern "C" int camblas_cuda_create(int device, void *stream, camblas_cuda_context **out)
+{
+    if (!out)
+        return fail(nullptr, "missing context output", 1);
+    *out = nullptr;
+    int status = 0;
+    cudaError_t error = cudaSuccess;
+    if (!host::on_device(device, error, [&] { status = create_here(device, stream, out); }))
+        return fail(nullptr, "activate device", error);
+    return status;
+}
+
+extern "C" int camblas_cuda_destroy(camblas_cuda_context *context)
+{
+    if (!context)
+        return 0;
+    int status = 0;
+    cudaError_t error = cudaSuccess;
+    if (!host::on_device(context->device, error, [&] { status = destroy_here(context); }))
+        return fail(context, "activate device for destruction", error);
+    return status;
 }
 
 extern "C" const char *camblas_cuda_error(const camblas_cuda_context *context)
@@ -178,7 +197,7 @@ extern "C" int camblas_cuda_set_option(camblas_cuda_context *context, const char
         {"pair_tail", &options.pair_tail, 0, 2},
         {"pair_width", &options.pair_width, 0, 256},
         {"push_width", &options.push_width, 0, 256},
-        {"fp8_rows", &options.fp8_rows, 0, 2},
+        {"fp8_rows", &options.fp8_rows, 0, 4},
         {"fp8_swapped_rows", &options.fp8_swapped_rows, 64, 128},
         {"cluster_split", &options.cluster_split, 0, 2},
         {"bf16_strassen", &options.bf16_strassen, 0, 1},

@@ -112,46 +112,64 @@ inline int unavailable(camblas_cuda_context *context, const char *name)
     return -1;
 }
 
-class DeviceScope
+/* Run `work` with `device` current and put the caller's device back afterwards,
+ * whichever way `work` ends. False, with `error` set and `work` not run, when
+ * the device could not be made current. */
+template <typename Work> bool on_device(int device, cudaError_t &error, Work work)
 {
-    int previous = -1;
-    bool changed = false;
-
-  public:
-    cudaError_t status;
-    explicit DeviceScope(int device) : status(cudaGetDevice(&previous))
-    {
-        if (status == cudaSuccess && previous != device) {
-            status = cudaSetDevice(device);
-            changed = status == cudaSuccess;
-        }
-    }
-    ~DeviceScope()
-    {
-        if (changed)
-            cudaSetDevice(previous);
-    }
-};
-
-/* Run one entry point on the context's device, restoring the caller's device
- * and turning host exceptions into a status (reference: backend.cu:913-951). */
-template <typename Function> int guarded(camblas_cuda_context *context, Function function)
-{
-    if (!context)
-        return fail(nullptr, "missing context", 1);
-    DeviceScope scope(context->device);
-    if (scope.status != cudaSuccess)
-        return fail(context, "activate device", scope.status);
+    int home = -1;
+    error = cudaGetDevice(&home);
+    const bool move = error == cudaSuccess && home != device;
+    if (move)
+        error = cudaSetDevice(device);
+    if (error != cudaSuccess)
+        return false;
     try {
-        return function();
+        work();
+    } catch (...) {
+        if (move)
+            cudaSetDevice(home);
+        throw;
+    }
+    if (move)
+        cudaSetDevice(home);
+    return true;
+}
+
+/* Status and message for the exception in flight (call from a catch block).
+ * The C ABI lets none out: -2 for an allocation failure, -1 otherwise, the
+ * codes of the reference's entry points (backend.cu:913-951). */
+inline int exception_status(camblas_cuda_context *context) noexcept
+{
+    try {
+        throw;
     } catch (const std::bad_alloc &) {
         return fail(context, "host allocation", 2);
     } catch (const std::exception &error) {
         std::snprintf(context->error, sizeof(context->error), "host exception: %s", error.what());
-        return -1;
     } catch (...) {
         return fail(context, "unexpected host exception", 1);
     }
+    return -1;
+}
+
+/* Every entry point that takes a context runs through here: on the context's
+ * device, with the caller's device restored and host exceptions turned into a
+ * status. */
+template <typename Function> int guarded(camblas_cuda_context *context, Function function)
+{
+    if (!context)
+        return fail(nullptr, "missing context", 1);
+    int status = 0;
+    cudaError_t error = cudaSuccess;
+    const bool ran = on_device(context->device, error, [&] {
+        try {
+            status = function();
+        } catch (...) {
+            status = exception_status(context);
+        }
+    });
+    return ran ? status : fail(context, "activate device", error);
 }
 
 inline int launched(camblas_cuda_context *context, const char *what)

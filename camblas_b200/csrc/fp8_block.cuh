@@ -893,6 +893,11 @@ void launch_block(camblas_cuda_context *context, const CUtensorMap &p, const CUt
                                                                                          task);
 }
 
+/* 256-column tiles for many token rows (fp8_block_wide.cuh) */
+inline int block_gemm_wide(camblas_cuda_context *context, bool pair, int rows, int outputs, int inner,
+                           const void *q, const float *q_scale, const void *w, const float *w_scale,
+                           void *out, int ldo);
+
 inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int inner,
                       const void *q, const float *q_scale, const void *w, const float *w_scale,
                       void *out, int ldo)
@@ -917,6 +922,9 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
     const bool swapped = rows <= 64 || (rows <= std::min(kSwappedRowLimit,
                                                          context->options.fp8_swapped_rows) &&
                                         outputs <= 24 * 128);
+    if (!swapped && (context->options.fp8_rows == 3 || context->options.fp8_rows == 4))
+        return block_gemm_wide(context, context->options.fp8_rows == 4, rows, outputs, inner, q, q_scale,
+                               w, w_scale, out, ldo);
     if (!swapped) {
         task.rows = rows, task.cols = outputs;
         task.r_blocks = (rows + 127) / 128, task.c_blocks = (outputs + 127) / 128;

@@ -93,11 +93,14 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
 
 
 def test_peer_region_size_is_host_arithmetic():
-    """camblas_cuda_peer_bytes: result + world staging slots (256-byte aligned) + 65536 flag words."""
+    """camblas_cuda_peer_bytes: result + world staging slots (256-byte aligned) + 65536 flag
+    words + two buffers of one 2 MiB slot of flagged lines per rank."""
     library = _native.library()
     slot = (1000 * 2 + 255) // 256 * 256
-    assert library.camblas_cuda_peer_bytes(2, 1000) == slot * 3 + 65536 * 4
-    assert library.camblas_cuda_peer_bytes(8, 512 * 8192) == 512 * 8192 * 2 * 9 + 65536 * 4
+    lines = 2 * 64 * 8192 * 4  # per rank: two buffers, 16 bytes per 8 bytes of a 1 MiB tensor
+    assert library.camblas_cuda_peer_bytes(2, 1000) == slot * 3 + 65536 * 4 + 2 * lines
+    assert library.camblas_cuda_peer_bytes(8, 512 * 8192) == (512 * 8192 * 2 * 9 + 65536 * 4
+                                                               + 8 * lines)
     assert library.camblas_cuda_peer_bytes(9, 1000) == 0
     assert library.camblas_cuda_peer_bytes(0, 1000) == 0
     assert library.camblas_cuda_peer_bytes(2, 0) == 0
