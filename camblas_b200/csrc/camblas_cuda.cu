@@ -197,7 +197,7 @@ extern "C" int camblas_cuda_set_option(camblas_cuda_context *context, const char
         {"pair_tail", &options.pair_tail, 0, 2},
         {"pair_width", &options.pair_width, 0, 256},
         {"push_width", &options.push_width, 0, 256},
-        {"fp8_rows", &options.fp8_rows, 0, 4},
+        {"fp8_rows", &options.fp8_rows, 0, 5},
         {"fp8_swapped_rows", &options.fp8_swapped_rows, 64, 128},
         {"cluster_split", &options.cluster_split, 0, 2},
         {"bf16_strassen", &options.bf16_strassen, 0, 1},

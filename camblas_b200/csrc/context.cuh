@@ -35,8 +35,10 @@ struct ContextOptions {
                               the two-SM kernel, 0 = fixed 256/128-column tiles */
     int push_width = 0;    /* "push_width" (CAMBLAS_B200_PUSH_WIDTH): tile width of the peer-memory
                               row-parallel product, 0 = by shape */
-    int fp8_rows = 0;      /* "fp8_rows" (CAMBLAS_B200_FP8_ROWS=four|single): 1, 2 select the older
-                              many-row FP8 kernels, which give the same bits */
+    int fp8_rows = 0;      /* "fp8_rows" (CAMBLAS_B200_FP8_ROWS=four|single): which many-row FP8
+                              kernel; all give the same bits. 0 by size; 1, 2 the older
+                              128 x 128 forms; 3 / 4 256-column tiles on one / two SMs; 5 the
+                              current 128 x 128 form whatever the size */
     int fp8_swapped_rows = 128; /* "fp8_swapped_rows": most token rows the weight-streaming
                                    (swapped, split-K) FP8 modes take, 64 or 128 */
     int cluster_split = 1; /* "cluster_split": K split inside a thread-block cluster: 0 never,

@@ -1,34 +1,37 @@
 /*
  * FP8 E4M3 block-scaled GEMM for many token rows with 256-column tiles.
  *
- * The 128 x 128 tiles of fp8_block_rows take in 32 KB of operands per 128-deep K
- * block, i.e. per 256 tensor-pipe cycles, and an SM cannot be fed that fast from
- * L2: the pipe is busy less than a third of the time. The kernels here halve
- * the bytes per multiplication.
+ * What bounds the 128 x 128 tiles of fp8_block_rows is neither the operand feed
+ * nor the promotion but the one thread that issues the MMAs. Measured on B200
+ * with a stand-alone loop: a kind::f8f6f4 MMA of M = 128, N = 128, K = 32 keeps
+ * the tensor pipe busy for 64 cycles, N = 256 for 128 cycles; issuing one costs
+ * the thread some 55 cycles and every tcgen05.commit about 100 more, and the
+ * pipe only stays busy while the thread runs ahead of it. A 128-deep K block of
+ * a 128 x 128 tile is four 64-cycle MMAs, a commit for the accumulator and half
+ * a commit for the stage, plus two barrier waits: about 600 cycles of issue for
+ * 256 cycles of arithmetic (with the operand loads removed altogether the kernel
+ * took the same 199 us; with the promotion removed, 185 us). So here every MMA
+ * is N = 256 wide, a K block costs four of them and ONE commit, and the stage
+ * is handed back to the producer by a promotion warp, not by a second commit:
  *
- *   Pair = false  one CTA per 128-row x 256-column tile: 48 KB per 512 cycles.
+ *   Pair = false  one CTA per 128-row x 256-column tile.
  *   Pair = true   two CTAs of a cluster per 256-row x 256-column tile with
- *                 tcgen05.mma.cta_group::2: every CTA stages its own 128 token
- *                 rows and half of the weight rows, 32 KB per 512 cycles.
+ *                 tcgen05.mma.cta_group::2: one thread issues for both SMs, the
+ *                 commit arrives on both CTAs' barriers at once (multicast),
+ *                 every CTA stages its own 128 token rows and 128 of the weight
+ *                 rows: half the issue work and half the operand bytes per flop.
  *
  * The scales (FP32 per 1 x 128 activation block and per 128 x 128 weight block)
  * make every K block a fresh accumulation that is promoted in registers,
  *     acc = fma(block sum, a_scale[row, g] * w_scale[band, g], acc)   g ascending,
  * with one rounding at the end - the same arithmetic as fp8_block_rows, bit for
- * bit. The hand-over between the tensor pipe and the promotion warps is what a
- * wide tile makes hard, so it is cut fine: a K block is multiplied as two
- * N = 128 halves (one weight band each) into one of four 128-column
- * tensor-memory buffers (block parity x half), each with its own full/empty
- * barrier pair, and the issuer may run a whole K block ahead of the promotion.
- * Eight promotion warps per CTA: two per quarter of the tensor-memory lanes,
- * one for each half, 128 running sums per thread. They take 232 registers
- * (setmaxnreg), which the producer and issuer warps give up.
- *
- * In the pair form only the leader CTA issues MMAs; its commits arrive on the
- * barriers of both CTAs, and the promotion warps of the second CTA release a
- * buffer with an arrival on the leader's barrier through the cluster's shared
- * window. The scale products of the next two K blocks are fetched ahead so that
- * no global load sits between a finished block and its release.
+ * bit. Two 256-column accumulator buffers alternate. Eight promotion warps per
+ * CTA: two per quarter of the tensor-memory lanes, one for each 128-column weight
+ * band of the tile, 128 running sums per thread. They take 232 registers
+ * (setmaxnreg), which the producer and issuer warps give up. A buffer must be
+ * back within the 512 cycles of the next block's MMAs, so the recurring waits
+ * poll without suspending (mbarrier.test_wait) and a warp hands the buffer back
+ * as soon as its second load has landed, before the additions.
  */
 #pragma once
 
@@ -40,14 +43,14 @@ namespace fp8
 
 constexpr int kWideThreads = 384; /* warps 0-3: producer, MMA issuer, two spare; 4-11: promotion */
 constexpr int kWideColumns = 256;
-constexpr int kWideBuffers = 4;
+constexpr int kWideBuffers = 2;
+constexpr int kWideScaleAhead = 4; /* K blocks whose scales are in flight ahead of the promotion */
 constexpr int kWidePromotionRegisters = 232, kWideOtherRegisters = 40;
 
 template <bool Pair> struct WideSmem {
     static constexpr int kStages = Pair ? 6 : 4;
     static constexpr int kPBytes = 128 * 128;                   /* 128 token rows x 128 B */
     static constexpr int kQBytes = (Pair ? 128 : 256) * 128;    /* this CTA's weight rows */
-    static constexpr int kHalfBytes = kQBytes / 2;              /* the rows of one band */
     static constexpr int kStageBytes = kPBytes + kQBytes;
     static constexpr int kStaging = 8 * 4096; /* one 32 x 64 BF16 slab per promotion warp */
     static constexpr int kTotal = kStages * kStageBytes + kStaging + 512 + 1024;
@@ -62,6 +65,26 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t desc_a, u
                  "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
                  "}\n" ::"r"(tmem_d),
                  "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+/* One commit that arrives on the barrier at the same shared-memory offset in both
+ * CTAs of the pair. */
+__device__ __forceinline__ void umma_commit_both(uint32_t barrier)
+{
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+                 "[%0], %1;" ::"r"(barrier),
+                 "h"(both)
+                 : "memory");
+}
+
+/* Arrival on a barrier of the other CTA that orders nothing but itself: the
+ * tensor-memory loads it follows have completed (tcgen05.wait::ld), and a
+ * release at cluster scope would wait for this warp's unrelated stores. */
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_address)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address)
                  : "memory");
 }
 
@@ -118,7 +141,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         }
         for (int s = 0; s < kWideBuffers; ++s) {
             mbar_init(&tmem_full[s], 1);
-            mbar_init(&tmem_empty[s], Pair ? 8 : 4); /* the warps of one half, in every CTA */
+            mbar_init(&tmem_empty[s], Pair ? 16 : 8); /* every promotion warp of every CTA */
         }
         *abort = 0;
         fence_barrier_init();
@@ -172,21 +195,19 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                     uint8_t *p_tile = smem + stage * Layout::kStageBytes;
                     uint8_t *q_tile = p_tile + Layout::kPBytes;
                     if constexpr (Pair) {
-                        /* both CTAs' bytes are counted on the leader's barrier */
+                        /* both CTAs' bytes are counted on the leader's barrier; of the
+                         * tile's 256 weight rows this CTA stages 128 */
                         const uint32_t barrier = map_to_rank(smem_u32(&full[stage]), 0);
                         if (leader)
                             mbar_arrive_expect_tx(&full[stage], 2 * Layout::kStageBytes);
                         tma_load_2d_pair(p_tile, &map_p, barrier, kb * kBlockDepth, p_row, keep);
-                        /* of each band's 128 weight rows this CTA multiplies 64 */
-                        for (int half = 0; half < 2; ++half)
-                            tma_load_2d_pair(q_tile + half * Layout::kHalfBytes, &map_q, barrier,
-                                             kb * kBlockDepth,
-                                             cb * kWideColumns + half * 128 + int(rank) * 64, keep);
+                        tma_load_2d_pair(q_tile, &map_q, barrier, kb * kBlockDepth,
+                                         cb * kWideColumns + int(rank) * 128, keep);
                     } else {
                         mbar_arrive_expect_tx(&full[stage], Layout::kStageBytes);
                         tma_load_2d_hint(p_tile, &map_p, &full[stage], kb * kBlockDepth, p_row, keep);
                         for (int half = 0; half < 2; ++half)
-                            tma_load_2d_hint(q_tile + half * Layout::kHalfBytes, &map_q, &full[stage],
+                            tma_load_2d_hint(q_tile + half * 128 * 128, &map_q, &full[stage],
                                              kb * kBlockDepth, cb * kWideColumns + half * 128, keep);
                     }
                     if (++stage == kStages) {
@@ -199,54 +220,40 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                 for (int wait = 0; wait < 64; ++wait)
                     __nanosleep(1000);
         } else if (warp == 1 && lane == 0 && leader) {
-            /* ---- MMA issuer ---- */
-            constexpr uint32_t idesc = make_idesc(0, kTileRows, 128, 0, 0); /* E4M3 x E4M3 */
+            /* ---- MMA issuer: per K block two waits, four MMAs, one commit ---- */
+            constexpr uint32_t idesc = make_idesc(0, kTileRows, kWideColumns, 0, 0); /* E4M3 x E4M3 */
             uint32_t stage = 0, phase = 0, block = 0;
             bool ok = true;
             for (int tile = worker; ok && tile < tiles; tile += workers) {
-                for (int kb = 0; ok && kb < groups; ++kb, ++block) {
-                    if (!mbar_wait(&full[stage], phase, abort)) {
+                for (int kb = 0; kb < groups; ++kb, ++block) {
+                    const uint32_t buffer = block & 1, use = block >> 1;
+                    if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                        report(task.status, abort, kRoleMmaTmemEmpty);
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait_polling(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
                     }
+                    tcgen05_fence_after();
                     const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
                     const uint64_t desc_p = desc_kmajor_sw128(p_address);
-                    for (int half = 0; half < 2; ++half) {
-                        const uint32_t buffer = (block & 1) * 2 + half, use = block >> 1;
-                        if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
-                            report(task.status, abort, kRoleMmaTmemEmpty);
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        const uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes +
-                                                                  half * Layout::kHalfBytes);
-                        const uint32_t tmem_d = tmem_base + buffer * 128;
-#pragma unroll
-                        for (int k = 0; k < kBlockDepth / 32; ++k) { /* 32 E4M3 = 32 bytes per MMA */
-                            if constexpr (Pair)
-                                umma_f8_pair(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc,
-                                             k > 0 ? 1u : 0u);
-                            else
-                                umma_f8(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, k > 0 ? 1u : 0u);
-                        }
-                        if constexpr (Pair) {
-                            const uint32_t local = smem_u32(&tmem_full[buffer]);
-                            umma_commit_pair(local);
-                            umma_commit_pair(map_to_rank(local, 1));
-                        } else {
-                            umma_commit(&tmem_full[buffer]);
-                        }
-                    }
-                    if (!ok)
-                        break;
+                    const uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
+                    const uint32_t tmem_d = tmem_base + buffer * kWideColumns;
                     if constexpr (Pair) {
-                        const uint32_t local = smem_u32(&empty[stage]);
-                        umma_commit_pair(local);
-                        umma_commit_pair(map_to_rank(local, 1));
+                        umma_f8_pair(tmem_d, desc_p, desc_q, idesc, 0u);
+                        umma_f8_pair(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
+                        umma_f8_pair(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
+                        umma_f8_pair(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
+                        umma_commit_both(smem_u32(&tmem_full[buffer]));
                     } else {
-                        umma_commit(&empty[stage]);
+                        umma_f8(tmem_d, desc_p, desc_q, idesc, 0u);
+                        umma_f8(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
+                        umma_f8(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
+                        umma_f8(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
+                        umma_commit(&tmem_full[buffer]);
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -264,7 +271,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         uint32_t release = smem_u32(&tmem_empty[0]);
         if constexpr (Pair)
             release = map_to_rank(release, 0);
-        uint32_t block = 0;
+        uint32_t block = 0, stage = 0;
         bool ok = true;
         for (int tile = worker; ok && tile < tiles; tile += workers) {
             int rb, cb;
@@ -280,48 +287,63 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 #pragma unroll
             for (int i = 0; i < 128; ++i)
                 acc[i] = 0.f;
-            /* scale products of this block and the next: fetched two blocks ahead */
-            float now = __fmul_rn(row_scale[0], band_scale[0]);
-            float next = groups > 1 ? __fmul_rn(row_scale[1], band_scale[1]) : 0.f;
-            for (int kb = 0; kb < groups; ++kb, ++block) {
-                const uint32_t buffer = (block & 1) * 2 + half, use = block >> 1;
-                float own = 0.f, weight = 0.f;
-                if (kb + 2 < groups) {
-                    own = row_scale[kb + 2];
-                    weight = band_scale[kb + 2];
-                }
-                if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
-                    report(task.status, abort, kRoleEpilogueFull);
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t taddr =
-                    tmem_base + buffer * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
-                const float scale = now;
+            /* the scales of the next kWideScaleAhead K blocks are in flight */
+            float own[kWideScaleAhead], weight[kWideScaleAhead];
 #pragma unroll
-                for (int chunk = 0; chunk < 2; ++chunk) {
-                    uint32_t piece[64];
-                    tmem_ld_32x64(taddr + chunk * 64, piece);
-                    tmem_ld_wait();
-                    if (chunk == 1) {
-                        /* the buffer is in registers: hand it back before the additions */
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if constexpr (Pair)
-                                mbar_arrive_cluster(release + buffer * 8);
-                            else
-                                mbar_arrive(&tmem_empty[buffer]);
-                        }
+            for (int j = 0; j < kWideScaleAhead; ++j) {
+                const int at = min(j, groups - 1);
+                own[j] = row_scale[at];
+                weight[j] = band_scale[at];
+            }
+            for (int kb_group = 0; ok && kb_group < groups; kb_group += kWideScaleAhead) {
+#pragma unroll
+                for (int j = 0; j < kWideScaleAhead; ++j) {
+                    const int kb = kb_group + j;
+                    if (kb >= groups)
+                        break;
+                    const uint32_t buffer = block & 1, use = block >> 1;
+                    ++block;
+                    const float scale = __fmul_rn(own[j], weight[j]);
+                    if (kb + kWideScaleAhead < groups) {
+                        own[j] = row_scale[kb + kWideScaleAhead];
+                        weight[j] = band_scale[kb + kWideScaleAhead];
                     }
+                    if (!mbar_wait_polling(&tmem_full[buffer], use & 1, abort)) {
+                        report(task.status, abort, kRoleEpilogueFull);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    /* the block's MMAs are done, so its operand stage is free: the
+                     * first promotion warp says so, which spares the issuer a commit */
+                    if (warp == 4 && lane == 0)
+                        mbar_arrive(&empty[stage]);
+                    if (++stage == kStages)
+                        stage = 0;
+                    const uint32_t taddr = tmem_base + buffer * kWideColumns + half * 128 +
+                                           (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        acc[chunk * 64 + i] =
-                            fmaf(__uint_as_float(piece[i]), scale, acc[chunk * 64 + i]);
+                    for (int chunk = 0; chunk < 2; ++chunk) {
+                        uint32_t piece[64];
+                        tmem_ld_32x64(taddr + chunk * 64, piece);
+                        tmem_ld_wait();
+                        if (chunk == 1) {
+                            /* the buffer is in registers: hand it back before the additions */
+                            tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) {
+                                if constexpr (Pair)
+                                    mbar_arrive_cluster_relaxed(release + buffer * 8);
+                                else
+                                    mbar_arrive(&tmem_empty[buffer]);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 64; ++i)
+                            acc[chunk * 64 + i] =
+                                fmaf(__uint_as_float(piece[i]), scale, acc[chunk * 64 + i]);
+                    }
                 }
-                now = next;
-                next = __fmul_rn(own, weight);
             }
             if (!ok)
                 break;
@@ -399,7 +421,7 @@ inline int block_gemm_wide(camblas_cuda_context *context, bool pair, int rows, i
     CUtensorMap p, qm, d;
     const auto type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
     bool ok = encode_2d(context, &p, type, 1, q, inner, rows, inner, 128, 128) &&
-              encode_2d(context, &qm, type, 1, w, inner, outputs, inner, 128, pair ? 64 : 128) &&
+              encode_2d(context, &qm, type, 1, w, inner, outputs, inner, 128, 128) &&
               encode_2d(context, &d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, outputs, rows,
                         size_t(ldo) * 2, 64, 32);
     if (!ok)

@@ -71,7 +71,8 @@ namespace peer
 constexpr int kMaxWorld = 8;
 constexpr int kFlagWords = 65536; /* word 0: delivery counter; word 1: CTAs of the reduction
                                      done; words 64..: one arrival word per slab, then one
-                                     word per slab counting the CTAs that have read it */
+                                     word per slab counting the CTAs that have read it, then
+                                     one word per tile counting its finished slabs */
 constexpr int kFlagHeader = 64;
 constexpr int kMaxUnits = 24576; /* slabs of the tile path: two words each from kFlagHeader on */
 /* The rest of the flag words belongs to the all-reduce of small tensors: one
@@ -82,7 +83,8 @@ constexpr int kSmallChunkElements = 2048; /* 256 threads x 8 BF16 */
 constexpr long long kLineMaxElements = 64 * 8192; /* 1 MiB of BF16: 64 token rows of 8192 */
 constexpr int kLineChunks = int(kLineMaxElements / kSmallChunkElements);
 constexpr int kLineBase = kFlagWords - kLineChunks;
-constexpr int kSmallBase = kFlagHeader + 2 * kMaxUnits;
+constexpr int kTileBase = kFlagHeader + 2 * kMaxUnits; /* one word per tile: its finished slabs */
+constexpr int kSmallBase = kTileBase + kMaxUnits / 8;
 constexpr int kSmallChunks = (kLineBase - kSmallBase) / 3;
 /* A flagged line is 16 bytes: two 8-byte halves of 4 payload bytes and a 4-byte
  * flag each. One rank's tensor takes at most kLineSlotLines of them. */
@@ -152,7 +154,7 @@ __device__ __forceinline__ void accumulate8(float (&sum)[8], const uint4 &packed
     }
 }
 
-/* Waits until `expected` slabs have been delivered to this GPU, then clears the counter. */
+/* Waits until `expected` tiles have been delivered to this GPU, then clears the counter. */
 __device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned expected,
                                                unsigned *status, unsigned long long wait_ns)
 {
@@ -170,8 +172,13 @@ __device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned exp
  * applies bias and residual, rounds once and writes the piece, now as ordinary
  * matrix rows (eight threads store 128 contiguous bytes of a row), into every
  * GPU's result. The CTAs of a slab count themselves on the slab's second flag
- * word; the last one clears both words, before any of its deliveries is
- * announced, so the next call finds them zero. With `wait_inline` the CTA that
+ * word; the last one clears both words, so the next call finds them zero, and
+ * counts the slab on the tile's word. The CTA that completes a tile announces
+ * it to every GPU with one system-scope addition per GPU: a delivery counter
+ * takes one addition per tile from its owner, not one per CTA (thousands of
+ * remote additions to one word serialise and cost tens of microseconds). The
+ * counts are chained by fences, so the announcement is ordered after the stores
+ * of every CTA of the tile. With `wait_inline` the CTA that
  * finishes last also waits for the deliveries to this GPU, which saves the
  * launch of peer_wait_delivered. */
 __global__ void __launch_bounds__(256)
@@ -184,7 +191,10 @@ __global__ void __launch_bounds__(256)
     const int unit = (rb * task.c_blocks + cb) * 8 + slab;
     unsigned *const arrived = task.arrive + unit;
     unsigned *const readers = task.arrive + kMaxUnits + unit;
+    unsigned *const slabs_done = task.arrive + 2 * kMaxUnits + (rb * task.c_blocks + cb);
+    __shared__ int announce;
     if (threadIdx.x == 0) {
+        announce = 0;
         const bool ok = sm100::flag_wait_system(arrived, unsigned(task.world), task.wait_ns);
         if (!ok)
             atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
@@ -237,11 +247,15 @@ __global__ void __launch_bounds__(256)
         if (atomicAdd(readers, 1u) == unsigned(chunks) - 1u) {
             sm100::flag_store_relaxed_system(readers, 0u);
             sm100::flag_store_relaxed_system(arrived, 0u);
+            if (atomicAdd(slabs_done, 1u) == 7u) {
+                *slabs_done = 0u;
+                announce = 1;
+            }
         }
         __threadfence_system();
     }
     __syncthreads();
-    if (!failed && threadIdx.x < task.world)
+    if (announce && threadIdx.x < task.world)
         sm100::flag_add_release_system(task.delivered[threadIdx.x], 1u);
     if (wait_inline && threadIdx.x == 0) {
         /* word 1 of this GPU's flags counts the CTAs of this launch that are done */
@@ -629,7 +643,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
             config.numAttrs = 1;
             wait_inline = (call.phases & 4) != 0;
             cudaError_t error = cudaLaunchKernelEx(&config, peer_reduce_broadcast, task,
-                                                   unsigned(units * (bn / 64)), int(wait_inline));
+                                                   unsigned(units / 8), int(wait_inline));
             if (error != cudaSuccess)
                 return fail(context, "peer reduction and broadcast", error);
             context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
@@ -637,7 +651,7 @@ inline int run(camblas_cuda_context *context, const Call &call)
     }
     if ((call.phases & 4) && !wait_inline) {
         peer_wait_delivered<<<1, 32, 0, context->stream>>>(
-            own.flags, unsigned(units * (bn / 64)), context->status,
+            own.flags, unsigned(units / 8), context->status,
             1000000ull * unsigned(context->options.peer_wait_ms));
         return launched(context, "peer delivery wait");
     }
@@ -760,7 +774,7 @@ extern "C" int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, i
         const size_t chunks = (count + peer::kSmallChunkElements - 1) / peer::kSmallChunkElements;
         if (count > capacity || chunks > size_t(peer::kSmallChunks))
             return host::fail(context,
-                              "peer all-reduce exceeds the region capacity or 10.9 million elements", 1);
+                              "peer all-reduce exceeds the region capacity or 8.8 million elements", 1);
         if (count <= size_t(peer::kLineMaxElements)) {
             peer::LineTask task{};
             task.rank = rank, task.world = world;

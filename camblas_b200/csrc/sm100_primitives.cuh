@@ -131,6 +131,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+/* The same bounded wait with a poll that never suspends the thread
+ * (mbarrier.test_wait): for hand-overs that recur every few hundred cycles,
+ * where the time a suspended try_wait takes to resume is the cost that counts. */
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                 "selp.u32 %0, 1, 0, p;\n"
+                 "}\n"
+                 : "=r"(done)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_polling(uint64_t *bar, uint32_t parity,
+                                                  volatile uint32_t *abort)
+{
+    unsigned long long started = 0;
+    for (uint32_t spin = 0; spin < (kSpinLimit << 4); ++spin) {
+        if (mbar_test_wait(bar, parity))
+            return true;
+        if ((spin & 4095u) == 4095u) {
+            if (*abort)
+                return false;
+            const unsigned long long now = global_timer_ns();
+            if (started == 0)
+                started = now;
+            else if (now - started > kWaitLimitNs)
+                return false;
+        }
+    }
+    return false;
+}
+
 __device__ __forceinline__ bool flag_wait_system(const unsigned *word, unsigned target,
                                                  unsigned long long limit_ns)
 {

@@ -249,7 +249,7 @@ int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, 
  * buffers alternate. Larger tensors are stored into this rank's staging slot on
  * every GPU, announced and acknowledged through counted flag words per chunk of
  * 2048 elements. All ranks must make the same sequence of calls with the same
- * count. count is a multiple of 8, at most min(capacity, 10 964 992); input and
+ * count. count is a multiple of 8, at most min(capacity, 8 867 840); input and
  * output 16-byte
  * aligned, output may be input. `phases` is 3 in production; 1 (send) and 2
  * (receive and add) exist so that one process can drive several ranks on one
@@ -374,8 +374,10 @@ int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *
  *                    to 256, 0 = off (CAMBLAS_B200_PAIR_MODE=width=<n>)
  *   "push_width"     0, 128 or 256: tile width of the peer-memory row-parallel
  *                    product (CAMBLAS_B200_PUSH_WIDTH)
- *   "fp8_rows"       0 current, 1 four-warp, 2 one-block-per-stage FP8 row
- *                    kernel; same bits (CAMBLAS_B200_FP8_ROWS=four|single)
+ *   "fp8_rows"       which many-row FP8 kernel, all with the same bits: 0 by size,
+ *                    1 four-warp, 2 one-block-per-stage, 5 current 128 x 128
+ *                    tiles, 3 / 4 128 x 256 tiles on one SM / 256 x 256 on two
+ *                    (CAMBLAS_B200_FP8_ROWS=four|single)
  *   "fp8_swapped_rows" 64..128: most token rows for which the FP8 block GEMM
  *                    streams the weights with the K range split over the SMs
  *                    instead of tiling the rows (default 128)

@@ -180,3 +180,36 @@ def test_benchmark_shapes(outputs, inner, rows):
             oracle.fp8_dequantize(q_host, qs_host, 1),
             oracle.fp8_dequantize(wq_host[lo:hi], w_scale_host[band:band + 1], 128))
         assert oracle.rel_l2(actual, dequantised) <= FP8_TOLERANCE
+
+
+@pytest.mark.parametrize("rows,outputs,inner", [
+    (129, 264, 128),      # one ragged tile, a second band of eight columns
+    (300, 384, 256),      # ragged rows, a half-used column tile
+    (1000, 2112, 512),    # the last column tile holds 64 columns
+    (4096, 4096, 1536),   # the size at which the 256-column tiles are the default
+    (2304, 7168, 2048),   # an odd number of 128-row blocks: the last pair holds one
+])
+def test_many_row_kernels_give_the_same_bits(rng, rows, outputs, inner):
+    """The 128 x 128 row kernel (option fp8_rows = 5), the 128 x 256 form (3), the two-SM
+    256 x 256 form (4) and the choice by size (0) promote the same block sums in the same
+    order, so their outputs agree bit for bit; the first is checked against the oracle's
+    recurrence on a sample of rows."""
+    generator = torch.Generator(device="cuda").manual_seed(705541 + rows)
+    x = torch.randn(rows, inner, device="cuda", generator=generator).bfloat16()
+    w = torch.randn(outputs, inner, device="cuda", generator=generator).bfloat16()
+    q, q_scale = _kernels.fp8_quantize(x)
+    wq_host, w_scale_host = oracle.fp8_quantize_weight(tensor_to_bits(w))
+    wq, w_scale = fp8_tensor(wq_host), torch.from_numpy(w_scale_host).cuda()
+    results = {}
+    for variant in (5, 3, 4, 0):
+        with _native.options(fp8_rows=variant):
+            results[variant] = _kernels.fp8_block_gemm(q, q_scale, wq, w_scale)
+            torch.cuda.synchronize()
+            assert _native.context(0).device_status() == 0
+    for variant in (3, 4, 0):
+        assert torch.equal(results[variant], results[5]), variant
+    sample = np.unique(np.linspace(0, rows - 1, 5).astype(int))
+    expected = oracle.bf16_values(oracle.fp8_block_gemm(fp8_bytes(q)[sample], q_scale.cpu().numpy()[sample],
+                                                        wq_host[:256], w_scale_host[:2]))
+    actual = results[5][sample][:, :256].float().cpu().numpy()
+    assert oracle.rel_l2(actual, expected) < 4e-3

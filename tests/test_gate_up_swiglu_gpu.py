@@ -65,8 +65,10 @@ def test_matches_oracle_and_two_step(rows, inner, intermediate):
     expected = oracle.bf16_values(oracle_two_step(x, w))
     assert oracle.rel_l2(oracle.bf16_values(tensor_to_bits(fused)), expected) <= BF16_TOLERANCE
     if rows > 128:
-        # the two-step path runs the same two-SM kernel over the same K ranges here
-        assert torch.equal(fused, two_step(bits_to_tensor(x), w_device))
+        # with the K split inside a cluster switched off the two-step path runs the same
+        # two-SM kernel over the same K ranges, so the bits must agree
+        with _native.options(cluster_split=0):
+            assert torch.equal(fused, two_step(bits_to_tensor(x), w_device))
     else:
         reference = two_step(bits_to_tensor(x), w_device).float()
         assert ((fused.float() - reference).norm() / reference.norm()).item() <= BF16_TOLERANCE
