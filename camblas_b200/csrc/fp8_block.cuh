@@ -601,7 +601,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
                     const int blocks = min(Sub, kb1 - kb);
                     for (int sub = 0; sub < blocks; ++sub, ++block) {
                         const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
-                        if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                        if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
                             report(task.status, abort, kRoleMmaTmemEmpty);
                             ok = false;
                             break;
@@ -619,7 +619,10 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
                     }
                     if (!ok)
                         break;
-                    umma_commit(&empty[stage]);
+                    /* no commit for the stage: the first promotion warp hands it back
+                     * once it has seen the stage's last block complete (a commit
+                     * costs this thread about a hundred cycles, and this thread's
+                     * instruction stream is what the tensor pipe waits for) */
                     if (++stage == Stages) {
                         stage = 0;
                         phase ^= 1;
@@ -631,7 +634,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
         const int quarter = warp & 3;       /* tensor-memory lanes 32*quarter .. +31 */
         const int half = (warp - 2) >> 2;   /* columns 64*half .. +63 of the tile */
         uint8_t *slab = staging + (warp - 2) * 4096;
-        uint32_t block = 0;
+        uint32_t block = 0, stage = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
             int rb, cb, kb0, kb1;
             decode(unit, rb, cb);
@@ -653,12 +656,19 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
                     own = lane_scale[kb + 1];
                     band = band_scale[kb + 1];
                 }
-                if (!mbar_wait(&tmem_full[buffer], use & 1, abort)) {
+                if (!mbar_wait_polling(&tmem_full[buffer], use & 1, abort)) {
                     report(task.status, abort, kRoleEpilogueFull);
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after();
+                /* the last block of a stage is done: its operands may be overwritten */
+                if (((kb - kb0) % Sub) == Sub - 1 || kb == kb1 - 1) {
+                    if (warp == 2 && lane == 0)
+                        mbar_arrive(&empty[stage]);
+                    if (++stage == Stages)
+                        stage = 0;
+                }
                 uint32_t piece[64];
                 tmem_ld_32x64(tmem_base + buffer * BN + half * 64 +
                                   (static_cast<uint32_t>(quarter * 32) << 16),

@@ -164,10 +164,16 @@ __device__ __forceinline__ void wait_delivered(unsigned *delivered, unsigned exp
         atomicCAS(status, 0u, unsigned(sm100::kRolePeerDelivered));
 }
 
-/* grid = (column blocks this GPU owns, 8 * r_blocks, width / 64); 256 threads.
- * Each CTA finishes 64 columns of one 32-row slab of one owned tile - in the
- * staging layout (see sm100::epilogue_push) that is one contiguous 4 KB chunk
- * per rank: it waits for the slab's `world` partial copies, adds them in rank
+/* grid = (column blocks this GPU owns, 8 * r_blocks, 1..width / 64); 256 threads.
+ * The CTAs of a slab (32 rows of one owned tile) share its 64-column pieces - in
+ * the staging layout (see sm100::epilogue_push) a piece is one contiguous 4 KB
+ * chunk per rank. The host picks their number so that the launch has some 256
+ * CTAs: with eight ranks a GPU owns few slabs and needs four CTAs on each to keep
+ * its NVLink ports busy; with two ranks one CTA per slab is right, because the
+ * CTAs become resident while the product kernel still runs (programmatic
+ * dependent launch) and every one of them polls a flag, which a thousand of them
+ * did at the product's expense (tp2 step 0.368 -> 0.391 ms). A CTA
+ * waits for the slab's `world` partial copies, adds them in rank
  * order (one 16-byte piece per thread, all ranks' loads in flight together),
  * applies bias and residual, rounds once and writes the piece, now as ordinary
  * matrix rows (eight threads store 128 contiguous bytes of a row), into every
@@ -187,7 +193,7 @@ __global__ void __launch_bounds__(256)
     __shared__ int failed;
     const int cb = task.rank + blockIdx.x * task.world;
     const int rb = blockIdx.y >> 3, slab = blockIdx.y & 7;
-    const int chunk = blockIdx.z, chunks = gridDim.z;
+    const int chunks = gridDim.z; /* CTAs that share this slab */
     const int unit = (rb * task.c_blocks + cb) * 8 + slab;
     unsigned *const arrived = task.arrive + unit;
     unsigned *const readers = task.arrive + kMaxUnits + unit;
@@ -203,39 +209,43 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     if (!failed) {
         const int r = threadIdx.x >> 3, piece = threadIdx.x & 7;
-        const int row = rb * 256 + slab * 32 + r, c = cb * task.width + chunk * 64 + piece * 8;
-        const long long offset = static_cast<long long>(unit) * (32 * task.width) + chunk * 2048 +
-                                 r * 64 + ((piece ^ (r & 7)) << 3);
-        uint4 part[kMaxWorld];
-#pragma unroll
-        for (int s = 0; s < kMaxWorld; ++s)
-            if (s < task.world)
-                part[s] = __ldcg(
-                    reinterpret_cast<const uint4 *>(task.staging + s * task.slot_elements + offset));
-        if (row < task.rows && c < task.cols) {
-            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const int row = rb * 256 + slab * 32 + r;
+        /* the slab's 64-column pieces are dealt out to the CTAs of the slab in turn */
+        for (int chunk = blockIdx.z; chunk < task.width / 64; chunk += chunks) {
+            const int c = cb * task.width + chunk * 64 + piece * 8;
+            const long long offset = static_cast<long long>(unit) * (32 * task.width) + chunk * 2048 +
+                                     r * 64 + ((piece ^ (r & 7)) << 3);
+            uint4 part[kMaxWorld];
 #pragma unroll
             for (int s = 0; s < kMaxWorld; ++s)
                 if (s < task.world)
-                    accumulate8(sum, part[s]);
-            if (task.bias != nullptr)
-                accumulate8(sum, *reinterpret_cast<const uint4 *>(task.bias + c));
-            if (task.residual != nullptr)
-                accumulate8(sum, *reinterpret_cast<const uint4 *>(
-                                     task.residual + static_cast<long long>(row) * task.ld_residual +
-                                     c));
-            uint4 packed;
-            packed.x = sm100::pack_bf16(sum[0], sum[1]);
-            packed.y = sm100::pack_bf16(sum[2], sum[3]);
-            packed.z = sm100::pack_bf16(sum[4], sum[5]);
-            packed.w = sm100::pack_bf16(sum[6], sum[7]);
-            const long long target_offset = static_cast<long long>(row) * task.cols + c;
-            /* start with the next GPU so that the owners do not all write to the same one */
-            for (int hop = 1; hop <= task.world; ++hop) {
-                int target = task.rank + hop;
-                if (target >= task.world)
-                    target -= task.world;
-                *reinterpret_cast<uint4 *>(task.result[target] + target_offset) = packed;
+                    part[s] = __ldcg(reinterpret_cast<const uint4 *>(
+                        task.staging + s * task.slot_elements + offset));
+            if (row < task.rows && c < task.cols) {
+                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < task.world)
+                        accumulate8(sum, part[s]);
+                if (task.bias != nullptr)
+                    accumulate8(sum, *reinterpret_cast<const uint4 *>(task.bias + c));
+                if (task.residual != nullptr)
+                    accumulate8(sum,
+                                *reinterpret_cast<const uint4 *>(
+                                    task.residual + static_cast<long long>(row) * task.ld_residual + c));
+                uint4 packed;
+                packed.x = sm100::pack_bf16(sum[0], sum[1]);
+                packed.y = sm100::pack_bf16(sum[2], sum[3]);
+                packed.z = sm100::pack_bf16(sum[4], sum[5]);
+                packed.w = sm100::pack_bf16(sum[6], sum[7]);
+                const long long target_offset = static_cast<long long>(row) * task.cols + c;
+                /* start with the next GPU so that the owners do not all write to the same one */
+                for (int hop = 1; hop <= task.world; ++hop) {
+                    int target = task.rank + hop;
+                    if (target >= task.world)
+                        target -= task.world;
+                    *reinterpret_cast<uint4 *>(task.result[target] + target_offset) = packed;
+                }
             }
         }
         __threadfence_system();
@@ -633,7 +643,9 @@ inline int run(camblas_cuda_context *context, const Call &call)
              * may become resident while that kernel still runs (it says so at its
              * start) and wait on the arrival words, not on the kernel boundary. */
             cudaLaunchConfig_t config = {};
-            config.gridDim = dim3(owned, 8 * r_blocks, bn / 64);
+            const int slabs = owned * 8 * r_blocks;
+            const int share = std::max(1, std::min(bn / 64, 256 / slabs));
+            config.gridDim = dim3(owned, 8 * r_blocks, share == 3 ? 2 : share);
             config.blockDim = dim3(256);
             config.stream = context->stream;
             cudaLaunchAttribute attribute[1];
