@@ -25,13 +25,18 @@
  * make every K block a fresh accumulation that is promoted in registers,
  *     acc = fma(block sum, a_scale[row, g] * w_scale[band, g], acc)   g ascending,
  * with one rounding at the end - the same arithmetic as fp8_block_rows, bit for
- * bit. Two 256-column accumulator buffers alternate. Eight promotion warps per
- * CTA: two per quarter of the tensor-memory lanes, one for each 128-column weight
- * band of the tile, 128 running sums per thread. They take 232 registers
- * (setmaxnreg), which the producer and issuer warps give up. A buffer must be
- * back within the 512 cycles of the next block's MMAs, so the recurring waits
- * poll without suspending (mbarrier.test_wait) and a warp hands the buffer back
- * as soon as its second load has landed, before the additions.
+ * bit. Two 256-column accumulator buffers alternate, each with an issuing thread
+ * of its own (warps 1 and 2: even and odd K blocks), because even this K block
+ * costs one thread some 1 100 cycles (two barrier polls 500, four MMAs and a
+ * commit 500) against 512 cycles of MMA. Eight promotion warps per CTA: two per
+ * quarter of the tensor-memory lanes, one for each 128-column weight band of the
+ * tile, 128 running sums per thread. They take 232 registers (setmaxnreg), which
+ * the producer and issuer warps give up. The recurring waits poll without
+ * suspending (mbarrier.test_wait) and a warp hands the buffer back as soon as
+ * its second load has landed, before the additions. What is left (about 950
+ * cycles per K block, 55 % of the pipe): the promotion warps are busy three
+ * quarters of the time, their tensor-memory loads taking several times longer
+ * next to running MMAs than alone.
  */
 #pragma once
 
@@ -219,46 +224,45 @@ __global__ void __launch_bounds__(kWideThreads, 1)
             if (!ok) /* loads in flight must land before the CTA may leave */
                 for (int wait = 0; wait < 64; ++wait)
                     __nanosleep(1000);
-        } else if (warp == 1 && lane == 0 && leader) {
-            /* ---- MMA issuer: per K block two waits, four MMAs, one commit ---- */
+        } else if ((warp == 1 || warp == 2) && lane == 0 && leader) {
+            /* ---- two MMA issuers: warp 1 takes the even K blocks (accumulator buffer
+             * 0), warp 2 the odd ones (buffer 1). Timed inside the kernel, one thread
+             * needs about 1 100 cycles per K block - two barrier polls (500), four
+             * MMAs and a commit (500), the loop - against 512 cycles of MMA; with two
+             * threads, each has two blocks' time for it. The blocks use different
+             * accumulators and different operand stages, so their MMAs need no order
+             * between them. */
             constexpr uint32_t idesc = make_idesc(0, kTileRows, kWideColumns, 0, 0); /* E4M3 x E4M3 */
-            uint32_t stage = 0, phase = 0, block = 0;
-            bool ok = true;
-            for (int tile = worker; ok && tile < tiles; tile += workers) {
-                for (int kb = 0; kb < groups; ++kb, ++block) {
-                    const uint32_t buffer = block & 1, use = block >> 1;
-                    if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
-                        report(task.status, abort, kRoleMmaTmemEmpty);
-                        ok = false;
-                        break;
-                    }
-                    if (!mbar_wait_polling(&full[stage], phase, abort)) {
-                        report(task.status, abort, kRoleMma);
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
-                    const uint64_t desc_p = desc_kmajor_sw128(p_address);
-                    const uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
-                    const uint32_t tmem_d = tmem_base + buffer * kWideColumns;
-                    if constexpr (Pair) {
-                        umma_f8_pair(tmem_d, desc_p, desc_q, idesc, 0u);
-                        umma_f8_pair(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
-                        umma_f8_pair(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
-                        umma_f8_pair(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
-                        umma_commit_both(smem_u32(&tmem_full[buffer]));
-                    } else {
-                        umma_f8(tmem_d, desc_p, desc_q, idesc, 0u);
-                        umma_f8(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
-                        umma_f8(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
-                        umma_f8(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
-                        umma_commit(&tmem_full[buffer]);
-                    }
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+            const uint32_t buffer = warp - 1;
+            const uint32_t tmem_d = tmem_base + buffer * kWideColumns;
+            const int total = ((tiles - worker + workers - 1) / workers) * groups;
+            for (int block = int(buffer); block < total; block += 2) {
+                const uint32_t use = uint32_t(block) >> 1;
+                const uint32_t stage = uint32_t(block) % kStages, phase = (uint32_t(block) / kStages) & 1;
+                if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                    report(task.status, abort, kRoleMmaTmemEmpty);
+                    break;
+                }
+                if (!mbar_wait_polling(&full[stage], phase, abort)) {
+                    report(task.status, abort, kRoleMma);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t p_address = smem_u32(smem + stage * Layout::kStageBytes);
+                const uint64_t desc_p = desc_kmajor_sw128(p_address);
+                const uint64_t desc_q = desc_kmajor_sw128(p_address + Layout::kPBytes);
+                if constexpr (Pair) {
+                    umma_f8_pair(tmem_d, desc_p, desc_q, idesc, 0u);
+                    umma_f8_pair(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
+                    umma_f8_pair(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
+                    umma_f8_pair(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
+                    umma_commit_both(smem_u32(&tmem_full[buffer]));
+                } else {
+                    umma_f8(tmem_d, desc_p, desc_q, idesc, 0u);
+                    umma_f8(tmem_d, desc_p + 2, desc_q + 2, idesc, 1u);
+                    umma_f8(tmem_d, desc_p + 4, desc_q + 4, idesc, 1u);
+                    umma_f8(tmem_d, desc_p + 6, desc_q + 6, idesc, 1u);
+                    umma_commit(&tmem_full[buffer]);
                 }
             }
         }
