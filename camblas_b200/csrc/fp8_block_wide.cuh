@@ -73,17 +73,6 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t desc_a, u
                  : "memory");
 }
 
-/* One commit that arrives on the barrier at the same shared-memory offset in both
- * CTAs of the pair. */
-__device__ __forceinline__ void umma_commit_both(uint32_t barrier)
-{
-    const uint16_t both = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-                 "[%0], %1;" ::"r"(barrier),
-                 "h"(both)
-                 : "memory");
-}
-
 /* Arrival on a barrier of the other CTA that orders nothing but itself: the
  * tensor-memory loads it follows have completed (tcgen05.wait::ld), and a
  * release at cluster scope would wait for this warp's unrelated stores. */
