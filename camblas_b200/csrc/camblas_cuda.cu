@@ -10,6 +10,7 @@
 #include "fp8_block.cuh"
 #include "fp8_block_wide.cuh"
 #include "gemm_simt.cuh"
+#include "dense_fp.cuh"
 #include "quantized.cuh"
 #include "rms_norm.cuh"
 #include "row_parallel.cuh"
@@ -825,26 +826,191 @@ extern "C" int camblas_cuda_dgemm(camblas_cuda_context *context, char trans_a, c
 {
     return simt_gemm<double>(context, trans_a, trans_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
 }
-extern "C" int camblas_cuda_affine(camblas_cuda_context *context, int, int, int, int, const void *,
-                                   const void *, const void *, int, void *)
+namespace
 {
-    return host::unavailable(context, "camblas_cuda_affine");
+/* ---- FP32 / FP64 layer compositions on the CUDA-core GEMM -----------------------
+ * Row-major operands; a row-major product X . W is the column-major product
+ * W . X of the same buffers, which is how the GEMM is called. */
+
+/* out[rows][columns] = act(x[rows][inner] . w[inner][columns] + bias[columns]) */
+template <typename T>
+int affine_layer(camblas_cuda_context *context, int rows, int inner, int columns, const T *x, const T *w,
+                 const T *bias, bool relu, T *out)
+{
+    return guarded(context, [&] {
+        if (rows < 0 || inner < 0 || columns < 0)
+            return fail(context, "invalid affine dimensions", 1);
+        if (rows == 0 || columns == 0)
+            return 0;
+        if (!out || !bias || (inner > 0 && (!x || !w)))
+            return fail(context, "missing affine operand", 1);
+        context->counts[3]++;
+        int status = simt_gemm<T>(context, 'N', 'N', columns, rows, inner, T(1), w, std::max(1, columns), x,
+                                  std::max(1, inner), T(0), out, columns);
+        if (status != 0)
+            return status;
+        const long long count = 1ll * rows * columns;
+        dense::add_bias<T><<<unsigned(std::min<long long>((count + 255) / 256, 65535)), 256, 0,
+                             context->stream>>>(out, bias, count, columns, relu ? 1 : 0);
+        return launched(context, "bias and activation");
+    });
 }
-extern "C" int camblas_cuda_mlp(camblas_cuda_context *context, int, int, int, int, int,
-                                const void *, const void *, const void *, const void *,
-                                const void *, void *, void *)
+
+/* out[queries][values] = softmax(scale q . k^T) . v; the scores live in the
+ * context's scratch arena between the two products. */
+template <typename T>
+int attention_layer(camblas_cuda_context *context, int queries, int keys, int depth, int values, T scale,
+                    const T *q, const T *k, const T *v, T *out)
 {
-    return host::unavailable(context, "camblas_cuda_mlp");
+    return guarded(context, [&] {
+        if (queries < 0 || keys < 0 || depth < 0 || values < 0)
+            return fail(context, "invalid attention dimensions", 1);
+        if (queries == 0 || values == 0)
+            return 0;
+        if (!out || (depth > 0 && !q) || (keys > 0 && depth > 0 && !k) || (keys > 0 && !v))
+            return fail(context, "missing attention operand", 1);
+        if (keys > 0 && size_t(queries) > SIZE_MAX / sizeof(T) / size_t(keys))
+            return fail(context, "attention scratch size overflow", 2);
+        context->counts[6]++;
+        int status = host::reserve_scratch(context, std::max<size_t>(16, size_t(queries) * keys * sizeof(T)));
+        if (status != 0)
+            return status;
+        T *scores = static_cast<T *>(context->scratch);
+        status = simt_gemm<T>(context, 'T', 'N', keys, queries, depth, T(1), k, std::max(1, depth), q,
+                              std::max(1, depth), T(0), scores, std::max(1, keys));
+        if (status != 0)
+            return status;
+        if (keys > 0) {
+            dense::softmax_scaled<T><<<unsigned(queries), 256, 0, context->stream>>>(scores, keys, scale);
+            status = launched(context, "attention softmax");
+            if (status != 0)
+                return status;
+        }
+        return simt_gemm<T>(context, 'N', 'N', values, queries, keys, T(1), v, std::max(1, values), scores,
+                            std::max(1, keys), T(0), out, std::max(1, values));
+    });
 }
-extern "C" int camblas_cuda_attention(camblas_cuda_context *context, int, int, int, int, int,
-                                      double, const void *, const void *, const void *, void *)
+
+/* First derivatives of out = relu(x . w1 + b1) . w2 + b2 with respect to
+ * whatever is requested (non-NULL): dw2 = h^T . g, db2 = column sums of g,
+ * dh = (g . w2^T) where h > 0, db1 = column sums of dh, dw1 = x^T . dh,
+ * dx = dh . w1^T. */
+template <typename T>
+int perceptron_backward(camblas_cuda_context *context, int rows, int inputs, int hidden, int outputs,
+                        const T *x, const T *w1, const T *w2, const T *h, const T *g, T *dh, T *dx, T *dw1,
+                        T *db1, T *dw2, T *db2)
 {
-    return host::unavailable(context, "camblas_cuda_attention");
+    return guarded(context, [&] {
+        if (rows < 0 || inputs < 0 || hidden < 0 || outputs < 0)
+            return fail(context, "invalid backward dimensions", 1);
+        const bool first_layer = dx || dw1 || db1;
+        if ((rows > 0 && outputs > 0 && !g) || (rows > 0 && hidden > 0 && first_layer && (!dh || !h)))
+            return fail(context, "missing backward operand", 1);
+        context->counts[7]++;
+        int status = 0;
+        if (dw2) {
+            status = simt_gemm<T>(context, 'N', 'T', outputs, hidden, rows, T(1), g, std::max(1, outputs), h,
+                                  std::max(1, hidden), T(0), dw2, std::max(1, outputs));
+            if (status != 0)
+                return status;
+        }
+        if (db2 && outputs > 0) {
+            dense::column_sums<T, false><<<unsigned((outputs + 127) / 128), 128, 0, context->stream>>>(
+                const_cast<T *>(g), nullptr, rows, outputs, db2);
+            status = launched(context, "output bias gradient");
+            if (status != 0)
+                return status;
+        }
+        if (!first_layer)
+            return 0;
+        status = simt_gemm<T>(context, 'T', 'N', hidden, rows, outputs, T(1), w2, std::max(1, outputs), g,
+                              std::max(1, outputs), T(0), dh, std::max(1, hidden));
+        if (status != 0)
+            return status;
+        if (hidden > 0) {
+            dense::column_sums<T, true><<<unsigned((hidden + 127) / 128), 128, 0, context->stream>>>(
+                dh, h, rows, hidden, db1);
+            status = launched(context, "hidden gradient gate");
+            if (status != 0)
+                return status;
+        }
+        if (dw1) {
+            status = simt_gemm<T>(context, 'N', 'T', hidden, inputs, rows, T(1), dh, std::max(1, hidden), x,
+                                  std::max(1, inputs), T(0), dw1, std::max(1, hidden));
+            if (status != 0)
+                return status;
+        }
+        if (dx)
+            status = simt_gemm<T>(context, 'T', 'N', inputs, rows, hidden, T(1), w1, std::max(1, hidden), dh,
+                                  std::max(1, hidden), T(0), dx, std::max(1, inputs));
+        return status;
+    });
 }
-extern "C" int camblas_cuda_mlp_backward(camblas_cuda_context *context, int, int, int, int, int,
-                                         const void *, const void *, const void *, const void *,
-                                         const void *, void *, void *, void *, void *, void *,
-                                         void *)
+} // namespace
+
+/* Replaces camblas_cuda_affine (camblas_cuda.h:73-75; backend.cu:870-911, 1086-1101). */
+extern "C" int camblas_cuda_affine(camblas_cuda_context *context, int dtype, int rows, int inner,
+                                   int columns, const void *x, const void *weight, const void *bias,
+                                   int relu, void *output)
 {
-    return host::unavailable(context, "camblas_cuda_mlp_backward");
+    if (dtype == 0)
+        return affine_layer<float>(context, rows, inner, columns, static_cast<const float *>(x),
+                                   static_cast<const float *>(weight), static_cast<const float *>(bias),
+                                   relu != 0, static_cast<float *>(output));
+    if (dtype == 1)
+        return affine_layer<double>(context, rows, inner, columns, static_cast<const double *>(x),
+                                    static_cast<const double *>(weight), static_cast<const double *>(bias),
+                                    relu != 0, static_cast<double *>(output));
+    return fail(context, "unsupported affine dtype", 1);
+}
+
+/* Replaces camblas_cuda_mlp (camblas_cuda.h:76-78; backend.cu:1103-1117): two affine
+ * layers, ReLU after the first, whose output the caller keeps for the backward pass. */
+extern "C" int camblas_cuda_mlp(camblas_cuda_context *context, int dtype, int rows, int inputs,
+                                int hidden, int outputs, const void *x, const void *w1, const void *b1,
+                                const void *w2, const void *b2, void *hidden_output, void *output)
+{
+    int status = camblas_cuda_affine(context, dtype, rows, inputs, hidden, x, w1, b1, 1, hidden_output);
+    if (status != 0)
+        return status;
+    return camblas_cuda_affine(context, dtype, rows, hidden, outputs, hidden_output, w2, b2, 0, output);
+}
+
+/* Replaces camblas_cuda_attention (camblas_cuda.h:80-85; backend.cu:1495-1510). */
+extern "C" int camblas_cuda_attention(camblas_cuda_context *context, int dtype, int queries, int keys,
+                                      int depth, int values, double scale, const void *q,
+                                      const void *k, const void *v, void *output)
+{
+    if (dtype == 0)
+        return attention_layer<float>(context, queries, keys, depth, values, float(scale),
+                                      static_cast<const float *>(q), static_cast<const float *>(k),
+                                      static_cast<const float *>(v), static_cast<float *>(output));
+    if (dtype == 1)
+        return attention_layer<double>(context, queries, keys, depth, values, scale,
+                                       static_cast<const double *>(q), static_cast<const double *>(k),
+                                       static_cast<const double *>(v), static_cast<double *>(output));
+    return fail(context, "unsupported attention dtype", 1);
+}
+
+/* Replaces camblas_cuda_mlp_backward (camblas_cuda.h:87-99; backend.cu:1512-1535). */
+extern "C" int camblas_cuda_mlp_backward(camblas_cuda_context *context, int dtype, int rows, int inputs,
+                                         int hidden, int outputs, const void *x, const void *w1,
+                                         const void *w2, const void *h, const void *grad, void *dh,
+                                         void *dx, void *dw1, void *db1, void *dw2, void *db2)
+{
+    if (dtype == 0)
+        return perceptron_backward<float>(
+            context, rows, inputs, hidden, outputs, static_cast<const float *>(x),
+            static_cast<const float *>(w1), static_cast<const float *>(w2), static_cast<const float *>(h),
+            static_cast<const float *>(grad), static_cast<float *>(dh), static_cast<float *>(dx),
+            static_cast<float *>(dw1), static_cast<float *>(db1), static_cast<float *>(dw2),
+            static_cast<float *>(db2));
+    if (dtype == 1)
+        return perceptron_backward<double>(
+            context, rows, inputs, hidden, outputs, static_cast<const double *>(x),
+            static_cast<const double *>(w1), static_cast<const double *>(w2),
+            static_cast<const double *>(h), static_cast<const double *>(grad), static_cast<double *>(dh),
+            static_cast<double *>(dx), static_cast<double *>(dw1), static_cast<double *>(db1),
+            static_cast<double *>(dw2), static_cast<double *>(db2));
+    return fail(context, "unsupported backward dtype", 1);
 }

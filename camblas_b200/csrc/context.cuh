@@ -107,13 +107,6 @@ inline int fail(camblas_cuda_context *context, const char *what, int code)
     return code > 0 ? -code : -1;
 }
 
-inline int unavailable(camblas_cuda_context *context, const char *name)
-{
-    char *message = context ? context->error : creation_error;
-    std::snprintf(message, 256, "%s is not provided by the B200 build", name);
-    return -1;
-}
-
 /* Run `work` with `device` current and put the caller's device back afterwards,
  * whichever way `work` ends. False, with `error` set and `work` not run, when
  * the device could not be made current. */

@@ -5,10 +5,9 @@
  * here with the same name, argument list and status convention, so a caller
  * compiled against the reference links against this library unchanged. Each
  * declaration cites the reference declaration and implementation it stands in
- * for. Entry points that are outside the GEMM path (affine, MLP, attention,
- * MLP backward) are exported but return -1 with a
- * message naming the operation; nothing here falls back to a CPU or to a vendor
- * GEMM library.
+ * for. The FP32 / FP64 entry points outside the BF16/FP8 GEMM path (sgemm, dgemm,
+ * affine, MLP, attention, MLP backward) run on a tiled CUDA-core GEMM of this
+ * library; nothing here falls back to a CPU or to a vendor GEMM library.
  *
  * Conventions shared by all entry points
  *   status      0 on success, negative on failure; the text of the last
@@ -80,9 +79,9 @@ const char *camblas_cuda_error(const camblas_cuda_context *context);
 int camblas_cuda_set_algorithm(camblas_cuda_context *context, int algorithm);
 /* Replace camblas_cuda_stats / reset_stats (camblas_cuda.h:211-215;
  * backend.cu:1477-1493). Slots: 0 classical GEMM launches (tcgen05, skinny and
- * generic kernels), 1 Strassen, 2 Gram (always 0), 3 affine (always 0), 4 LT
- * policy launches, 5 guarded classical fall-backs, 6 attention (0), 7 MLP
- * backward (0). length is 6 or 8. */
+ * generic kernels), 1 Strassen, 2 Gram (always 0), 3 affine layers, 4 LT
+ * policy launches, 5 guarded classical fall-backs, 6 attention calls, 7 MLP
+ * backward calls. length is 6 or 8. */
 int camblas_cuda_stats(const camblas_cuda_context *context, uint64_t *counts, int length);
 int camblas_cuda_reset_stats(camblas_cuda_context *context);
 
@@ -471,10 +470,17 @@ int camblas_cuda_dgemm(camblas_cuda_context *context, char trans_a, char trans_b
                        int k, double alpha, const double *a, int lda, const double *b, int ldb,
                        double beta, double *c, int ldc);
 
-/* ---- exported for link compatibility; not on the BF16/FP8 GEMM path ------- */
-/* Each returns -1 and sets "<name> is not provided by the B200 build".
- * Reference declarations: camblas_cuda.h:77-82 (affine, mlp), :87-89
- * (attention), :94-99 (mlp_backward). */
+/* ---- FP32 / FP64 layer compositions (off the BF16/FP8 GEMM path) ----------- */
+/* dtype 0 FP32, 1 FP64; all arrays row-major, contiguous, caller-owned; every
+ * product runs on the CUDA-core GEMM above, sums in a fixed order.
+ * Replace camblas_cuda_affine / _mlp (camblas_cuda.h:70-78; backend.cu:870-911,
+ * 1086-1117): output = x . weight + bias, ReLU on request; the MLP is two such
+ * layers with ReLU after the first, whose activations are returned in
+ * hidden_output. camblas_cuda_attention (camblas_cuda.h:80-85; fusion.cuh:95-156):
+ * softmax(scale q k^T) v for one head, no mask; the scores live in the context's
+ * scratch arena. camblas_cuda_mlp_backward (camblas_cuda.h:87-99;
+ * fusion.cuh:204-263): every non-NULL gradient is filled; grad_hidden is
+ * rows x hidden caller scratch, required when dx, dw1 or db1 is requested. */
 int camblas_cuda_affine(camblas_cuda_context *context, int dtype, int rows, int inner, int columns,
                         const void *x, const void *weight, const void *bias, int relu,
                         void *output);

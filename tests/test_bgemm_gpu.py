@@ -198,14 +198,6 @@ def test_argument_validation_and_error_text():
     assert library.camblas_cuda_set_algorithm(context.handle, 0) == 0
 
 
-def test_cold_entry_points_say_so():
-    context = _native.context(0)
-    library = _native.library()
-    status = library.camblas_cuda_attention(context.handle, 0, 1, 1, 1, 1, 1.0, None, None, None, None)
-    assert status == -1
-    assert error_text(context) == "camblas_cuda_attention is not provided by the B200 build"
-
-
 def test_counters_count_launches(rng):
     context = _native.context(0)
     before = _native.stats(0, reset=True)

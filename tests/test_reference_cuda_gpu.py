@@ -286,3 +286,121 @@ def test_sgemm_dgemm_against_the_reference_library_and_float64(both, rng, dtype,
             result = dc.cpu().numpy()
             assert np.all(np.isnan(result[:, m:])), "padding rows of C were written"
             assert np.all(np.abs(result[:, :m].T - exact) <= bound + 1e-300)
+
+
+def _device(array):
+    return torch.from_numpy(np.ascontiguousarray(array)).cuda()
+
+
+def _close(actual, exact, dtype, terms):
+    """rel-L2 within a few roundings of `dtype` per summed term."""
+    error = np.linalg.norm(actual.astype(np.float64) - exact) / max(np.linalg.norm(exact), 1e-300)
+    return error <= 16 * np.finfo(dtype).eps * np.sqrt(max(terms, 1))
+
+
+@pytest.mark.parametrize("dtype,code", [(np.float32, 0), (np.float64, 1)])
+@pytest.mark.parametrize("rows,inputs,hidden,outputs", [(5, 7, 9, 3), (130, 96, 200, 64), (1, 300, 1, 17)])
+def test_affine_and_two_layer_perceptron(both, rng, dtype, code, rows, inputs, hidden, outputs):
+    """camblas_cuda_affine (with and without ReLU) and camblas_cuda_mlp on both libraries
+    against float64: row-major x . w + bias, ReLU after the first layer, the hidden
+    activations handed back to the caller."""
+    ours, theirs = both
+    x = rng.standard_normal((rows, inputs)).astype(dtype)
+    w1, b1 = rng.standard_normal((inputs, hidden)).astype(dtype), rng.standard_normal(hidden).astype(dtype)
+    w2, b2 = rng.standard_normal((hidden, outputs)).astype(dtype), rng.standard_normal(outputs).astype(dtype)
+    hidden_exact = np.maximum(x.astype(np.float64) @ w1 + b1, 0)
+    plain_exact = x.astype(np.float64) @ w1 + b1
+    dx, dw1, db1, dw2, db2 = map(_device, (x, w1, b1, w2, b2))
+    for library in (ours, theirs):
+        out = torch.full((rows, hidden), float("nan"), dtype=dx.dtype, device="cuda")
+        library.call("affine", code, rows, inputs, hidden, pointer(dx), pointer(dw1), pointer(db1), 0,
+                     pointer(out))
+        torch.cuda.synchronize()
+        assert _close(out.cpu().numpy(), plain_exact, dtype, inputs)
+        h = torch.full((rows, hidden), float("nan"), dtype=dx.dtype, device="cuda")
+        y = torch.full((rows, outputs), float("nan"), dtype=dx.dtype, device="cuda")
+        library.call("mlp", code, rows, inputs, hidden, outputs, pointer(dx), pointer(dw1), pointer(db1),
+                     pointer(dw2), pointer(db2), pointer(h), pointer(y))
+        torch.cuda.synchronize()
+        assert _close(h.cpu().numpy(), hidden_exact, dtype, inputs)
+        assert _close(y.cpu().numpy(), h.cpu().numpy().astype(np.float64) @ w2 + b2, dtype, hidden)
+    counts = (ct.c_uint64 * 8)()
+    assert ours.lib.camblas_cuda_stats(ours.context, counts, 8) == 0 and counts[3] >= 3
+
+
+@pytest.mark.parametrize("dtype,code", [(np.float32, 0), (np.float64, 1)])
+@pytest.mark.parametrize("queries,keys,depth,values", [(4, 6, 8, 5), (100, 300, 64, 48), (8, 32, 256, 256),
+                                                       (3, 5000, 16, 7)])
+def test_single_head_attention(both, rng, dtype, code, queries, keys, depth, values):
+    """softmax(scale q k^T) v on both libraries against float64 (the third case is the one
+    the reference serves with its fused FP64 kernel, fusion.cuh:110-127)."""
+    ours, theirs = both
+    q = rng.standard_normal((queries, depth)).astype(dtype)
+    k = rng.standard_normal((keys, depth)).astype(dtype)
+    v = rng.standard_normal((keys, values)).astype(dtype)
+    scale = 1.0 / np.sqrt(depth)
+    scores = scale * (q.astype(np.float64) @ k.astype(np.float64).T)
+    weights = np.exp(scores - scores.max(axis=1, keepdims=True))
+    exact = (weights / weights.sum(axis=1, keepdims=True)) @ v
+    dq, dk, dv = map(_device, (q, k, v))
+    for library in (ours, theirs):
+        out = torch.full((queries, values), float("nan"), dtype=dq.dtype, device="cuda")
+        library.call("attention", code, queries, keys, depth, values, scale, pointer(dq), pointer(dk),
+                     pointer(dv), pointer(out))
+        torch.cuda.synchronize()
+        assert _close(out.cpu().numpy(), exact, dtype, depth + keys)
+
+
+@pytest.mark.parametrize("dtype,code", [(np.float32, 0), (np.float64, 1)])
+@pytest.mark.parametrize("rows,inputs,hidden,outputs", [(6, 5, 7, 4), (300, 64, 130, 33)])
+def test_perceptron_backward(both, rng, dtype, code, rows, inputs, hidden, outputs):
+    """All six gradients of the two-layer perceptron on both libraries against float64,
+    then a call that asks for the second layer's gradients only (NULL elsewhere)."""
+    ours, theirs = both
+    x = rng.standard_normal((rows, inputs)).astype(dtype)
+    w1 = rng.standard_normal((inputs, hidden)).astype(dtype)
+    w2 = rng.standard_normal((hidden, outputs)).astype(dtype)
+    h = np.maximum(x @ w1 + rng.standard_normal(hidden).astype(dtype), 0).astype(dtype)
+    g = rng.standard_normal((rows, outputs)).astype(dtype)
+    h64, g64 = h.astype(np.float64), g.astype(np.float64)
+    dh_exact = (g64 @ w2.astype(np.float64).T) * (h64 > 0)
+    exact = {"dh": dh_exact, "dx": dh_exact @ w1.astype(np.float64).T,
+             "dw1": x.astype(np.float64).T @ dh_exact, "db1": dh_exact.sum(axis=0),
+             "dw2": h64.T @ g64, "db2": g64.sum(axis=0)}
+    terms = {"dh": outputs, "dx": hidden, "dw1": rows, "db1": rows, "dw2": rows, "db2": rows}
+    dx_, dw1_, dw2_, dh_, dg_ = map(_device, (x, w1, w2, h, g))
+    for library in (ours, theirs):
+        outs = {name: torch.full(value.shape, float("nan"), dtype=dx_.dtype, device="cuda")
+                for name, value in exact.items()}
+        library.call("mlp_backward", code, rows, inputs, hidden, outputs, pointer(dx_), pointer(dw1_),
+                     pointer(dw2_), pointer(dh_), pointer(dg_), pointer(outs["dh"]), pointer(outs["dx"]),
+                     pointer(outs["dw1"]), pointer(outs["db1"]), pointer(outs["dw2"]), pointer(outs["db2"]))
+        torch.cuda.synchronize()
+        for name, value in exact.items():
+            assert _close(outs[name].cpu().numpy(), value, dtype, terms[name]), name
+        second = {name: torch.full(exact[name].shape, float("nan"), dtype=dx_.dtype, device="cuda")
+                  for name in ("dw2", "db2")}
+        library.call("mlp_backward", code, rows, inputs, hidden, outputs, pointer(dx_), pointer(dw1_),
+                     pointer(dw2_), pointer(dh_), pointer(dg_), None, None, None, None,
+                     pointer(second["dw2"]), pointer(second["db2"]))
+        torch.cuda.synchronize()
+        for name in second:
+            assert _close(second[name].cpu().numpy(), exact[name], dtype, rows), name
+
+
+def test_layer_compositions_reject_what_the_reference_rejects(both):
+    ours, _ = both
+    x = torch.zeros(4, 4, device="cuda")
+    for name, arguments in (
+            ("affine", (0, -1, 4, 4, pointer(x), pointer(x), pointer(x), 0, pointer(x))),
+            ("affine", (0, 4, 4, 4, pointer(x), pointer(x), None, 0, pointer(x))),
+            ("affine", (2, 4, 4, 4, pointer(x), pointer(x), pointer(x), 0, pointer(x))),
+            ("attention", (0, 4, 4, 4, 4, 1.0, pointer(x), pointer(x), pointer(x), None)),
+            ("attention", (3, 4, 4, 4, 4, 1.0, pointer(x), pointer(x), pointer(x), pointer(x))),
+            ("mlp_backward", (0, 4, 4, 4, 4, pointer(x), pointer(x), pointer(x), pointer(x), None,
+                              None, None, None, None, pointer(x), None))):
+        status = getattr(ours.lib, "camblas_cuda_" + name)(ours.context, *arguments)
+        assert status < 0, name
+    # empty problems succeed without touching anything
+    assert ours.lib.camblas_cuda_affine(ours.context, 0, 0, 4, 4, None, None, None, 0, None) == 0
+    assert ours.lib.camblas_cuda_attention(ours.context, 0, 0, 4, 4, 4, 1.0, None, None, None, None) == 0
