@@ -333,6 +333,97 @@ def gate_up_swiglu_fp8(x, weight_interleaved):
     return q, scale
 
 
+def gated_mlp(x, gate_weight, up_weight, down_weight):
+    """Bias-free SiLU-gated MLP for inference: ``linear(silu_multiply(linear(x, Wg), linear(x, Wu)), Wd)``.
+
+    The reference's ``gated_mlp`` (``torch_bindings.cpp:703-723``): two projections, the
+    elementwise product written over the gate, the down projection. ``GatedMLP`` does the
+    same with the first two projections and the product in one GEMM pass.
+    """
+    _require(x.dim() >= 1 and gate_weight.dim() == 2 and up_weight.dim() == 2 and down_weight.dim() == 2
+             and gate_weight.shape == up_weight.shape and x.shape[-1] == gate_weight.shape[1]
+             and down_weight.shape[1] == gate_weight.shape[0], "Invalid gated MLP dimensions")
+    return linear(silu_multiply(linear(x, gate_weight), linear(x, up_weight)), down_weight)
+
+
+class GatedMLP:
+    """The gated MLP with its weights prepared once: gate and up rows interleaved in blocks
+    of 128 so that ``gate_up_swiglu`` produces ``silu(gate) * up`` from one GEMM pass
+    (no ``[rows, 2 * intermediate]`` round trip through HBM), then the down projection.
+    Same roundings as ``gated_mlp``; the bits agree whenever the GEMM sums do. The
+    intermediate width must be a multiple of 128.
+    """
+
+    def __init__(self, gate_weight, up_weight, down_weight):
+        _require(gate_weight.dim() == 2 and gate_weight.shape == up_weight.shape
+                 and down_weight.dim() == 2 and down_weight.shape[1] == gate_weight.shape[0]
+                 and gate_weight.shape[0] % 128 == 0, "Invalid gated MLP dimensions")
+        self.gate_up = interleave_gate_up(torch.cat((gate_weight, up_weight)))
+        self.down = down_weight
+
+    def __call__(self, x):
+        return linear(gate_up_swiglu(x, self.gate_up), self.down)
+
+
+def _float_code(tensor):
+    _require(tensor.is_cuda and tensor.dtype in (torch.float32, torch.float64),
+             "operand must be a CUDA FP32 or FP64 tensor")
+    return 0 if tensor.dtype == torch.float32 else 1
+
+
+def affine(x, weight, bias, relu=False):
+    """``x @ weight + bias`` with optional ReLU in FP32 / FP64 (``camblas_cuda_affine``; the
+    reference's ``affine``, ``torch_bindings.cpp:738-770``, forward only). ``x`` is
+    ``[rows, inner]``, ``weight`` ``[inner, columns]``."""
+    code = _float_code(x)
+    _require(x.dim() == 2 and weight.dim() == 2 and bias.dim() == 1 and x.shape[1] == weight.shape[0]
+             and bias.shape[0] == weight.shape[1] and weight.dtype == x.dtype == bias.dtype
+             and weight.device == x.device == bias.device, "Invalid affine operands")
+    x2, w2, b2 = x.contiguous(), weight.contiguous(), bias.contiguous()
+    out = torch.empty((x.shape[0], weight.shape[1]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _native.context(x.device.index).call("affine", code, x.shape[0], x.shape[1], weight.shape[1],
+                                             _pointer(x2), _pointer(w2), _pointer(b2), int(bool(relu)),
+                                             _pointer(out))
+    return out
+
+
+def mlp(x, w1, b1, w2, b2):
+    """``relu(x @ w1 + b1) @ w2 + b2`` in FP32 / FP64 (``camblas_cuda_mlp``); returns
+    ``(output, hidden)`` - the hidden activations are what the backward pass needs."""
+    code = _float_code(x)
+    _require(x.dim() == 2 and w1.dim() == 2 and w2.dim() == 2 and x.shape[1] == w1.shape[0]
+             and w1.shape[1] == w2.shape[0] and b1.shape == (w1.shape[1],) and b2.shape == (w2.shape[1],)
+             and all(t.dtype == x.dtype and t.device == x.device for t in (w1, b1, w2, b2)),
+             "Invalid MLP operands")
+    operands = [t.contiguous() for t in (x, w1, b1, w2, b2)]
+    hidden = torch.empty((x.shape[0], w1.shape[1]), dtype=x.dtype, device=x.device)
+    out = torch.empty((x.shape[0], w2.shape[1]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _native.context(x.device.index).call("mlp", code, x.shape[0], x.shape[1], w1.shape[1], w2.shape[1],
+                                             *(_pointer(t) for t in operands), _pointer(hidden),
+                                             _pointer(out))
+    return out, hidden
+
+
+def attention(q, k, v, scale=None):
+    """Dense single-head ``softmax(scale * q @ k.T) @ v`` in FP32 / FP64, no mask
+    (``camblas_cuda_attention``); the default scale is ``1 / sqrt(depth)``."""
+    code = _float_code(q)
+    _require(q.dim() == 2 and k.dim() == 2 and v.dim() == 2 and q.shape[1] == k.shape[1]
+             and k.shape[0] == v.shape[0] and all(t.dtype == q.dtype and t.device == q.device for t in (k, v)),
+             "Invalid attention operands")
+    if scale is None:
+        scale = q.shape[1] ** -0.5 if q.shape[1] else 1.0
+    q2, k2, v2 = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty((q.shape[0], v.shape[1]), dtype=q.dtype, device=q.device)
+    with torch.cuda.device(q.device):
+        _native.context(q.device.index).call("attention", code, q.shape[0], k.shape[0], q.shape[1],
+                                             v.shape[1], float(scale), _pointer(q2), _pointer(k2),
+                                             _pointer(v2), _pointer(out))
+    return out
+
+
 def swiglu(gate, up, limit=0.0, routing=None):
     """Return ``rnd(silu(gate) * up [* routing[row]])`` with optional clipping."""
     _require(gate.is_cuda and gate.shape == up.shape and gate.dtype == up.dtype

@@ -133,3 +133,52 @@ def test_quantising_epilogue_equals_quantising_the_bf16_result(rows, inner, inte
     expected_q, expected_scale = _kernels.fp8_quantize(_kernels.gate_up_swiglu(x, mixed))
     assert torch.equal(scale, expected_scale)
     assert torch.equal(q.view(torch.uint8), expected_q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("rows,inner,intermediate", [(1, 256, 128), (40, 384, 256), (300, 512, 384)])
+def test_gated_mlp_function_and_prepared_module(rows, inner, intermediate):
+    """`gated_mlp` (the reference's torch_bindings.cpp:703-723: gate and up projections,
+    silu_multiply, down projection) against the oracle's BF16 linear layers and its
+    silu_multiply; `GatedMLP` (weights interleaved once, SwiGLU in the GEMM epilogue) against
+    the function - same roundings, so within the BF16 bound of one more GEMM."""
+    rng = np.random.default_rng(705560 + rows)
+    x = normal_bits(rng, (rows, inner))
+    gate, up = normal_bits(rng, (intermediate, inner), 0.06), normal_bits(rng, (intermediate, inner), 0.06)
+    down = normal_bits(rng, (inner, intermediate), 0.06)
+    hidden = oracle.silu_multiply_bf16(oracle.linear_bf16(x, gate), oracle.linear_bf16(x, up))
+    expected = oracle.bf16_values(oracle.linear_bf16(hidden, down))
+    tensors = [bits_to_tensor(a) for a in (x, gate, up, down)]
+    plain = _kernels.gated_mlp(*tensors)
+    assert _native.context(0).device_status() == 0
+    assert plain.shape == (rows, inner)
+    assert oracle.rel_l2(oracle.bf16_values(tensor_to_bits(plain)), expected) <= 2 * BF16_TOLERANCE
+    prepared = _kernels.GatedMLP(*tensors[1:])(tensors[0])
+    assert oracle.rel_l2(oracle.bf16_values(tensor_to_bits(prepared)), expected) <= 2 * BF16_TOLERANCE
+    difference = (prepared.float() - plain.float()).norm() / plain.float().norm()
+    assert difference.item() <= BF16_TOLERANCE
+    with pytest.raises(ValueError):
+        _kernels.gated_mlp(tensors[0], tensors[1], tensors[2][:-1], tensors[3])
+
+
+def test_python_wrappers_of_the_float_layers():
+    """`affine`, `mlp` and `attention` of the host mirror (FP32 / FP64 tensors) against torch."""
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    for dtype, tolerance in ((torch.float32, 1e-5), (torch.float64, 1e-13)):
+        x = torch.randn(33, 20, device="cuda", dtype=dtype, generator=generator)
+        w1 = torch.randn(20, 50, device="cuda", dtype=dtype, generator=generator)
+        b1 = torch.randn(50, device="cuda", dtype=dtype, generator=generator)
+        w2 = torch.randn(50, 7, device="cuda", dtype=dtype, generator=generator)
+        b2 = torch.randn(7, device="cuda", dtype=dtype, generator=generator)
+        hidden = torch.relu(x.double() @ w1.double() + b1.double())
+        assert torch.allclose(_kernels.affine(x, w1, b1, relu=True).double(), hidden, rtol=0,
+                              atol=tolerance * 50)
+        out, kept = _kernels.mlp(x, w1, b1, w2, b2)
+        assert torch.allclose(kept.double(), hidden, rtol=0, atol=tolerance * 50)
+        assert torch.allclose(out.double(), kept.double() @ w2.double() + b2.double(), rtol=0,
+                              atol=tolerance * 200)
+        q, k = x, torch.randn(9, 20, device="cuda", dtype=dtype, generator=generator)
+        v = torch.randn(9, 4, device="cuda", dtype=dtype, generator=generator)
+        expected = torch.softmax(q.double() @ k.double().T / 20 ** 0.5, dim=1) @ v.double()
+        assert torch.allclose(_kernels.attention(q, k, v).double(), expected, rtol=0, atol=tolerance * 50)
+    with pytest.raises(ValueError):
+        _kernels.affine(x.bfloat16(), w1, b1)
