@@ -686,6 +686,30 @@ inline int run_tensor_swapped(camblas_cuda_context *context, const Product &x)
     int bn = x.n <= 16 ? 16 : (x.n <= 32 ? 32 : 64);
     task.c_blocks = (x.n + bn - 1) / bn;
     task.k_blocks = (x.k + 63) / 64;
+    /* A few tiles more than whole waves (448 tiles of the Llama gate_up on 148 SMs:
+     * three waves and four tiles) would leave all but those few SMs idle for a
+     * whole tile's time, and splitting every tile's K to even that out costs a
+     * pass over `split` copies of the result. The leftover output rows are
+     * multiplied as a product of their own instead, which with so few tiles
+     * splits its K over all SMs: 181 -> 156 us at 64 tokens, 159 -> 153 at 32, 154 -> 150
+     * at 16. Up to eight tokens the partial sums are so small that splitting every
+     * tile is cheaper than the two extra launches (144 against 148 us at two tokens). */
+    const int sms = context->sm_count;
+    const int leftover = task.c_blocks == 1 ? task.r_blocks % sms : 0;
+    if (x.n > 8 && task.r_blocks > sms && leftover != 0 && 4 * leftover <= sms && task.k_blocks >= 32) {
+        const int whole = (task.r_blocks - leftover) * 128; /* output features of the whole waves */
+        Product head = x, tail = x;
+        head.m = whole, head.cut0 = head.cut1 = whole;
+        tail.m = x.m - whole, tail.cut0 = tail.cut1 = tail.m;
+        tail.a = x.a + whole * x.lda; /* 'T' operand: a block of weight rows */
+        tail.c = x.c + whole;
+        if (x.addend != nullptr)
+            tail.addend = x.addend + whole;
+        if (x.bias != nullptr)
+            tail.bias = x.bias + whole;
+        int status = run_tensor_swapped(context, head);
+        return status != 0 ? status : run_tensor_swapped(context, tail);
+    }
     task.split = choose_split(task.r_blocks * task.c_blocks, task.k_blocks, context->sm_count);
     task.split = split_if_it_pays(task.split, task.r_blocks * task.c_blocks, task.k_blocks,
                                   context->sm_count, x.n, x.m, bn);

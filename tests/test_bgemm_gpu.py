@@ -280,6 +280,31 @@ def test_full_size_properties(tokens, outputs, inner):
             assert (part == whole).float().mean() > 0.5
 
 
+@pytest.mark.parametrize("tokens", [9, 24, 64])
+def test_leftover_tiles_of_the_few_token_kernel_are_a_product_of_their_own(tokens):
+    """57 344 output features are 448 tiles of 128 on 148 SMs: three waves and four tiles. The
+    four are multiplied as a separate product (bias, residual and output offset by the
+    18 944 x 3 features before them): sampled features of both parts against the oracle, and
+    the leftover part bit for bit against the product of its weight rows alone."""
+    outputs, inner = 57344, 2048
+    generator = torch.Generator(device="cuda").manual_seed(705571 + tokens)
+    x = torch.randn(tokens, inner, device="cuda", generator=generator).bfloat16()
+    w = (torch.randn(outputs, inner, device="cuda", generator=generator) * 0.05).bfloat16()
+    bias = torch.randn(outputs, device="cuda", generator=generator).bfloat16()
+    residual = torch.randn(tokens, outputs, device="cuda", generator=generator).bfloat16()
+    y = _kernels.linear(x, w, bias, residual)
+    assert _native.context(0).device_status() == 0
+    whole = (outputs // 128 // 148) * 148 * 128
+    sample = torch.cat([torch.arange(0, whole, 7001, device="cuda"), torch.tensor([whole - 1], device="cuda"),
+                        torch.arange(whole, outputs, 37, device="cuda")])
+    expected = oracle.linear_bf16(tensor_to_bits(x), tensor_to_bits(w[sample]), tensor_to_bits(bias[sample]),
+                                  tensor_to_bits(residual[:, sample].contiguous()))
+    actual = y[:, sample].float().cpu().numpy()
+    assert oracle.rel_l2(actual, oracle.bf16_values(expected)) <= BF16_TOLERANCE
+    alone = _kernels.linear(x, w[whole:], bias[whole:], residual[:, whole:])
+    assert torch.equal(alone, y[:, whole:])
+
+
 @pytest.mark.parametrize("ta,tb", [("N", "N"), ("N", "T"), ("T", "N"), ("T", "T")])
 @pytest.mark.parametrize("m,n,k", [(256, 128, 64), (264, 136, 200), (520, 300, 72), (1024, 384, 1032)])
 def test_tensor_family_takes_every_transpose_pair(rng, ta, tb, m, n, k):
