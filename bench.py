@@ -495,27 +495,6 @@ def run_ours(args):
     plain_ms = across_ranks(torch, dist, world, device, begin.elapsed_time(end))
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- the same step for at least `--sustain` seconds: the clock under sustained load ----
-    sustained = None
-    if args.sustain > 0:
-        count = int(max(steps, min(200000, args.sustain * 1e3 / max(1e-3, plain_ms / steps))))
-        sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid))
-        if rank == 0:
-            sampler.start()
-        barrier()
-        begin.record()
-        for _ in range(count):
-            if resident is not None:
-                resident[0][0].replay()
-            else:
-                block.step(block.x, block.residual)
-        end.record()
-        barrier()
-        sustained_ms = across_ranks(torch, dist, world, device, begin.elapsed_time(end))
-        sustained = {"steps": count, "seconds": sustained_ms * 1e-3,
-                     "value": FLOPS_PER_STEP * count / (sustained_ms * 1e-3) / 1e12,
-                     "clocks": sampler.stop() if rank == 0 else None}
-
     # ---- end to end: pinned host activations in, result out, every step ----
     # Every step copies its own x and residual from pinned host memory and copies its
     # result back; the copies run on their own streams with two buffer sets, so the
@@ -591,6 +570,30 @@ def run_ours(args):
     expected_out = block.step(block.x, block.residual)
     torch.cuda.synchronize()
     e2e_matches = bool(torch.equal(host_out[(e2e_steps - 1) & 1][mine], expected_out[mine].cpu()))
+
+    # ---- the same step for at least `--sustain` seconds: the clock under sustained load ----
+    # (last of the measurements, so that the end-to-end leg above is not taken on a GPU
+    # that three seconds of full load have just driven into its power cap)
+    sustained = None
+    if args.sustain > 0:
+        count = int(max(steps, min(200000, args.sustain * 1e3 / max(1e-3, plain_ms / steps))))
+        sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid))
+        if rank == 0:
+            sampler.start()
+        barrier()
+        begin.record()
+        for _ in range(count):
+            if resident is not None:
+                resident[0][0].replay()
+            else:
+                block.step(block.x, block.residual)
+        end.record()
+        barrier()
+        sustained_ms = across_ranks(torch, dist, world, device, begin.elapsed_time(end))
+        sustained = {"steps": count, "seconds": sustained_ms * 1e-3,
+                     "value": FLOPS_PER_STEP * count / (sustained_ms * 1e-3) / 1e12,
+                     "clocks": sampler.stop() if rank == 0 else None}
+
 
     launches_before = _native.context(local).kernel_launches()
     block.step(block.x, block.residual)
