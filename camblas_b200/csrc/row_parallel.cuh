@@ -549,6 +549,149 @@ __global__ void __launch_bounds__(256) peer_lines_allreduce(const LineTask task,
     }
 }
 
+/* ---- the same through flagged lines in two steps, for four ranks and more ----------
+ *
+ * One shot sends every rank's whole tensor to every peer: 2 x (world - 1) x bytes
+ * of lines leave each GPU, 14 MB for a 1 MB tensor on eight ranks (27 us). With
+ * four ranks or more and enough data it is cheaper to cut the tensor into
+ * `world` slices: every rank sends slice o to rank o, which adds the `world`
+ * copies of its slice in rank order (same FP32 order and single rounding as the
+ * one-shot form, so the same bits) and sends the sum to every rank: two trips,
+ * but 2 x 2 x (world - 1) / world x bytes of lines per GPU, a quarter at eight
+ * ranks. The host takes this form where the one-shot form would send more than
+ * about 1.75 MB of payload per GPU. CTA c serves elements [2048 c, 2048 c + 2048) of EVERY slice. The
+ * first step uses the lines of chunk c of a slot, the second those of chunk
+ * kLineChunks / 2 + c, each with the call counter of its own chunk, so a line
+ * position always carries numbers of one counter whichever form wrote it last.
+ * `phases`: 1 send the slices, 2 add my slice and send the sum, 4 collect the
+ * sums and count the call. */
+constexpr int kLineHalf = kLineChunks / 2;
+
+struct SliceTask {
+    LineTask base;
+    long long slice; /* elements per slice, a multiple of 8; at most kLineHalf chunks */
+};
+
+/* Polls the two lines of every rank but `skip` until they carry `flag`; false when
+ * the limit ran out. part[s] holds the 16 payload bytes of rank s. */
+__device__ __forceinline__ bool collect_lines(const uint4 *inbox, int world, int skip, unsigned flag,
+                                              unsigned long long wait_ns, uint4 (&part)[kMaxWorld])
+{
+    unsigned long long started = 0;
+    for (uint32_t spin = 0; spin < sm100::kSpinLimit; ++spin) {
+        uint4 low[kMaxWorld], high[kMaxWorld];
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (s < world && s != skip) {
+                low[s] = load_line(inbox + size_t(s) * kLineSlotLines);
+                high[s] = load_line(inbox + size_t(s) * kLineSlotLines + 256);
+            }
+        bool complete = true;
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (s < world && s != skip) {
+                complete = complete && low[s].y == flag && low[s].w == flag && high[s].y == flag &&
+                           high[s].w == flag;
+                part[s] = make_uint4(low[s].x, low[s].z, high[s].x, high[s].z);
+            }
+        if (complete)
+            return true;
+        if ((spin & 63u) == 63u) {
+            const unsigned long long now = sm100::global_timer_ns();
+            if (started == 0)
+                started = now;
+            else if (now - started > wait_ns)
+                return false;
+        }
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(256) peer_lines_allreduce_sliced(const SliceTask sliced, int phases)
+{
+    const LineTask &task = sliced.base;
+    const int chunk = blockIdx.x;
+    const long long local = static_cast<long long>(chunk) * kSmallChunkElements + threadIdx.x * 8;
+    const bool in_slice = local < sliced.slice;
+    const unsigned flag_a = task.calls[chunk] + 1u, flag_b = task.calls[kLineHalf + chunk] + 1u;
+    const size_t buffer_a = size_t(flag_a & 1u) * size_t(task.world) * kLineSlotLines;
+    const size_t buffer_b = size_t(flag_b & 1u) * size_t(task.world) * kLineSlotLines;
+    const size_t first_a = size_t(chunk) * kLinesPerChunk + threadIdx.x;
+    const size_t first_b = size_t(kLineHalf + chunk) * kLinesPerChunk + threadIdx.x;
+    auto of_slice = [&](int owner) { return static_cast<long long>(owner) * sliced.slice + local; };
+    auto read_input = [&](int owner) {
+        const long long element = of_slice(owner);
+        return in_slice && element < task.elements
+                   ? *reinterpret_cast<const uint4 *>(task.input + element)
+                   : make_uint4(0u, 0u, 0u, 0u);
+    };
+    if (phases & 1) {
+        for (int hop = 1; hop < task.world; ++hop) {
+            int owner = task.rank + hop;
+            if (owner >= task.world)
+                owner -= task.world;
+            const uint4 piece = read_input(owner);
+            uint4 *const slot = task.slot_at[owner] + buffer_a + first_a;
+            store_line(slot, piece.x, piece.y, flag_a);
+            store_line(slot + 256, piece.z, piece.w, flag_a);
+        }
+    }
+    bool failed = false;
+    if (phases & 2) {
+        /* my slice: the other ranks' copies arrive in my line area, mine comes from `input` */
+        uint4 part[kMaxWorld];
+        const uint4 mine = read_input(task.rank);
+        if (collect_lines(task.lines + buffer_a + first_a, task.world, task.rank, flag_a, task.wait_ns,
+                          part)) {
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < task.world)
+                    accumulate8(sum, s == task.rank ? mine : part[s]);
+            uint4 packed;
+            packed.x = sm100::pack_bf16(sum[0], sum[1]);
+            packed.y = sm100::pack_bf16(sum[2], sum[3]);
+            packed.z = sm100::pack_bf16(sum[4], sum[5]);
+            packed.w = sm100::pack_bf16(sum[6], sum[7]);
+            for (int hop = 1; hop < task.world; ++hop) {
+                int target = task.rank + hop;
+                if (target >= task.world)
+                    target -= task.world;
+                uint4 *const slot = task.slot_at[target] + buffer_b + first_b;
+                store_line(slot, packed.x, packed.y, flag_b);
+                store_line(slot + 256, packed.z, packed.w, flag_b);
+            }
+            const long long element = of_slice(task.rank);
+            if (in_slice && element < task.elements)
+                *reinterpret_cast<uint4 *>(task.output + element) = packed;
+        } else {
+            failed = true;
+        }
+    }
+    if (phases & 4) {
+        uint4 part[kMaxWorld];
+        if (collect_lines(task.lines + buffer_b + first_b, task.world, task.rank, flag_b, task.wait_ns,
+                          part)) {
+#pragma unroll
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < task.world && s != task.rank) {
+                    const long long element = of_slice(s);
+                    if (in_slice && element < task.elements)
+                        *reinterpret_cast<uint4 *>(task.output + element) = part[s];
+                }
+        } else {
+            failed = true;
+        }
+        __syncthreads(); /* every thread has read the counters */
+        if (threadIdx.x == 0) {
+            task.calls[chunk] = flag_a == 0xFFFFFFFEu ? 0u : flag_a;
+            task.calls[kLineHalf + chunk] = flag_b == 0xFFFFFFFEu ? 0u : flag_b;
+        }
+    }
+    if (failed)
+        atomicCAS(task.status, 0u, sm100::kRolePeerArrive | (blockIdx.x << 4));
+}
+
 struct Call {
     int rank, world;
     size_t capacity;
@@ -772,7 +915,7 @@ extern "C" int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, i
 {
     return host::guarded(context, [&] {
         if (world < 1 || world > peer::kMaxWorld || rank < 0 || rank >= world || !memory ||
-            capacity == 0 || (phases & ~3) != 0 || phases == 0)
+            capacity == 0 || (phases & ~7) != 0 || phases == 0)
             return host::fail(context, "invalid all-reduce group description", 1);
         for (int r = 0; r < world; ++r)
             if (!memory[r])
@@ -803,7 +946,25 @@ extern "C" int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, i
             }
             task.status = context->status;
             task.wait_ns = 1000000ull * unsigned(context->options.peer_wait_ms);
-            peer::peer_lines_allreduce<<<unsigned(chunks), 256, 0, context->stream>>>(task, phases);
+            /* Two steps over slices where the one-shot form would send more than about
+             * 1.75 MB of payload per GPU (measured on four ranks: 1 MB 13.9 -> 10.8 us,
+             * 512 KB level, 128-256 KB 6-7 -> 8-9 us: the second trip costs some 3 us);
+             * `phases` 3 means all of it. */
+            if (world >= 4 && count * sizeof(__nv_bfloat16) * size_t(world - 1) >= 1792 * 1024) {
+                peer::SliceTask sliced{};
+                sliced.base = task;
+                sliced.slice = static_cast<long long>((count / size_t(world) + 7) / 8 * 8);
+                if (sliced.slice * world < static_cast<long long>(count))
+                    sliced.slice += 8;
+                const size_t slice_chunks =
+                    (size_t(sliced.slice) + peer::kSmallChunkElements - 1) / peer::kSmallChunkElements;
+                peer::peer_lines_allreduce_sliced<<<unsigned(slice_chunks), 256, 0, context->stream>>>(
+                    sliced, phases == 3 ? 7 : phases);
+                return host::launched(context, "peer all-reduce through flagged lines, sliced");
+            }
+            if ((phases & 3) == 0)
+                return 0; /* the third phase exists only in the sliced form */
+            peer::peer_lines_allreduce<<<unsigned(chunks), 256, 0, context->stream>>>(task, phases & 3);
             return host::launched(context, "peer all-reduce through flagged lines");
         }
         peer::SmallTask task{};

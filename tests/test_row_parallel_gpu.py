@@ -218,14 +218,16 @@ def test_expired_wait_reports_and_reset_recovers():
 
 
 @pytest.mark.parametrize("world,count", [(1, 8192), (2, 8), (2, 8192), (4, 64 * 8192), (8, 16 * 8192),
-                                         (8, 3 * 2048 + 264), (2, 64 * 8192 + 8), (3, 80 * 8192)])
+                                         (8, 3 * 2048 + 264), (2, 64 * 8192 + 8), (3, 80 * 8192),
+                                         (4, 40 * 8192), (8, 64 * 8192), (5, 33 * 8192 + 8), (7, 24 * 8192)])
 def test_small_all_reduce_sums_in_rank_order(world, count):
     """`camblas_cuda_peer_allreduce_bf16` with emulated ranks: every rank's result is the FP32
     sum of the ranks' tensors in rank order, rounded once - bit for bit - and stays so over
     repeated calls (both line buffers come round again; the counted flag words of the larger
     sizes hand themselves back), in place as well. Counts up to 64 x 8192 take the
-    flagged-line exchange, the last two cases the counted one. The two phases of the ranks
-    are issued in turn so that no kernel waits for an unlaunched one."""
+    flagged-line exchange (in one step, or with four ranks and more and enough data in two
+    steps over slices, which must give the same bits), the last two cases the counted one. The phases
+    of the ranks are issued in turn so that no kernel waits for an unlaunched one."""
     torch.manual_seed(705537 + world + count)
     capacity = PeerRegions.capacity_for(80, 8192)
     views = PeerRegions.emulate(capacity, world, 0)
@@ -238,7 +240,7 @@ def test_small_all_reduce_sums_in_rank_order(world, count):
             expected = total.bfloat16()
             outputs = [tensor.clone() if call == 2 else torch.empty_like(tensor) for tensor in inputs]
             sources = outputs if call == 2 else inputs  # third call: in place
-            for phase in (1, 2):
+            for phase in (1, 2, 4):  # the third phase exists in the sliced form only
                 for view, source, output in zip(views, sources, outputs):
                     view.all_reduce(source, out=output, phases=phase)
             torch.cuda.synchronize()
@@ -251,19 +253,20 @@ def test_small_all_reduce_sums_in_rank_order(world, count):
 
 def test_small_all_reduce_of_changing_sizes_never_takes_an_old_line_for_a_new_one():
     """Calls of different sizes share the chunks' call counters and line buffers: a long
-    tensor, then short ones, then the long one again. Lines that the short calls did not
-    touch still carry older call numbers and must not pass for current ones."""
+    tensor (two steps over slices at this size), then short ones and a medium one (one step),
+    then the long one again. Lines that a call did not touch still carry older call numbers,
+    of either form, and must not pass for current ones."""
     world = 4
     torch.manual_seed(20261201)
     views = PeerRegions.emulate(PeerRegions.capacity_for(64, 8192), world, 0)
     try:
-        for count in (32 * 8192, 8, 2048 + 8, 8, 32 * 8192, 4096, 32 * 8192):
+        for count in (48 * 8192, 8, 2048 + 8, 8, 48 * 8192, 4096, 32 * 8192, 48 * 8192):
             inputs = [torch.randn(count, device="cuda").bfloat16() for _ in range(world)]
             total = torch.zeros(count, device="cuda")
             for tensor in inputs:
                 total = total + tensor.float()
             outputs = [torch.empty_like(tensor) for tensor in inputs]
-            for phase in (1, 2):
+            for phase in (1, 2, 4):  # the third phase exists in the sliced form only
                 for view, source, output in zip(views, inputs, outputs):
                     view.all_reduce(source, out=output, phases=phase)
             torch.cuda.synchronize()
@@ -294,7 +297,7 @@ def test_small_all_reduce_whose_peer_never_sends_gives_up_and_reset_recovers():
             view.reset()
         torch.cuda.synchronize()
         outputs = [torch.empty_like(tensor) for tensor in inputs]
-        for phase in (1, 2):
+        for phase in (1, 2, 4):  # the third phase exists in the sliced form only
             for view, source, result in zip(views, inputs, outputs):
                 view.all_reduce(source, out=result, phases=phase)
         torch.cuda.synchronize()
