@@ -245,14 +245,17 @@ int camblas_cuda_linear_bf16_allreduce(camblas_cuda_context *context, int rank, 
  * beside the payload, the receiver polls the lines until the number is the
  * current one (bounded, "peer_wait_ms"), and the exchange costs one trip over
  * NVLink; the calls of one rank must then run in stream order, because two line
- * buffers alternate. Larger tensors are stored into this rank's staging slot on
+ * buffers alternate. With four ranks or more, where that would send more than
+ * about 1.75 MB per GPU, the tensor goes in two such trips over `world` slices
+ * (every rank adds one slice and sends the sum to all), with the same bits. Larger tensors are stored into this rank's staging slot on
  * every GPU, announced and acknowledged through counted flag words per chunk of
  * 2048 elements. All ranks must make the same sequence of calls with the same
  * count. count is a multiple of 8, at most min(capacity, 8 867 840); input and
  * output 16-byte
- * aligned, output may be input. `phases` is 3 in production; 1 (send) and 2
- * (receive and add) exist so that one process can drive several ranks on one
- * GPU in turn. After a wait has expired (device status) the region needs
+ * aligned, output may be input. `phases` is 3 in production (everything); 1
+ * (send), 2 (receive and add; in the two-trip form also send the sum) and 4
+ * (two-trip form: collect the sums; otherwise nothing) exist so that one process
+ * can drive several ranks on one GPU in turn. After a wait has expired (device status) the region needs
  * camblas_cuda_peer_reset. */
 int camblas_cuda_peer_allreduce_bf16(camblas_cuda_context *context, int rank, int world,
                                      size_t capacity, void *const *memory, int phases,
