@@ -433,32 +433,24 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
 
 /* ---- 2b. many token rows: eight promotion warps, four accumulator buffers ------ */
 
-/* Row mode for more than 128 token rows. Two warps share each quarter of the
- * tensor-memory lanes and take 64 columns each (64 accumulator registers, one
- * 64-column load, 64 FMAs per K block), so every scheduler has two promotion
- * warps to interleave, and the accumulator ring has four 128-column buffers
- * (all 512 tensor-memory columns) so that the MMA issuer can run up to three K
- * blocks ahead; a pipeline stage holds two K blocks. Bit-identical to the
- * four-warp kernel above and 8-9 % faster.
- * The arithmetic: acc = fma(block sum, a_scale * w_scale, acc) in ascending K
- * order, one rounding at the end.
+/* Row mode on 128 x 128 tiles, taken when 128 x 256 tiles (fp8_block_wide.cuh)
+ * would leave SMs without one. Two warps share each quarter of the tensor-memory
+ * lanes and take 64 columns each (64 accumulator registers, one 64-column load,
+ * 64 FMAs per K block), so every scheduler has two promotion warps to
+ * interleave, and the accumulator ring has four 128-column buffers (all 512
+ * tensor-memory columns); a pipeline stage holds two K blocks. The arithmetic:
+ * acc = fma(block sum, a_scale * w_scale, acc) in ascending K order, one
+ * rounding at the end; every form of the kernel gives the same bits.
  *
- * What bounds it (measured on B200, M=4096): not the promotion. With the
- * tensor-memory loads taken out the kernel takes the same time, and the tensor
- * pipe is busy 29 % of the cycles at exactly the FP8 rate when it is. A 128 x
- * 128 tile needs 32 KB of operands per 128-deep K block, i.e. per 256 MMA
- * cycles, and an SM takes in 40-50 bytes per cycle from L2 with the 192 KB of
- * stages it can keep in flight - the same feed that the BF16 two-SM kernel
- * spends on four times the multiplications. Wider tiles would fix the feed but
- * need 256 accumulator columns per row in registers next to the loaded block,
- * which ten warps cannot hold (168 registers per thread) and more warps even
- * less. A two-SM variant (256 x 128 tiles, 24 KB of operands per K block and
- * SM, same promotion) was built twice, gave the same bits and ran at half the
- * speed: with one accumulator hand-over per K block instead of per tile, the
- * round trip between the leader's MMA issuer and the other CTA's promotion
- * warps (remote barrier arrivals) is paid every 256 MMA cycles and the four
- * buffers cannot cover it. */
-constexpr int kRowsThreads = 320; /* producer, MMA issuer, eight promotion warps */
+ * What bounds it is the instruction stream of the thread that issues the MMAs,
+ * not the operand feed and not the promotion (with the loads removed the kernel
+ * took the same time, with the promotion removed 7 % less): issuing an MMA
+ * costs the thread some 55-100 cycles and a commit about 100, against 64 cycles
+ * that an M = 128, N = 128, K = 32 MMA occupies the pipe. Hence: the stage is
+ * handed back by a promotion warp instead of a second commit, the recurring
+ * waits poll without suspending, and two threads issue (even and odd K blocks,
+ * buffers 0/2 and 1/3): 185 -> 146 us at 4096 x 4096 x 7168. */
+constexpr int kRowsThreads = 352; /* producer, MMA issuer, eight promotion warps, second issuer */
 constexpr int kRowsBuffers = 4;
 
 template <int Stages, int Sub = 1> struct RowsSmem {
@@ -584,8 +576,13 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
                             if (mbar_try_wait(&full[s], (armed_parity >> s) & 1))
                                 break;
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 10) {
         if (lane == 0) {
+            /* Two issuing threads, the even K blocks on warp 1 and the odd ones on warp
+             * 10: four 64-cycle MMAs, a commit and two barrier polls cost one thread
+             * several times the 256 cycles the MMAs take (fp8_block_wide.cuh). The
+             * blocks go to different accumulator buffers, so they need no order. */
+            const uint32_t mine = warp == 1 ? 0u : 1u;
             constexpr uint32_t idesc = make_idesc(0, kBlockR, BN, 0, 0); /* E4M3 x E4M3 */
             uint32_t stage = 0, phase = 0, block = 0;
             bool ok = true;
@@ -600,6 +597,8 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
                     }
                     const int blocks = min(Sub, kb1 - kb);
                     for (int sub = 0; sub < blocks; ++sub, ++block) {
+                        if ((block & 1u) != mine)
+                            continue;
                         const uint32_t buffer = block % kRowsBuffers, use = block / kRowsBuffers;
                         if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
                             report(task.status, abort, kRoleMmaTmemEmpty);
