@@ -239,12 +239,16 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                 int kb1 = min(task.k_blocks, kb0 + task.k_blocks_per_split);
                 for (int kb = kb0; kb < kb1; ++kb, ++block) {
                     uint32_t buffer = block % kBuffers, use = block / kBuffers;
-                    if (!mbar_wait(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
+                    /* This one thread's instruction stream bounds the kernel when the
+                     * tiles are narrow: it polls instead of suspending, and commits once
+                     * per block; the stage goes back to the producer from the first
+                     * promotion warp, which sees the same completion. */
+                    if (!mbar_wait_polling(&tmem_empty[buffer], (use & 1) ^ 1, abort)) {
                         report(task.status, abort, kRoleMmaTmemEmpty);
                         ok = false;
                         break;
                     }
-                    if (!mbar_wait(&full[stage], phase, abort)) {
+                    if (!mbar_wait_polling(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
@@ -257,7 +261,6 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
 #pragma unroll
                     for (int k = 0; k < kBlockDepth / 32; ++k) /* 32 E4M3 = 32 bytes per MMA */
                         umma_f8(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, k > 0 ? 1u : 0u);
-                    umma_commit(&empty[stage]);
                     umma_commit(&tmem_full[buffer]);
                     if (++stage == Stages) {
                         stage = 0;
@@ -335,6 +338,9 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
                     break;
                 }
                 tcgen05_fence_after();
+                /* the block's products are complete, so its operand stage is free */
+                if (warp == 2 && lane == 0)
+                    mbar_arrive(&empty[block % Stages]);
                 const uint32_t taddr =
                     tmem_base + buffer * BN + (static_cast<uint32_t>(quarter * 32) << 16);
                 constexpr int kPiece = BN >= 64 ? 64 : (BN >= 32 ? 32 : 16);

@@ -908,7 +908,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tcgen05_fence_after();
                 uint32_t tmem_d = tmem_base + buffer * BN;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&full[stage], phase, abort)) {
+                    if (!mbar_wait_polling(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
