@@ -331,7 +331,7 @@ def kernel_family(name):
 
 
 _OPTION_DEFAULTS = {"pair_tail": 0, "pair_width": 0, "push_width": 0, "fp8_rows": 0,
-                    "fp8_swapped_rows": 128, "cluster_split": 1,
+                    "fp8_swapped_rows": 16, "cluster_split": 1,
                     "bf16_strassen": 0, "peer_wait_ms": 5000}
 
 

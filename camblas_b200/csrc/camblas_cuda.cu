@@ -199,7 +199,7 @@ extern "C" int camblas_cuda_set_option(camblas_cuda_context *context, const char
         {"pair_width", &options.pair_width, 0, 256},
         {"push_width", &options.push_width, 0, 256},
         {"fp8_rows", &options.fp8_rows, 0, 5},
-        {"fp8_swapped_rows", &options.fp8_swapped_rows, 64, 128},
+        {"fp8_swapped_rows", &options.fp8_swapped_rows, 0, 128},
         {"cluster_split", &options.cluster_split, 0, 2},
         {"bf16_strassen", &options.bf16_strassen, 0, 1},
         {"peer_wait_ms", &options.peer_wait_ms, 1, 60000},

@@ -926,17 +926,14 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
     task.status = context->status;
     CUtensorMap p, qm, d;
     const auto type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    /* Up to 128 token rows the product is bound by streaming the weights, and a
-     * 128 x 128 row tiling would leave most SMs idle (32 tiles for N = 4096): those
-     * shapes take the swapped kernel, one or two 64-token column blocks per weight
-     * band with the K range split over the SMs. */
-    /* between 65 and 128 rows the swapped kernel reads the weights twice (two
-     * 64-token column blocks); it still wins while the 128 x 128 row tiling has
-     * few tiles to offer (measured: N = 2112 16 against 30 us, N = 7168 15
-     * against 12 us) */
-    const bool swapped = rows <= 64 || (rows <= std::min(kSwappedRowLimit,
-                                                         context->options.fp8_swapped_rows) &&
-                                        outputs <= 24 * 128);
+    /* Few token rows: the product is bound by streaming the weights, and the
+     * swapped kernel puts them on the 128-row side with the tokens on a 16, 32 or
+     * 64 column side and the K range split over the SMs. The row tiling needs an
+     * output it can store through a tensor map; without one, up to 128 rows stay
+     * here whatever the limit. */
+    const bool storable = host::aligned16(out) && ldo % 8 == 0 && outputs % 8 == 0;
+    const bool swapped =
+        rows <= context->options.fp8_swapped_rows || (rows <= kSwappedRowLimit && !storable);
     /* Many token rows: 128 x 256 tiles with N = 256 MMAs (fp8_block_wide.cuh) as soon
      * as they give every SM a tile; measured 27-44 % faster than the 128 x 128 tiles
      * at 4096 rows (same bits), slower when they leave SMs idle (512 x 4096: 64

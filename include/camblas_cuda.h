@@ -380,9 +380,11 @@ int camblas_cuda_kernel_launches(const camblas_cuda_context *context, uint64_t *
  *                    1 four-warp, 2 one-block-per-stage, 5 current 128 x 128
  *                    tiles, 3 / 4 128 x 256 tiles on one SM / 256 x 256 on two
  *                    (CAMBLAS_B200_FP8_ROWS=four|single)
- *   "fp8_swapped_rows" 64..128: most token rows for which the FP8 block GEMM
- *                    streams the weights with the K range split over the SMs
- *                    instead of tiling the rows (default 128)
+ *   "fp8_swapped_rows" 0..128: most token rows for which the FP8 block GEMM
+ *                    puts the weights on the 128-row side of the tiles and
+ *                    the tokens on a 16 to 64 column side (default 16; an
+ *                    output that is not 16-byte aligned, or whose ldo is not
+ *                    a multiple of 8, stays there up to 128 rows)
  *   "cluster_split"  K split inside a thread-block cluster with the partial
  *                    sums added through distributed shared memory: 0 never,
  *                    1 for products of 65 token rows and more with few tiles

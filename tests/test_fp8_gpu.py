@@ -46,15 +46,21 @@ def test_row_quantiser_is_byte_exact(rng, rows, inner):
     assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(scale2, scale)
 
 
-@pytest.mark.parametrize("rows", [1, 5, 16, 33, 64, 65, 128, 300])
+@pytest.mark.parametrize("swapped_rows", [16, 128, 0])
+@pytest.mark.parametrize("rows", [1, 5, 16, 17, 33, 64, 65, 128, 300])
 @pytest.mark.parametrize("outputs,inner", [(128, 128), (264, 256), (1000, 1536), (2112, 512)])
-def test_block_gemm_against_oracle(rng, rows, outputs, inner):
+def test_block_gemm_against_oracle(rng, rows, outputs, inner, swapped_rows):
+    """Every row count through the default choice of kernel, through the swapped
+    (weights on the 128-row side) kernel wherever it is allowed, and through the row
+    tiling alone."""
     x, w = normal_bits(rng, (rows, inner)), normal_bits(rng, (outputs, inner))
     q, q_scale = oracle.fp8_quantize_rows(x)
     wq, w_scale = oracle.fp8_quantize_weight(w)
     expected = oracle.bf16_values(oracle.fp8_block_gemm(q, q_scale, wq, w_scale))
-    out = _kernels.fp8_block_gemm(fp8_tensor(q), torch.from_numpy(q_scale).cuda(), fp8_tensor(wq),
-                                  torch.from_numpy(w_scale).cuda())
+    with _native.options(fp8_swapped_rows=swapped_rows):
+        out = _kernels.fp8_block_gemm(fp8_tensor(q), torch.from_numpy(q_scale).cuda(),
+                                      fp8_tensor(wq), torch.from_numpy(w_scale).cuda())
+        torch.cuda.synchronize()
     assert _native.context(0).device_status() == 0
     error = oracle.rel_l2(out.float().cpu().numpy(), expected)
     assert error <= FP8_TOLERANCE and error < 4e-3, error
