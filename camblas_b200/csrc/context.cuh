@@ -90,6 +90,7 @@ struct camblas_cuda_context {
     /* clusters of each cluster-split kernel the device keeps resident, by kernel
      * slot and cluster size (0 not asked yet, -1 none) */
     int cluster_capacity[5][9] = {};
+    int fp8_cluster_capacity[9] = {}; /* the same for the FP8 row kernel, by cluster size */
     std::atomic<uint64_t> counts[8] = {};
     std::atomic<uint64_t> kernel_launches{0}; /* every kernel this context put on its stream */
     char error[256] = "";

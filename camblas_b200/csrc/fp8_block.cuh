@@ -459,21 +459,26 @@ __global__ void __launch_bounds__(sm100::kThreads, 1)
 constexpr int kRowsThreads = 352; /* producer, MMA issuer, eight promotion warps, second issuer */
 constexpr int kRowsBuffers = 4;
 
-template <int Stages, int Sub = 1> struct RowsSmem {
+constexpr int kRowsInboxPitch = 128 + sm100::kInboxPad; /* floats per row of the cluster form's inbox */
+
+template <int Stages, int Sub = 1, bool Cluster = false> struct RowsSmem {
     static constexpr int kBlockBytes = 2 * 128 * 128;    /* 128 rows x 128 B of each operand */
     static constexpr int kStageBytes = Sub * kBlockBytes; /* Sub K blocks per stage */
-    static constexpr int kStaging = 8 * 4096;         /* one 32 x 128 B slab per promotion warp */
+    /* one 32 x 128 B slab per promotion warp; in the cluster form the inbox instead:
+     * FP32 [K range][owned row][pitch], at most 128 + 7 rows in all */
+    static constexpr int kStaging =
+        Cluster ? ((128 + 8) * kRowsInboxPitch * 4 + 1023) / 1024 * 1024 : 8 * 4096;
     static constexpr int kTotal = Stages * kStageBytes + kStaging + 256 + 1024;
 };
 
-template <int Stages, int Sub = 1>
+template <int Stages, int Sub = 1, bool Cluster = false>
 __global__ void __launch_bounds__(kRowsThreads, 1)
     fp8_block_rows(const __grid_constant__ CUtensorMap map_p,
                    const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_d, const BlockTask task)
 {
     using namespace sm100;
-    using Layout = RowsSmem<Stages, Sub>;
+    using Layout = RowsSmem<Stages, Sub, Cluster>;
     constexpr int BN = 128;
     constexpr uint32_t kTmemColumns = kRowsBuffers * BN;
 
@@ -485,16 +490,23 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
     uint64_t *empty = full + Stages;
     uint64_t *tmem_full = empty + Stages;
     uint64_t *tmem_empty = tmem_full + kRowsBuffers;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + kRowsBuffers);
+    uint64_t *inbox_full = tmem_empty + kRowsBuffers; /* Cluster: every warp of every CTA delivered */
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(inbox_full + 1);
     volatile uint32_t *abort = tmem_slot + 1;
+    /* Cluster: FP32 sums delivered by the CTAs of the cluster, [K range][owned row][kPitch];
+     * memory of its own, so a CTA that is done early delivers while the others multiply */
+    constexpr int kPitch = kRowsInboxPitch;
+    float *inbox = reinterpret_cast<float *>(staging);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    bool cluster_waited = false; /* Cluster: this thread has waited on the set-up barrier */
     /* a unit is a tile, or one of `split` contiguous K ranges of a tile when the
      * tiles alone would leave most SMs idle; consecutive units are the K ranges
-     * of one tile */
+     * of one tile. Cluster: the grid has one CTA per unit and a cluster is the
+     * `split` units of one tile. */
     const int units = task.r_blocks * task.c_blocks * task.split;
     const int groups = task.k_blocks;
-    if (task.split > 1) {
+    if (!Cluster && task.split > 1) {
         /* the reduction over the K ranges may become resident now; it waits for
          * this grid's completion itself */
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -509,6 +521,14 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 8);
         }
+        if (Cluster) {
+            /* completed by the bytes of the bulk copies alone: every CTA of the
+             * cluster sends all the rows this one owns, 512 bytes each */
+            const int parts = task.split, part = static_cast<int>(cluster_rank());
+            const int owned = cluster_first_row(part + 1, parts) - cluster_first_row(part, parts);
+            mbar_init(inbox_full, 1);
+            mbar_arrive_expect_tx(inbox_full, uint32_t(owned) * 512u * uint32_t(parts));
+        }
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_p);
@@ -521,6 +541,10 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
     }
     tcgen05_fence_before();
     __syncthreads();
+    /* every CTA's inbox barrier must exist before a remote arrival: arrive here, wait
+     * only in front of the first remote access, after the multiplication */
+    if (Cluster)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -689,7 +713,76 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
             }
             if (!ok)
                 break;
-            if (task.split > 1) {
+            if constexpr (Cluster) {
+                /* The K ranges of this tile sit in the CTAs of this cluster. Each thread
+                 * puts its row of 64 sums into this CTA's operand ring (idle: the thread
+                 * has seen the last block complete) and sends it with one bulk copy
+                 * through distributed shared memory to the CTA that owns the row (tile
+                 * row i belongs to CTA i * parts / 128), slot `part` of its inbox; the
+                 * copy's bytes complete the owner's barrier. Stores of 16 bytes per
+                 * lane straight into the other CTA took 2.6 us for the 64 KB of a CTA
+                 * and their fence 1.1 us more. The owner adds the slots in K-range
+                 * order, as fp8_rows_reduce does, so the bits are those of the
+                 * two-launch form with the same ranges. The cluster barrier below was
+                 * arrived at by every thread of the cluster during set-up, so it cannot
+                 * hang; the wait for the bytes is bounded. */
+                const int parts = task.split, part = unit % parts;
+                const int rows_owned_max = (kBlockR + parts - 1) / parts;
+                asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+                cluster_waited = true;
+                {
+                    const int tile_row = quarter * 32 + lane;
+                    const int owner = (tile_row * parts) / kBlockR;
+                    const int local_row = tile_row - cluster_first_row(owner, parts);
+                    /* 272-byte pitch: 16-byte aligned rows, no bank conflicts between lanes */
+                    const uint32_t mine = smem_u32(smem) + ((warp - 2) * 32 + lane) * 272;
+#pragma unroll
+                    for (int i = 0; i < 64; i += 4)
+                        st_shared_v4(mine + i * 4, __float_as_uint(acc[i]), __float_as_uint(acc[i + 1]),
+                                     __float_as_uint(acc[i + 2]), __float_as_uint(acc[i + 3]));
+                    fence_proxy_async_smem();
+                    const uint32_t target = map_to_rank(
+                        smem_u32(inbox + (part * rows_owned_max + local_row) * kPitch + half * 64),
+                        owner);
+                    const uint32_t barrier = map_to_rank(smem_u32(inbox_full), owner);
+                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes "
+                                 "[%0], [%1], 256, [%2];" ::"r"(target),
+                                 "r"(mine), "r"(barrier)
+                                 : "memory");
+                }
+                if (!mbar_wait(inbox_full, 0, abort)) {
+                    report(task.status, abort, kRoleDrain);
+                    break;
+                }
+                const int first = cluster_first_row(part, parts);
+                const int owned = cluster_first_row(part + 1, parts) - first;
+                const int thread = (warp - 2) * 32 + lane; /* 0..255 */
+                constexpr int kVectors = BN / 8;
+                for (int item = thread; item < owned * kVectors; item += 256) {
+                    const int local_row = item / kVectors, c8 = (item - local_row * kVectors) * 8;
+                    const int out_row = rb * kBlockR + first + local_row, col = cb * BN + c8;
+                    if (out_row >= task.rows || col >= task.cols)
+                        continue;
+                    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int s = 0; s < parts; ++s) {
+                        const float4 *source = reinterpret_cast<const float4 *>(
+                            inbox + (s * rows_owned_max + local_row) * kPitch + c8);
+                        const float4 low = source[0], high = source[1];
+                        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
+                        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
+                    }
+                    /* the row tiling is only taken with a 16-byte aligned output whose
+                     * width and pitch are multiples of eight */
+                    uint4 packed;
+                    packed.x = pack_bf16(sum[0], sum[1]);
+                    packed.y = pack_bf16(sum[2], sum[3]);
+                    packed.z = pack_bf16(sum[4], sum[5]);
+                    packed.w = pack_bf16(sum[6], sum[7]);
+                    *reinterpret_cast<uint4 *>(task.out + static_cast<long long>(out_row) * task.ld_out +
+                                               col) = packed;
+                }
+                continue;
+            } else if (task.split > 1) {
                 /* FP32 sums of this K range: [range][row][column], 256 contiguous
                  * bytes per thread; fp8_rows_reduce adds the ranges in order */
                 if (row < task.rows) {
@@ -730,6 +823,15 @@ __global__ void __launch_bounds__(kRowsThreads, 1)
 
     tcgen05_fence_before();
     __syncthreads();
+    if (Cluster) {
+        /* The copies out of this CTA's shared memory are known to be complete only
+         * when their owners' barriers are: no CTA leaves before every CTA is past
+         * its inbox. Every thread of the cluster gets here, whatever gave up before. */
+        if (!cluster_waited)
+            asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    }
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
@@ -883,6 +985,9 @@ inline int prepare_kernels()
     status |= int(cudaFuncSetAttribute(fp8_block_rows<3, 2>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        RowsSmem<3, 2>::kTotal));
+    status |= int(cudaFuncSetAttribute(fp8_block_rows<4, 1, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       RowsSmem<4, 1, true>::kTotal));
 
     status |= prepare_kernel<16, 8, kStoreColumns>();
     status |= prepare_kernel<32, 8, kStoreColumns>();
@@ -895,6 +1000,53 @@ inline int prepare_kernels()
     status |= int(cudaFuncSetAttribute(fp8_token_kernel<true>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 16384));
     return status;
+}
+
+/* Launch shape of the row kernel whose K ranges are the CTAs of a cluster. */
+inline cudaLaunchConfig_t rows_cluster_config(camblas_cuda_context *context, int tiles, int parts,
+                                              cudaLaunchAttribute *attribute)
+{
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(unsigned(tiles) * unsigned(parts));
+    config.blockDim = dim3(kRowsThreads);
+    config.dynamicSmemBytes = RowsSmem<4, 1, true>::kTotal;
+    config.stream = context->stream;
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = unsigned(parts);
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return config;
+}
+
+/* Number of K ranges (2..8, at most `wanted`) for which the clusters of all
+ * `tiles` are resident together and no range is empty; 0 when there is none or
+ * the cluster form is switched off. The device is asked once per cluster size. */
+inline int rows_cluster_parts(camblas_cuda_context *context, int tiles, int k_blocks, int wanted)
+{
+    if (context->options.cluster_split == 0)
+        return 0;
+    for (int parts = std::min(wanted, 8); parts >= 2; --parts) {
+        const int per = (k_blocks + parts - 1) / parts;
+        if ((k_blocks + per - 1) / per != parts || 1ll * tiles * parts > context->sm_count)
+            continue;
+        int &cached = context->fp8_cluster_capacity[parts];
+        if (cached == 0) {
+            cudaLaunchAttribute attribute[1];
+            cudaLaunchConfig_t config = rows_cluster_config(context, 1, parts, attribute);
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, fp8_block_rows<4, 1, true>, &config) !=
+                cudaSuccess) {
+                cudaGetLastError();
+                clusters = 0;
+            }
+            cached = clusters > 0 ? clusters : -1;
+        }
+        if (cached >= tiles)
+            return parts;
+    }
+    return 0;
 }
 
 template <int BN, int Stages, int Mode>
@@ -954,13 +1106,30 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
          * 22 against 30 us). With half the SMs busy or a short K the second launch
          * costs more than it recovers (N = 7168, K = 2048: 15.6 against 12.1 us). */
         const int tiles = task.r_blocks * task.c_blocks;
+        int cluster_parts = 0;
         if ((context->options.fp8_rows == 0 || context->options.fp8_rows == 5) &&
             3 * tiles <= context->sm_count && task.k_blocks >= 32 &&
             outputs % 4 == 0) {
             int split = host::choose_split(tiles, task.k_blocks * 2, context->sm_count);
+            /* The K ranges as the CTAs of a cluster, added through distributed shared
+             * memory, when the device keeps all the clusters resident: no scratch
+             * round trip and no second launch. Its time does not depend on the
+             * number of rows, the two-launch form's does (N = 4096, K = 7168, 32 to
+             * 128 rows: 14.9 us against 14.3, 15.8, 18.4, 21.4 us; the forms cross
+             * between 64 and 96 rows on every shape measured). A cluster has at
+             * most eight CTAs, so with very few tiles the scratch form has several
+             * times as many CTAs and stays ahead (N = 512, K = 16384: 14.6 against
+             * 10.5-14.5 us). */
+            if (context->options.fp8_rows == 0 && rows >= 80) {
+                cluster_parts = rows_cluster_parts(context, tiles, task.k_blocks, split);
+                if (5 * cluster_parts < 2 * split)
+                    cluster_parts = 0;
+            }
+            if (cluster_parts > 0)
+                split = cluster_parts;
             task.k_blocks_per_split = (task.k_blocks + split - 1) / split;
             task.split = (task.k_blocks + task.k_blocks_per_split - 1) / task.k_blocks_per_split;
-            if (task.split > 1) {
+            if (task.split > 1 && cluster_parts == 0) {
                 int status = host::reserve_scratch(context,
                                                    size_t(task.split) * rows * outputs * sizeof(float));
                 if (status != 0)
@@ -977,6 +1146,16 @@ inline int block_gemm(camblas_cuda_context *context, int rows, int outputs, int 
         if (!ok)
             return host::fail(context, "tensor map encoding", 1);
         const int variant = context->options.fp8_rows; /* tuning aid: 1 four warps, 2 one block per stage */
+        if (cluster_parts > 0) {
+            cudaLaunchAttribute attribute[1];
+            cudaLaunchConfig_t config = rows_cluster_config(context, tiles, cluster_parts, attribute);
+            cudaError_t error =
+                cudaLaunchKernelEx(&config, fp8_block_rows<4, 1, true>, p, qm, d, task);
+            if (error != cudaSuccess)
+                return host::fail(context, "tcgen05 FP8 block GEMM, K ranges in a cluster", error);
+            context->kernel_launches.fetch_add(1, std::memory_order_relaxed);
+            return 0;
+        }
         if (variant == 1) {
             launch_block<128, 6, kStoreRows>(context, p, qm, d, task);
         } else {

@@ -219,3 +219,48 @@ def test_many_row_kernels_give_the_same_bits(rng, rows, outputs, inner):
                                                         wq_host[:256], w_scale_host[:2]))
     actual = results[5][sample][:, :256].float().cpu().numpy()
     assert oracle.rel_l2(actual, expected) < 4e-3
+
+
+@pytest.mark.parametrize("rows,outputs,inner", [
+    (128, 4096, 7168),   # 32 tiles, four K ranges each
+    (100, 2112, 7168),   # 17 tiles (the last holds 64 columns), ragged rows
+    (88, 1000, 4096),    # eight tiles, the last ragged, eight K ranges
+    (81, 1032, 4096),    # nine tiles, the last eight columns wide
+    (40, 1000, 4096),    # fewer than 80 rows: the two-launch form either way
+    (256, 512, 8192),    # two row blocks
+])
+def test_k_ranges_in_a_cluster(rng, rows, outputs, inner):
+    """Few tiles and a long K: the K ranges of a tile are the CTAs of a cluster and their
+    FP32 sums meet in distributed shared memory. Against the two-launch form (ranges to
+    scratch, then a reduction; option cluster_split = 0), which may cut K differently, and
+    against the oracle's recurrence on a sample of rows."""
+    generator = torch.Generator(device="cuda").manual_seed(88172 + rows)
+    x = torch.randn(rows, inner, device="cuda", generator=generator).bfloat16()
+    w = torch.randn(outputs, inner, device="cuda", generator=generator).bfloat16()
+    q, q_scale = _kernels.fp8_quantize(x)
+    wq_host, w_scale_host = oracle.fp8_quantize_weight(tensor_to_bits(w))
+    wq, w_scale = fp8_tensor(wq_host), torch.from_numpy(w_scale_host).cuda()
+    results = {}
+    for cluster_split in (1, 0):
+        with _native.options(cluster_split=cluster_split):
+            first = _kernels.fp8_block_gemm(q, q_scale, wq, w_scale)
+            again = _kernels.fp8_block_gemm(q, q_scale, wq, w_scale)
+            torch.cuda.synchronize()
+            assert _native.context(0).device_status() == 0
+            assert torch.equal(first, again)
+            results[cluster_split] = first
+    assert oracle.rel_l2(results[1].float().cpu().numpy(), results[0].float().cpu().numpy()) < 3e-3
+    sample = np.unique(np.linspace(0, rows - 1, 4).astype(int))
+    columns = min(outputs, 256)
+    bands = (columns + 127) // 128
+    expected = oracle.bf16_values(oracle.fp8_block_gemm(fp8_bytes(q)[sample], q_scale.cpu().numpy()[sample],
+                                                        wq_host[:columns], w_scale_host[:bands]))
+    for result in results.values():
+        actual = result[sample][:, :columns].float().cpu().numpy()
+        assert oracle.rel_l2(actual, expected) < 4e-3
+    bands_all = w_scale_host.shape[0]
+    expected = oracle.bf16_values(oracle.fp8_block_gemm(
+        fp8_bytes(q)[sample], q_scale.cpu().numpy()[sample], wq_host[(bands_all - 1) * 128:],
+        w_scale_host[bands_all - 1:]))
+    actual = results[1][sample][:, (bands_all - 1) * 128:].float().cpu().numpy()
+    assert oracle.rel_l2(actual, expected) < 4e-3
