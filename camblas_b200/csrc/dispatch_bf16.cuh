@@ -365,21 +365,32 @@ inline int run_tensor_rows(camblas_cuda_context *context, const Product &x)
      * forms pull the same 126 MB through L2 for that product, which is what
      * bounds them. */
     if (x.ta && !x.tb && x.run_if_set == nullptr && bn >= 128 && task.k_blocks >= 16) {
-        const int tiles = task.r_blocks * task.c_blocks;
-        const int parts = bn == 256 ? choose_cluster_parts<256, 4, sm100::kStoreRows>(
-                                          context, 0, tiles, task.k_blocks)
-                                    : choose_cluster_parts<128, 6, sm100::kStoreRows>(
-                                          context, 1, tiles, task.k_blocks);
+        /* This kernel stores eight columns at a time and looks up the output of each,
+         * so a packed projection needs cuts on multiples of eight only, not on tile
+         * boundaries: 256-column tiles pull a quarter fewer bytes through L2 than
+         * 128-column ones (the QKV shard of a rank at tensor-parallel 8 is 1024 +
+         * 128 + 128 columns). */
+        int wide = bn;
+        if (packed && x.m > 128 && x.cut0 % 8 == 0 && x.cut1 % 8 == 0)
+            wide = 256;
+        const int c_blocks = (x.m + wide - 1) / wide;
+        const int tiles = task.r_blocks * c_blocks;
+        const int parts = wide == 256 ? choose_cluster_parts<256, 4, sm100::kStoreRows>(
+                                            context, 0, tiles, task.k_blocks)
+                                      : choose_cluster_parts<128, 6, sm100::kStoreRows>(
+                                            context, 1, tiles, task.k_blocks);
         if (parts >= 2) {
+            task.c_blocks = c_blocks;
             task.out1 = x.c1, task.out2 = x.c2;
             task.ld_out1 = x.ldc1, task.ld_out2 = x.ldc2;
             CUtensorMap p, q;
             const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
             if (!encode_2d(context, &p, bf16, 2, x.b, x.k, x.n, x.ldb * 2, 64, 128) ||
-                !encode_2d(context, &q, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, bn))
+                !encode_2d(context, &q, bf16, 2, x.a, x.k, x.m, x.lda * 2, 64, wide))
                 return fail(context, "tensor map encoding", 1);
-            return bn == 256 ? launch_cluster<256, 4, sm100::kStoreRows>(context, tiles, parts, p, q, task)
-                             : launch_cluster<128, 6, sm100::kStoreRows>(context, tiles, parts, p, q, task);
+            return wide == 256
+                       ? launch_cluster<256, 4, sm100::kStoreRows>(context, tiles, parts, p, q, task)
+                       : launch_cluster<128, 6, sm100::kStoreRows>(context, tiles, parts, p, q, task);
         }
     }
     if (task.r_blocks <= 8 && sms / task.r_blocks >= 2) {
