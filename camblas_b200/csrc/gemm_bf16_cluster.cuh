@@ -12,25 +12,25 @@
  * CTAs (2..8) owns one 128 x BN tile: CTA p multiplies K range p into its own
  * tensor memory exactly as gemm_bf16_tcgen05 does (TMA producer warp, MMA
  * issuer warp, four epilogue warps), and then
- *   1. every CTA tells every other that its MMAs are complete, i.e. that its
- *      operand ring is idle (one remote mbarrier arrival per pair);
- *   2. every epilogue warp reads its 32 accumulator rows from tensor memory and
- *      stores each row into the operand ring of the CTA that OWNS that row
- *      (row i of the tile belongs to CTA i*S/128), slot p of that CTA's inbox,
- *      with st.shared::cluster; then it arrives on every CTA's inbox barrier
- *      (release at cluster scope);
- *   3. every CTA waits for the 4*S arrivals on its own inbox barrier (acquire at
- *      cluster scope), adds the S slots of its rows in K order in FP32, applies
- *      alpha, bias and beta*addend, rounds once and stores its rows.
- * One tile per cluster, so the ring is never needed again after step 1 and no
- * further hand-shake is required: after step 3 nothing remote touches the CTA
- * (all arrivals on its barriers and all stores into its inbox precede the
- * completion of its inbox barrier), so it may exit at once.
+ *   1. every epilogue warp copies its 32 accumulator rows from tensor memory
+ *      into the CTA's own operand ring (idle once its last MMA is complete);
+ *   2. the cluster meets at a hardware barrier (release / acquire);
+ *   3. every CTA reads the rows it OWNS (row i of the tile belongs to CTA
+ *      i*S/128) out of all S rings with ld.shared::cluster, whole 512-byte
+ *      stretches per warp and all S loads of a value in flight together, adds
+ *      them in K order in FP32, applies alpha, bias and beta*addend, rounds
+ *      once and stores its rows;
+ *   4. a second cluster barrier keeps every ring alive until all have read it.
+ * An earlier form pushed: each lane stored its accumulator row, 16 bytes at a
+ * time, into the owner's ring, and the owner added from there. A timeline taken
+ * inside that kernel on the QKV shard of a rank at tensor-parallel 8 (512 x
+ * 8192 -> 1280, six CTAs per tile, 21 us in all) showed 6 us for the stores
+ * into the other CTAs, 0.9 us for their fence and 2.7 us for the additions
+ * against 8 us for the multiplication itself.
  *
  * The sums are added in ascending K order by exactly one CTA per row, so results
- * are repeatable; every wait is bounded as elsewhere, and because the only
- * hardware cluster barrier is the one after set-up, a CTA that gives up cannot
- * leave the others waiting for longer than their own limits.
+ * are repeatable. Every thread of the cluster reaches both barriers whatever its
+ * bounded waits did before (nothing returns early), so they cannot hang.
  *
  * Mode kStoreRows: D[R,C] row-major (tokens on the tile rows), optional second
  * and third outputs of a packed projection. Mode kStoreColumns: operands
@@ -94,7 +94,24 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity
     return false;
 }
 
-constexpr int kInboxPad = 4; /* floats added to an inbox row: keeps 16-byte alignment, spreads banks */
+__device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_address)
+{
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_address)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_address)
+{
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_address) : "memory");
+    return v;
+}
+
+constexpr int kInboxPad = 4; /* floats added to a row of FP32 sums in shared memory: keeps 16-byte alignment, spreads banks */
 
 /* First tile row owned by CTA `part` of `parts`: rows are dealt out in
  * contiguous, nearly equal ranges. */
@@ -111,9 +128,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     static_assert(Mode == kStoreRows || Mode == kStoreColumns, "cluster split: rows or swapped");
     using Layout = GemmSmem<BN, Stages, kStoreColumns>; /* ring + barriers, no staging buffers */
     constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
-    constexpr int kPitch = BN + kInboxPad; /* floats per inbox row */
-    static_assert((kBlockR + 8) * kPitch * 4 <= Stages * Layout::kStageBytes,
-                  "the inbox fits in the operand ring");
+    /* FP32 sums of this CTA's K range over the ring. Rows: [tile row][kPitch], a
+     * row is read by its owner in 16-byte pieces. Swapped: [token][kColPitch], the
+     * output features of a token are contiguous in memory, so they are here. */
+    constexpr int kPitch = BN + kInboxPad;
+    constexpr int kColPitch = kBlockR + kInboxPad;
+    static_assert(kBlockR * kPitch * 4 <= Stages * Layout::kStageBytes &&
+                      BN * kColPitch * 4 <= Stages * Layout::kStageBytes,
+                  "the sums fit in the operand ring");
 
     extern __shared__ uint8_t raw_smem[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -121,11 +143,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + Stages * Layout::kStageBytes);
     uint64_t *empty = full + Stages;
     uint64_t *tmem_full = empty + Stages;
-    uint64_t *all_done = tmem_full + 1;   /* S arrivals: every CTA's MMAs are complete */
-    uint64_t *inbox_full = all_done + 1;  /* 4*S arrivals: every warp of every CTA has delivered */
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(inbox_full + 1);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_full + 1);
     volatile uint32_t *abort = tmem_slot + 1;
-    float *inbox = reinterpret_cast<float *>(smem); /* [S slots][rows owned][kPitch], over the ring */
+    const uint32_t sums = smem_u32(smem);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int parts = static_cast<int>(cluster_size());
@@ -134,7 +154,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     locate_tile(task, blockIdx.x / parts, rb, cb, batch);
     const int per_part = (task.k_blocks + parts - 1) / parts;
     const int kb0 = min(task.k_blocks, part * per_part), kb1 = min(task.k_blocks, kb0 + per_part);
-    const int rows_owned_max = (kBlockR + parts - 1) / parts;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Stages; ++s) {
@@ -142,8 +161,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&empty[s], 1);
         }
         mbar_init(tmem_full, 1);
-        mbar_init(all_done, parts);
-        mbar_init(inbox_full, 4 * parts);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_p);
@@ -155,7 +172,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     tcgen05_fence_before();
     __syncthreads();
-    cluster_sync(); /* every CTA's barriers exist before any remote arrival */
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -190,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int kb = kb0; kb < kb1; ++kb) {
-                if (!mbar_wait(&full[stage], phase, abort)) {
+                if (!mbar_wait_polling(&full[stage], phase, abort)) {
                     report(task.status, abort, kRoleMma);
                     ok = false;
                     break;
@@ -216,25 +232,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else {
-        /* ---- epilogue warps: exchange, then finish the rows this CTA owns ---- */
+        /* ---- epilogue warps, step 1: the accumulators into this CTA's ring ---- */
         const int quarter = warp & 3;
-        bool ok = mbar_wait(tmem_full, 0, abort);
+        const bool ok = mbar_wait(tmem_full, 0, abort);
         if (!ok)
             report(task.status, abort, kRoleEpilogueFull);
         tcgen05_fence_after();
-        if (ok && warp == 2 && lane < parts)
-            mbar_arrive_cluster(map_to_rank(smem_u32(all_done), lane));
-        if (ok && !mbar_wait_cluster(all_done, 0, abort)) {
-            report(task.status, abort, kRoleDrain);
-            ok = false;
-        }
         if (ok) {
-            /* step 2: this lane's accumulator row to its owner's inbox, slot `part` */
             const int row = quarter * 32 + lane; /* row of the tile */
-            const int owner = (row * parts) / kBlockR;
-            const int local_row = row - cluster_first_row(owner, parts);
-            const uint32_t target =
-                map_to_rank(smem_u32(inbox + (part * rows_owned_max + local_row) * kPitch), owner);
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             constexpr int kPiece = BN >= 32 ? 32 : 16;
 #pragma unroll 1
@@ -251,42 +256,66 @@ __global__ void __launch_bounds__(kThreads, 1)
                     for (int i = 0; i < kPiece; ++i)
                         acc[i] = 0u;
                 }
+                if constexpr (Mode == kStoreRows) {
+                    const uint32_t target = sums + (row * kPitch + chunk * kPiece) * 4;
 #pragma unroll
-                for (int i = 0; i < kPiece; i += 4)
-                    st_cluster_v4(target + (chunk * kPiece + i) * 4, __uint_as_float(acc[i]),
-                                  __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
-                                  __uint_as_float(acc[i + 3]));
-            }
-            fence_cluster();
-            __syncwarp();
-            if (lane < parts)
-                mbar_arrive_cluster(map_to_rank(smem_u32(inbox_full), lane));
-            if (!mbar_wait_cluster(inbox_full, 0, abort)) {
-                report(task.status, abort, kRoleDrain);
-                ok = false;
+                    for (int i = 0; i < kPiece; i += 4)
+                        st_shared_v4(target + i * 4, acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kPiece; ++i)
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(
+                                         sums + ((chunk * kPiece + i) * kColPitch + row) * 4),
+                                     "r"(acc[i])
+                                     : "memory");
+                }
             }
         }
-        if (ok) {
-            /* step 3: add the slots of the owned rows in K order and store them */
-            const int first = cluster_first_row(part, parts);
-            const int owned = cluster_first_row(part + 1, parts) - first;
-            const int thread = (warp - 2) * 32 + lane; /* 0..127 */
-            if constexpr (Mode == kStoreRows) {
-                /* eight consecutive columns per thread and step */
-                constexpr int kVectors = BN / 8;
-                for (int item = thread; item < owned * kVectors; item += 128) {
-                    const int local_row = item / kVectors, c8 = (item - local_row * kVectors) * 8;
-                    const int row = rb * kBlockR + first + local_row, col = cb * BN + c8;
-                    if (row >= task.rows || col >= task.cols)
+    }
+
+    /* step 2: every ring holds its CTA's sums (or the CTA has given up and said so) */
+    tcgen05_fence_before();
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+    if (warp >= 2 && *abort == 0) {
+        /* step 3: add the sums of the owned rows in K order and store them */
+        const int first = cluster_first_row(part, parts);
+        const int owned = cluster_first_row(part + 1, parts) - first;
+        const int thread = (warp - 2) * 32 + lane; /* 0..127 */
+        if constexpr (Mode == kStoreRows) {
+            /* four consecutive columns per thread and item, two items in flight: every
+             * load instruction of a warp reads 512 contiguous bytes of one ring */
+            constexpr int kQuads = BN / 4;
+            const int total = owned * kQuads;
+            for (int item0 = thread; item0 < total; item0 += 256) {
+                float4 piece[2][8];
+                int rows_of[2], cols_of[2];
+                bool live[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int item = item0 + u * 128;
+                    const int local_row = item / kQuads, c4 = (item - local_row * kQuads) * 4;
+                    rows_of[u] = rb * kBlockR + first + local_row, cols_of[u] = cb * BN + c4;
+                    live[u] = item < total && rows_of[u] < task.rows && cols_of[u] < task.cols;
+                    const uint32_t local = sums + ((first + local_row) * kPitch + c4) * 4;
+#pragma unroll
+                    for (int s = 0; s < 8; ++s)
+                        if (s < parts && live[u])
+                            piece[u][s] = ld_cluster_v4(map_to_rank(local, s));
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (!live[u])
                         continue;
-                    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    for (int s = 0; s < parts; ++s) {
-                        const float4 *source = reinterpret_cast<const float4 *>(
-                            inbox + (s * rows_owned_max + local_row) * kPitch + c8);
-                        const float4 low = source[0], high = source[1];
-                        sum[0] += low.x, sum[1] += low.y, sum[2] += low.z, sum[3] += low.w;
-                        sum[4] += high.x, sum[5] += high.y, sum[6] += high.z, sum[7] += high.w;
-                    }
+                    const int row = rows_of[u], col = cols_of[u];
+                    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int s = 0; s < 8; ++s)
+                        if (s < parts)
+                            sum[0] += piece[u][s].x, sum[1] += piece[u][s].y, sum[2] += piece[u][s].z,
+                                sum[3] += piece[u][s].w;
                     __nv_bfloat16 *out = task.out;
                     long long ld = task.ld_out;
                     int shift = 0, limit = min(task.cols, task.cut0);
@@ -297,59 +326,66 @@ __global__ void __launch_bounds__(kThreads, 1)
                         shift = third ? task.cut1 : task.cut0;
                         limit = third ? task.cols : task.cut1;
                     }
-                    float v[8];
+                    float v[4];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                    for (int i = 0; i < 4; ++i) {
                         v[i] = task.alpha * sum[i];
                         if (col + i < task.cols) {
                             if (task.bias != nullptr)
                                 v[i] += __bfloat162float(task.bias[col + i]);
                             if (task.beta != 0.f)
                                 v[i] = fmaf(task.beta,
-                                            __bfloat162float(task.addend[static_cast<long long>(row) *
-                                                                             task.ld_add +
-                                                                         col + i]),
+                                            __bfloat162float(
+                                                task.addend[static_cast<long long>(row) * task.ld_add +
+                                                            col + i]),
                                             v[i]);
                         }
                     }
                     __nv_bfloat16 *target = out + static_cast<long long>(row) * ld + (col - shift);
-                    if (col + 8 <= limit && (reinterpret_cast<uintptr_t>(target) & 15) == 0) {
-                        uint4 packed;
+                    if (col + 4 <= limit && (reinterpret_cast<uintptr_t>(target) & 7) == 0) {
+                        uint2 packed;
                         packed.x = pack_bf16(v[0], v[1]);
                         packed.y = pack_bf16(v[2], v[3]);
-                        packed.z = pack_bf16(v[4], v[5]);
-                        packed.w = pack_bf16(v[6], v[7]);
-                        *reinterpret_cast<uint4 *>(target) = packed;
+                        *reinterpret_cast<uint2 *>(target) = packed;
                     } else {
-                        for (int i = 0; i < 8 && col + i < limit; ++i)
+                        for (int i = 0; i < 4 && col + i < limit; ++i)
                             target[i] = __float2bfloat16_rn(v[i]);
                     }
                 }
-            } else {
-                /* swapped: tile rows are output features (contiguous in memory), tile
-                 * columns are tokens; consecutive threads take consecutive features */
-                for (int item = thread; item < owned * BN; item += 128) {
-                    const int token = item / owned, local_row = item - token * owned;
-                    const int feature = rb * kBlockR + first + local_row, column = cb * BN + token;
-                    if (feature >= task.rows || column >= task.cols)
-                        continue;
-                    float sum = 0.f;
-                    for (int s = 0; s < parts; ++s)
-                        sum += inbox[(s * rows_owned_max + local_row) * kPitch + token];
-                    float v = task.alpha * sum;
-                    if (task.bias != nullptr)
-                        v += __bfloat162float(task.bias[feature]);
-                    const long long at = static_cast<long long>(column);
-                    if (task.beta != 0.f)
-                        v = fmaf(task.beta, __bfloat162float(task.addend[at * task.ld_add + feature]), v);
-                    task.out[at * task.ld_out + feature] = __float2bfloat16_rn(v);
-                }
+            }
+        } else {
+            /* swapped: tile rows are output features (contiguous in memory), tile
+             * columns are tokens; consecutive threads take consecutive features */
+            for (int item = thread; item < owned * BN; item += 128) {
+                const int token = item / owned, local_row = item - token * owned;
+                const int feature = rb * kBlockR + first + local_row, column = cb * BN + token;
+                if (feature >= task.rows || column >= task.cols)
+                    continue;
+                const uint32_t local = sums + (token * kColPitch + first + local_row) * 4;
+                float piece[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < parts)
+                        piece[s] = ld_cluster_f32(map_to_rank(local, s));
+                float sum = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < parts)
+                        sum += piece[s];
+                float v = task.alpha * sum;
+                if (task.bias != nullptr)
+                    v += __bfloat162float(task.bias[feature]);
+                const long long at = static_cast<long long>(column);
+                if (task.beta != 0.f)
+                    v = fmaf(task.beta, __bfloat162float(task.addend[at * task.ld_add + feature]), v);
+                task.out[at * task.ld_out + feature] = __float2bfloat16_rn(v);
             }
         }
     }
 
-    tcgen05_fence_before();
-    __syncthreads();
+    /* step 4: nobody leaves while another CTA may still be reading its ring */
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
