@@ -279,23 +279,26 @@ __global__ void __launch_bounds__(kThreads, 1)
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
-    if (warp >= 2 && *abort == 0) {
-        /* step 3: add the sums of the owned rows in K order and store them */
+    if (*abort == 0) {
+        /* step 3: add the sums of the owned rows in K order and store them. All six
+         * warps take part: a load from another CTA's ring takes most of a
+         * microsecond, so what counts is how many are in flight. */
         const int first = cluster_first_row(part, parts);
         const int owned = cluster_first_row(part + 1, parts) - first;
-        const int thread = (warp - 2) * 32 + lane; /* 0..127 */
+        const int thread = threadIdx.x; /* 0..191 */
         if constexpr (Mode == kStoreRows) {
-            /* four consecutive columns per thread and item, two items in flight: every
+            /* four consecutive columns per thread and item, four items in flight: every
              * load instruction of a warp reads 512 contiguous bytes of one ring */
             constexpr int kQuads = BN / 4;
+            constexpr int kInFlight = 4;
             const int total = owned * kQuads;
-            for (int item0 = thread; item0 < total; item0 += 256) {
-                float4 piece[2][8];
-                int rows_of[2], cols_of[2];
-                bool live[2];
+            for (int item0 = thread; item0 < total; item0 += kInFlight * kThreads) {
+                float4 piece[kInFlight][8];
+                int rows_of[kInFlight], cols_of[kInFlight];
+                bool live[kInFlight];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int item = item0 + u * 128;
+                for (int u = 0; u < kInFlight; ++u) {
+                    const int item = item0 + u * kThreads;
                     const int local_row = item / kQuads, c4 = (item - local_row * kQuads) * 4;
                     rows_of[u] = rb * kBlockR + first + local_row, cols_of[u] = cb * BN + c4;
                     live[u] = item < total && rows_of[u] < task.rows && cols_of[u] < task.cols;
@@ -306,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                             piece[u][s] = ld_cluster_v4(map_to_rank(local, s));
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < kInFlight; ++u) {
                     if (!live[u])
                         continue;
                     const int row = rows_of[u], col = cols_of[u];
@@ -356,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
             /* swapped: tile rows are output features (contiguous in memory), tile
              * columns are tokens; consecutive threads take consecutive features */
-            for (int item = thread; item < owned * BN; item += 128) {
+            for (int item = thread; item < owned * BN; item += kThreads) {
                 const int token = item / owned, local_row = item - token * owned;
                 const int feature = rb * kBlockR + first + local_row, column = cb * BN + token;
                 if (feature >= task.rows || column >= task.cols)
