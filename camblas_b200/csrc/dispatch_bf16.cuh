@@ -573,6 +573,21 @@ inline int run_tensor_pair(camblas_cuda_context *context, const Product &x)
             }
         }
     }
+    /* One exception, measured: when the 256-column tiles fit in a single wave that
+     * leaves pairs idle, the product takes as long as one tile, and a tile's time
+     * falls with its width (512 x 8192 -> 5120, 40 tiles on 74 pairs: 46.6 us at
+     * 256 columns, 44.1 at 208, 42.4 at 144 with 72 tiles). Take the narrowest width
+     * from 144 columns that still needs one wave only; with a second wave every
+     * narrower width loses (-> 10240: 73.8 us at 256, 81 and more below). */
+    if (!stream_k && forced_width == 0 && bn == 256 && x.ta && x.run_if_set == nullptr &&
+        (!packed || (x.cut0 % 16 == 0 && x.cut1 % 16 == 0)) &&
+        1ll * task.r_blocks * ((x.m + 255) / 256) <= pairs_max) {
+        for (int width = 144; width < 256; width += 16)
+            if (1ll * task.r_blocks * ((x.m + width - 1) / width) <= pairs_max) {
+                best_width = width, best = 0.0;
+                break;
+            }
+    }
     if (best_width != 0) {
         const long long tiles = 1ll * task.r_blocks * ((x.m + bn - 1) / bn);
         const double plain = double((tiles + pairs_max - 1) / pairs_max) * tile_us(bn);
