@@ -50,50 +50,6 @@ __device__ __forceinline__ uint32_t cluster_size()
     return size;
 }
 
-__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_address, float a, float b, float c,
-                                              float d)
-{
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_address), "f"(a),
-                 "f"(b), "f"(c), "f"(d)
-                 : "memory");
-}
-
-__device__ __forceinline__ void fence_cluster()
-{
-    asm volatile("fence.acq_rel.cluster;" ::: "memory");
-}
-
-/* Bounded wait whose completion makes the shared-memory stores of other CTAs of
- * the cluster, released before their arrivals, visible to this thread. */
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity,
-                                                  volatile uint32_t *abort)
-{
-    unsigned long long started = 0;
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile("{\n"
-                     ".reg .pred p;\n"
-                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-                     "selp.u32 %0, 1, 0, p;\n"
-                     "}\n"
-                     : "=r"(done)
-                     : "r"(smem_u32(bar)), "r"(parity)
-                     : "memory");
-        if (done)
-            return true;
-        if ((spin & 255u) == 255u) {
-            if (*abort)
-                return false;
-            const unsigned long long now = global_timer_ns();
-            if (started == 0)
-                started = now;
-            else if (now - started > kWaitLimitNs)
-                return false;
-        }
-    }
-    return false;
-}
-
 __device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_address)
 {
     float4 v;
