@@ -294,7 +294,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buffer * kLayoutWidth;
                 for (int kb = u.kb0; kb < u.kb1; kb += Sub) {
-                    if (!mbar_wait(&full[stage], phase, abort)) {
+                    /* polled, not suspended: measured against the suspending wait in one
+                     * process, alternating, the polling form was level or up to 5 % faster
+                     * on the Llama projections and their shards */
+                    if (!mbar_wait_polling(&full[stage], phase, abort)) {
                         report(task.status, abort, kRoleMma);
                         ok = false;
                         break;
