@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int p_row = u.rb * kPairRows + rank * kBlockR;
                 const int q_row = u.cb * BN + rank * kHalf;
                 for (int kb = u.kb0; kb < u.kb1; kb += Sub) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort)) {
+                    if (!mbar_wait_polling(&empty[stage], phase ^ 1, abort)) {
                         report(task.status, abort, kRoleProducer);
                         ok = false;
                         break;
