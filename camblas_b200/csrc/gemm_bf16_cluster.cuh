@@ -342,9 +342,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     }
 
-    /* step 4: nobody leaves while another CTA may still be reading its ring */
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    /* step 4: nobody leaves while another CTA may still be reading its ring (the
+     * lanes of a warp leave the loops above after different numbers of items, so
+     * this is the form that does not ask for a converged warp) */
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
